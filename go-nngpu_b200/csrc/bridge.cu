@@ -1,0 +1,886 @@
+// C-ABI bridge: buffer handles, host<->device staging, per-device streams, the
+// reference's error convention, argument validation, and the dispatch of every
+// exported entry point onto the sm_100a kernels.  It replaces the reference's
+// Objective-C bridge files internal/cgo/metal_bridge_{buffer,matrix,fused,
+// kernels,activation,common}.m for the dense-GEMM path.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_set>
+
+#include "../../include/gonngpu.h"
+#include "kernels.h"
+
+namespace {
+
+using gonn::GemmStatus;
+
+constexpr uint64_t kMagic = 0x676f6e6e67707562ull;  // "gonngpub"
+constexpr int kMaxDevices = 16;
+constexpr size_t kStageBytes = 16u << 20;  // pinned staging chunk
+
+std::recursive_mutex g_mu;
+
+// Converted copy of a buffer for the tensor cores ("operand plane").
+struct Plane {
+  void* p0 = nullptr;
+  void* p1 = nullptr;
+  size_t bytes = 0;  // per plane
+  uint64_t version = ~0ull;
+  uint64_t rows = 0, cols = 0, pitch = 0;
+};
+
+struct Buffer {
+  uint64_t magic = kMagic;
+  int device = 0;
+  float* dptr = nullptr;
+  size_t bytes = 0;
+  bool owns = true;
+  float* host = nullptr;      // caller memory registered by create_gpu_buffer
+  bool host_pending = false;  // host bytes not yet copied to the device
+  uint64_t version = 1;       // bumped whenever the device contents change
+  Plane f16[2];               // [F16_RN], [F16_TRUNC]
+  Plane tf32;
+};
+
+struct Device {
+  int ordinal = -1;
+  bool ready = false;
+  cudaStream_t stream = nullptr;
+  cudaStream_t copy_stream = nullptr;
+  int sm_count = 0;
+  GemmStatus* status_host = nullptr;  // mapped pinned memory the kernels report into
+  GemmStatus* status_dev = nullptr;
+  GemmStatus last_status{};
+  void* stage[2] = {nullptr, nullptr};
+  cudaEvent_t stage_ev[2] = {nullptr, nullptr};
+};
+
+Device g_dev[kMaxDevices];
+int g_current = 0;
+bool g_blocking = true;
+bool g_plane_cache = true;
+gonn::GemmTuning g_tune;
+std::unordered_set<Buffer*> g_buffers;
+long g_stats[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+
+void set_error(CError* err, const char* fmt, ...) {
+  if (!err) return;
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  err->message = strdup(buf);
+}
+
+// Brings up the device's streams and staging memory once.
+// 0 ok, -1 no usable device, -2 stream / staging set-up failed.
+int ensure_device(int ordinal, CError* err) {
+  if (ordinal < 0 || ordinal >= kMaxDevices) {
+    set_error(err, "CUDA device ordinal %d out of range.", ordinal);
+    return -1;
+  }
+  Device& d = g_dev[ordinal];
+  if (cudaSetDevice(ordinal) != cudaSuccess) {
+    cudaGetLastError();
+    set_error(err, "Could not select CUDA device %d (no usable GPU).", ordinal);
+    return -1;
+  }
+  if (d.ready) return 0;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, ordinal) != cudaSuccess) {
+    cudaGetLastError();
+    set_error(err, "Could not query CUDA device %d.", ordinal);
+    return -1;
+  }
+  if (prop.major != 10) {
+    set_error(err, "Device %d is sm_%d%d; this library contains sm_100a code only.", ordinal,
+              prop.major, prop.minor);
+    return -1;
+  }
+  d.ordinal = ordinal;
+  d.sm_count = prop.multiProcessorCount;
+  bool ok = cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaStreamCreateWithFlags(&d.copy_stream, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaHostAlloc(reinterpret_cast<void**>(&d.status_host), sizeof(GemmStatus),
+                          cudaHostAllocMapped) == cudaSuccess &&
+            cudaHostGetDevicePointer(reinterpret_cast<void**>(&d.status_dev), d.status_host, 0) ==
+                cudaSuccess;
+  for (int i = 0; ok && i < 2; ++i) {
+    ok = cudaHostAlloc(&d.stage[i], kStageBytes, cudaHostAllocDefault) == cudaSuccess &&
+         cudaEventCreateWithFlags(&d.stage_ev[i], cudaEventDisableTiming) == cudaSuccess;
+  }
+  if (!ok) {
+    cudaGetLastError();
+    set_error(err, "Could not create CUDA streams / staging memory on device %d.", ordinal);
+    return -2;
+  }
+  std::memset(d.status_host, 0, sizeof(GemmStatus));
+  d.ready = true;
+  return 0;
+}
+
+Buffer* as_buffer(GPUPtr p) {
+  Buffer* b = static_cast<Buffer*>(p);
+  if (!b || g_buffers.find(b) == g_buffers.end() || b->magic != kMagic) return nullptr;
+  return b;
+}
+
+bool host_is_pinned(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return a.type == cudaMemoryTypeHost;
+}
+
+// Host -> device on the compute stream.  Page-locked sources go in one async
+// copy; pageable sources are pipelined through two pinned staging chunks.
+bool copy_h2d(Device& d, void* dst, const void* src, size_t bytes) {
+  if (bytes == 0) return true;
+  g_stats[1] += long(bytes);
+  if (host_is_pinned(src)) {
+    return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, d.stream) == cudaSuccess;
+  }
+  size_t off = 0;
+  int slot = 0;
+  while (off < bytes) {
+    const size_t n = bytes - off < kStageBytes ? bytes - off : kStageBytes;
+    if (cudaEventSynchronize(d.stage_ev[slot]) != cudaSuccess) return false;
+    std::memcpy(d.stage[slot], static_cast<const char*>(src) + off, n);
+    if (cudaMemcpyAsync(static_cast<char*>(dst) + off, d.stage[slot], n, cudaMemcpyHostToDevice,
+                        d.stream) != cudaSuccess)
+      return false;
+    if (cudaEventRecord(d.stage_ev[slot], d.stream) != cudaSuccess) return false;
+    off += n;
+    slot ^= 1;
+  }
+  return true;
+}
+
+// Device -> host, complete on return.
+bool copy_d2h(Device& d, void* dst, const void* src, size_t bytes) {
+  if (bytes == 0) return true;
+  g_stats[2] += long(bytes);
+  if (host_is_pinned(dst)) {
+    return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, d.stream) == cudaSuccess &&
+           cudaStreamSynchronize(d.stream) == cudaSuccess;
+  }
+  // chunk i is copied out of staging while chunk i+1 crosses the bus
+  size_t off = 0, pending_off = 0, pending_n = 0;
+  int slot = 0, pending_slot = -1;
+  while (off < bytes || pending_slot >= 0) {
+    int issued_slot = -1;
+    size_t n = 0;
+    if (off < bytes) {
+      n = bytes - off < kStageBytes ? bytes - off : kStageBytes;
+      if (cudaMemcpyAsync(d.stage[slot], static_cast<const char*>(src) + off, n,
+                          cudaMemcpyDeviceToHost, d.stream) != cudaSuccess)
+        return false;
+      if (cudaEventRecord(d.stage_ev[slot], d.stream) != cudaSuccess) return false;
+      issued_slot = slot;
+    }
+    if (pending_slot >= 0) {
+      if (cudaEventSynchronize(d.stage_ev[pending_slot]) != cudaSuccess) return false;
+      std::memcpy(static_cast<char*>(dst) + pending_off, d.stage[pending_slot], pending_n);
+    }
+    pending_slot = issued_slot;
+    pending_off = off;
+    pending_n = n;
+    off += n;
+    slot ^= 1;
+  }
+  return true;
+}
+
+// Makes the device copy current (lazy upload of registered host memory).
+bool make_resident(Device& d, Buffer* b) {
+  if (!b->host_pending) return true;
+  if (!copy_h2d(d, b->dptr, b->host, b->bytes)) return false;
+  b->host_pending = false;
+  ++b->version;
+  return true;
+}
+
+void wrote(Buffer* b) {
+  b->host_pending = false;
+  ++b->version;
+}
+
+void free_plane(Plane& p) {
+  if (p.p0) {
+    cudaFree(p.p0);
+    g_stats[0] -= long(p.bytes);
+    g_stats[6] -= long(p.bytes);
+  }
+  if (p.p1) {
+    cudaFree(p.p1);
+    g_stats[0] -= long(p.bytes);
+    g_stats[6] -= long(p.bytes);
+  }
+  p = Plane{};
+}
+
+inline uint64_t round_up(uint64_t v, uint64_t m) { return (v + m - 1) / m * m; }
+
+// Returns the operand plane(s) of `b` viewed as [rows, cols], converting when
+// the cached copy is stale.  kind: 0 fp16 RN, 1 fp16 trunc, 2 tf32 hi/lo.
+Plane* get_plane(Device& d, Buffer* b, uint64_t rows, uint64_t cols, int kind) {
+  Plane& p = (kind == 2) ? b->tf32 : b->f16[kind];
+  if (p.p0 && p.version == b->version && p.rows == rows && p.cols == cols) return &p;
+  const uint64_t pitch = round_up(cols, 64);
+  const size_t esz = (kind == 2) ? 4 : 2;
+  const size_t bytes = size_t(rows) * pitch * esz;
+  if (!p.p0 || p.bytes < bytes) {
+    free_plane(p);
+    if (cudaMalloc(&p.p0, bytes) != cudaSuccess) {
+      cudaGetLastError();
+      p = Plane{};
+      return nullptr;
+    }
+    g_stats[0] += long(bytes);
+    g_stats[6] += long(bytes);
+    if (kind == 2) {
+      if (cudaMalloc(&p.p1, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(p.p0);
+        g_stats[0] -= long(bytes);
+        g_stats[6] -= long(bytes);
+        p = Plane{};
+        return nullptr;
+      }
+      g_stats[0] += long(bytes);
+      g_stats[6] += long(bytes);
+    }
+    p.bytes = bytes;
+  }
+  p.rows = rows;
+  p.cols = cols;
+  p.pitch = pitch;
+  if (kind == 2) {
+    gonn::launch_split_tf32(b->dptr, rows, cols, static_cast<float*>(p.p0),
+                            static_cast<float*>(p.p1), pitch, d.stream);
+  } else {
+    gonn::launch_cvt_f16(b->dptr, rows, cols, p.p0, pitch, kind, d.stream);
+  }
+  ++g_stats[3];
+  p.version = b->version;
+  return &p;
+}
+
+// Ends an entry point: waits when blocking, then turns CUDA errors and kernel
+// status words into the reference-style error.  `exec_code` is the value the
+// entry point returns for an execution failure.
+int finish(Device& d, CError* err, int exec_code, const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess && g_blocking) e = cudaStreamSynchronize(d.stream);
+  if (e != cudaSuccess) {
+    set_error(err, "%s: CUDA error: %s", what, cudaGetErrorString(e));
+    return exec_code;
+  }
+  if (g_blocking && d.status_host->code != 0) {
+    d.last_status = *d.status_host;
+    std::memset(d.status_host, 0, sizeof(GemmStatus));
+    set_error(err,
+              "%s: GEMM kernel gave up waiting (role %u, where 0x%x, tile %u, k block %u).", what,
+              d.last_status.code, d.last_status.where, d.last_status.tile, d.last_status.kblock);
+    return exec_code;
+  }
+  return 0;
+}
+
+struct MatmulArgs {
+  GPUPtr a, b, c, bias;
+  long aRows, aCols, bRows, bCols, cRows, cCols;
+  bool transA, transB;
+  int precision;
+  float alpha, beta;
+  int act;
+  float act_param;
+};
+
+// Shared body of every GEMM entry point.  `codes` maps the failing step to the
+// caller's return value: {device, buffer, dims, setup, scratch, exec}.
+int matmul_core(const MatmulArgs& m, const int codes[6], const char* what, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* A = as_buffer(m.a);
+  Buffer* B = as_buffer(m.b);
+  Buffer* C = as_buffer(m.c);
+  Buffer* bias = m.bias ? as_buffer(m.bias) : nullptr;
+  if (!A || !B || !C || (m.bias && !bias)) {
+    set_error(err, "Invalid input or output buffer pointers.");
+    return codes[1];
+  }
+  if (int rc = ensure_device(C->device, err)) return rc == -1 ? codes[0] : codes[0];
+  Device& d = g_dev[C->device];
+  if (A->device != C->device || B->device != C->device || (bias && bias->device != C->device)) {
+    set_error(err, "%s: buffers live on different devices.", what);
+    return codes[1];
+  }
+  if (m.aRows <= 0 || m.aCols <= 0 || m.bRows <= 0 || m.bCols <= 0 || m.cRows <= 0 ||
+      m.cCols <= 0) {
+    set_error(err, "%s: matrix dimensions must be positive.", what);
+    return codes[2];
+  }
+  const long M = m.transA ? m.aCols : m.aRows, K = m.transA ? m.aRows : m.aCols;
+  const long Kb = m.transB ? m.bCols : m.bRows, N = m.transB ? m.bRows : m.bCols;
+  if (K != Kb || m.cRows != M || m.cCols != N) {
+    set_error(err, "%s: incompatible dimensions: op(A) %ldx%ld, op(B) %ldx%ld, C %ldx%ld.", what, M,
+              K, Kb, N, m.cRows, m.cCols);
+    return codes[2];
+  }
+  if (M >= (1l << 31) || N >= (1l << 31) || K >= (1l << 31)) {
+    set_error(err, "%s: dimensions beyond 2^31-1 are not supported.", what);
+    return codes[2];
+  }
+  if (size_t(m.aRows) * m.aCols * 4 > A->bytes || size_t(m.bRows) * m.bCols * 4 > B->bytes ||
+      size_t(M) * N * 4 > C->bytes || (bias && size_t(N) * 4 > bias->bytes)) {
+    set_error(err, "%s: a buffer is smaller than its stated matrix.", what);
+    return codes[2];
+  }
+  if (C == A || C == B || C->dptr == A->dptr || C->dptr == B->dptr) {
+    set_error(err, "%s: the result buffer must not alias an input.", what);
+    return codes[2];
+  }
+  if (m.precision < 0 || m.precision > 2) {
+    set_error(err, "%s: unknown precision %d.", what, m.precision);
+    return codes[2];
+  }
+  if (!make_resident(d, A) || !make_resident(d, B) || (bias && !make_resident(d, bias)) ||
+      (m.beta != 0.f && !make_resident(d, C))) {
+    cudaGetLastError();
+    set_error(err, "%s: host to device copy failed.", what);
+    return codes[5];
+  }
+  const int pkind = (m.precision == GONNGPU_FP32_3XTF32) ? 2 : (m.precision == GONNGPU_FP16_RN ? 0 : 1);
+  Plane* pa = get_plane(d, A, uint64_t(m.aRows), uint64_t(m.aCols), pkind);
+  Plane* pb = get_plane(d, B, uint64_t(m.bRows), uint64_t(m.bCols), pkind);
+  if (!pa || !pb) {
+    set_error(err, "%s: could not allocate operand planes.", what);
+    return codes[4];
+  }
+  gonn::GemmOperand oa, ob;
+  oa.plane0 = pa->p0;
+  oa.plane1 = pa->p1;
+  oa.pitch = pa->pitch;
+  oa.mn_major = m.transA;  // stored [K, M]: M contiguous
+  ob.plane0 = pb->p0;
+  ob.plane1 = pb->p1;
+  ob.pitch = pb->pitch;
+  ob.mn_major = !m.transB;  // stored [K, N]: N contiguous
+  gonn::GemmEpilogue epi;
+  epi.alpha = m.alpha;
+  epi.beta = m.beta;
+  epi.c_in = C->dptr;
+  epi.bias = bias ? bias->dptr : nullptr;
+  epi.act = m.act;
+  epi.act_param = m.act_param;
+  const char* msg = gonn::launch_gemm(pkind == 2 ? gonn::Kind::TF32x3 : gonn::Kind::F16, uint32_t(M),
+                                      uint32_t(N), uint32_t(K), oa, ob, C->dptr, uint64_t(N), epi,
+                                      d.status_dev, d.sm_count, g_tune, d.stream);
+  if (msg) {
+    cudaGetLastError();
+    set_error(err, "%s: %s", what, msg);
+    return codes[3];
+  }
+  ++g_stats[3];
+  ++g_stats[4];
+  wrote(C);
+  const int rc = finish(d, err, codes[5], what);
+  if (!g_plane_cache) {
+    if (g_blocking || cudaStreamSynchronize(d.stream) == cudaSuccess) {
+      free_plane(A->f16[0]); free_plane(A->f16[1]); free_plane(A->tf32);
+      free_plane(B->f16[0]); free_plane(B->f16[1]); free_plane(B->tf32);
+    }
+  }
+  return rc;
+}
+
+int new_buffer(int device, float* host, size_t bytes, void* wrap, Buffer** out, CError* err) {
+  if (int rc = ensure_device(device, err)) return rc;
+  Buffer* b = new Buffer();
+  b->device = device;
+  b->bytes = bytes;
+  b->host = host;
+  b->host_pending = (host != nullptr);
+  if (wrap) {
+    b->dptr = static_cast<float*>(wrap);
+    b->owns = false;
+  } else {
+    if (cudaMalloc(reinterpret_cast<void**>(&b->dptr), bytes ? bytes : 4) != cudaSuccess) {
+      cudaGetLastError();
+      delete b;
+      set_error(err, "Could not allocate %zu bytes of device memory.", bytes);
+      return -3;
+    }
+    g_stats[0] += long(bytes);
+  }
+  g_buffers.insert(b);
+  ++g_stats[5];
+  *out = b;
+  return 0;
+}
+
+}  // namespace
+
+// =========================================================================
+// Part 1: the reference bridge's symbols
+// =========================================================================
+extern "C" {
+
+int create_gpu_buffer(float* data, long length_bytes, GPUPtr* outGPUPtr, DevicePtr* outDevicePtr,
+                      CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!outGPUPtr || length_bytes < 0 || (length_bytes > 0 && !data)) {
+    set_error(err, "Could not create buffer: invalid arguments.");
+    return -3;
+  }
+  Buffer* b = nullptr;
+  if (int rc = new_buffer(g_current, data, size_t(length_bytes), nullptr, &b, err)) return rc;
+  *outGPUPtr = b;
+  if (outDevicePtr) *outDevicePtr = &g_dev[g_current];
+  return 0;
+}
+
+int retrieve_gpu_buffer_data(GPUPtr gpuPtr, float* data, long length_bytes, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* b = as_buffer(gpuPtr);
+  if (!b) {
+    set_error(err, "Invalid GPU buffer pointer.");
+    return -1;
+  }
+  if (length_bytes < 0 || size_t(length_bytes) > b->bytes) {
+    set_error(err, "Buffer length mismatch during retrieval.");
+    return -2;
+  }
+  if (length_bytes == 0) return 0;
+  if (!data) {
+    set_error(err, "Retrieval into a NULL pointer.");
+    return -3;
+  }
+  if (b->host_pending) {
+    // Never uploaded, never written: the registered host bytes are the contents.
+    if (data != b->host) std::memmove(data, b->host, size_t(length_bytes));
+    return 0;
+  }
+  if (ensure_device(b->device, err)) return -3;
+  Device& d = g_dev[b->device];
+  if (!copy_d2h(d, data, b->dptr, size_t(length_bytes))) {
+    cudaError_t e = cudaGetLastError();
+    set_error(err, "Device to host copy failed: %s", cudaGetErrorString(e));
+    return -3;
+  }
+  return 0;
+}
+
+int release_gpu_buffer(GPUPtr gpuPtr) {
+  if (!gpuPtr) return 0;
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* b = as_buffer(gpuPtr);
+  if (!b) return -1;
+  if (cudaSetDevice(b->device) == cudaSuccess && g_dev[b->device].ready) {
+    cudaStreamSynchronize(g_dev[b->device].stream);  // nothing in flight may still use it
+  }
+  free_plane(b->f16[0]);
+  free_plane(b->f16[1]);
+  free_plane(b->tf32);
+  if (b->owns && b->dptr) {
+    cudaFree(b->dptr);
+    g_stats[0] -= long(b->bytes);
+  }
+  cudaGetLastError();
+  g_buffers.erase(b);
+  --g_stats[5];
+  b->magic = 0;
+  delete b;
+  return 0;
+}
+
+void free_c_error_message(char* message) {
+  if (message) free(message);
+}
+
+int perform_mps_matrix_multiplication(GPUPtr aMatrixPtr, long aRows, long aCols, GPUPtr bMatrixPtr,
+                                      long bRows, long bCols, GPUPtr resultMatrixPtr,
+                                      long resultRows, long resultCols, DevicePtr /*device*/,
+                                      CError* err) {
+  MatmulArgs m{aMatrixPtr, bMatrixPtr, resultMatrixPtr, nullptr, aRows, aCols, bRows, bCols,
+               resultRows, resultCols, false, false, GONNGPU_FP32_3XTF32, 1.f, 0.f,
+               GONNGPU_ACT_NONE, 0.f};
+  static const int codes[6] = {-1, -2, -3, -4, -5, -6};
+  return matmul_core(m, codes, "matrix multiplication", err);
+}
+
+int perform_optimized_gemm(GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long M, long N, long K,
+                           float alpha, float beta, DevicePtr /*device*/, CError* err) {
+  MatmulArgs m{aPtr, bPtr, cPtr, nullptr, M, K, K, N, M, N, false, false, GONNGPU_FP32_3XTF32,
+               alpha, beta, GONNGPU_ACT_NONE, 0.f};
+  static const int codes[6] = {-1, -2, -3, -3, -3, -6};
+  return matmul_core(m, codes, "optimized GEMM", err);
+}
+
+int perform_fused_linear_activation(GPUPtr input, long batch_size, long input_size, GPUPtr weight,
+                                    long output_size, GPUPtr bias, int activation_type, float alpha,
+                                    GPUPtr output, DevicePtr /*device*/, CError* error) {
+  // The reference decodes 0..4 and treats every other code as identity.
+  const int act = (activation_type >= 0 && activation_type <= 4) ? activation_type : GONNGPU_ACT_NONE;
+  MatmulArgs m{input, weight, output, bias, batch_size, input_size, input_size, output_size,
+               batch_size, output_size, false, false, GONNGPU_FP32_3XTF32, 1.f, 0.f, act, alpha};
+  static const int codes[6] = {-1, -1, -3, -4, -5, -6};
+  return matmul_core(m, codes, "fused linear+activation", error);
+}
+
+int gonngpu_matmul_ex(GPUPtr a, long aRows, long aCols, int transA, GPUPtr b, long bRows,
+                      long bCols, int transB, GPUPtr c, long cRows, long cCols, int precision,
+                      float alpha, float beta, GPUPtr bias, int activation_type,
+                      float activation_param, CError* err) {
+  const int act = (activation_type >= 0 && activation_type <= 4) ? activation_type : GONNGPU_ACT_NONE;
+  MatmulArgs m{a, b, c, bias, aRows, aCols, bRows, bCols, cRows, cCols, transA != 0, transB != 0,
+               precision, alpha, beta, act, activation_param};
+  static const int codes[6] = {-1, -2, -3, -4, -5, -6};
+  return matmul_core(m, codes, "matmul_ex", err);
+}
+
+int perform_mps_matrix_transpose(GPUPtr inputMatrixPtr, long inputRows, long inputCols,
+                                 GPUPtr outputMatrixPtr, long outputRows, long outputCols,
+                                 DevicePtr /*device*/, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (inputRows != outputCols || inputCols != outputRows || inputRows < 0 || inputCols < 0) {
+    set_error(err, "Invalid transpose dimensions.");
+    return -2;
+  }
+  Buffer* in = as_buffer(inputMatrixPtr);
+  Buffer* out = as_buffer(outputMatrixPtr);
+  if (!in || !out) {
+    set_error(err, "Invalid input or output buffer pointers.");
+    return -3;
+  }
+  const size_t need = size_t(inputRows) * size_t(inputCols) * 4;
+  if (need > in->bytes || need > out->bytes || in->device != out->device || in == out ||
+      inputRows >= (1l << 31) || inputCols >= (1l << 31)) {
+    set_error(err, "Invalid transpose dimensions.");
+    return -2;
+  }
+  if (ensure_device(out->device, err)) return -1;
+  Device& d = g_dev[out->device];
+  if (!make_resident(d, in)) {
+    cudaGetLastError();
+    set_error(err, "transpose: host to device copy failed.");
+    return -6;
+  }
+  gonn::launch_transpose(in->dptr, uint64_t(inputRows), uint64_t(inputCols), out->dptr, d.sm_count,
+                         d.stream);
+  ++g_stats[3];
+  wrote(out);
+  return finish(d, err, -6, "transpose");
+}
+
+int perform_mps_matrix_add_broadcast(GPUPtr aMatrixPtr, long aRows, long aCols, GPUPtr bMatrixPtr,
+                                     long bRows, long bCols, GPUPtr resultMatrixPtr,
+                                     long resultRows, long resultCols, DevicePtr /*device*/,
+                                     CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* A = as_buffer(aMatrixPtr);
+  Buffer* B = as_buffer(bMatrixPtr);
+  Buffer* C = as_buffer(resultMatrixPtr);
+  if (!A || !B || !C) {
+    set_error(err, "Invalid input or output buffer pointers.");
+    return -3;
+  }
+  int mode = -1;
+  if (aRows == resultRows && aCols == resultCols && bRows == 1 && bCols == resultCols) mode = 0;
+  else if (bRows == resultRows && bCols == resultCols && aRows == 1 && aCols == resultCols) mode = 1;
+  else if (aRows == resultRows && aCols == resultCols && bRows == resultRows && bCols == 1) mode = 2;
+  else if (bRows == resultRows && bCols == resultCols && aRows == resultRows && aCols == 1) mode = 3;
+  if (mode < 0 || resultRows < 0 || resultCols < 0 ||
+      size_t(aRows) * aCols * 4 > A->bytes || size_t(bRows) * bCols * 4 > B->bytes ||
+      size_t(resultRows) * resultCols * 4 > C->bytes || A->device != C->device ||
+      B->device != C->device) {
+    set_error(err, "Unsupported broadcasting pattern: A (%ldx%ld) + B (%ldx%ld) -> Result (%ldx%ld)",
+              aRows, aCols, bRows, bCols, resultRows, resultCols);
+    return -2;
+  }
+  if (ensure_device(C->device, err)) return -1;
+  Device& d = g_dev[C->device];
+  if (!make_resident(d, A) || !make_resident(d, B)) {
+    cudaGetLastError();
+    set_error(err, "add broadcast: host to device copy failed.");
+    return -6;
+  }
+  gonn::launch_add_broadcast(A->dptr, B->dptr, C->dptr, uint64_t(resultRows), uint64_t(resultCols),
+                             mode, d.stream);
+  ++g_stats[3];
+  wrote(C);
+  return finish(d, err, -6, "add broadcast");
+}
+
+int perform_activation_relu_forward(GPUPtr inputPtr, long size, GPUPtr outputPtr,
+                                    DevicePtr /*device*/, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* in = as_buffer(inputPtr);
+  Buffer* out = as_buffer(outputPtr);
+  if (!in || !out || size < 0 || size_t(size) * 4 > in->bytes || size_t(size) * 4 > out->bytes ||
+      in->device != out->device) {
+    set_error(err, "Invalid buffer pointers for ReLU forward.");
+    return -1;
+  }
+  if (ensure_device(out->device, err)) return -1;
+  Device& d = g_dev[out->device];
+  if (!make_resident(d, in)) {
+    cudaGetLastError();
+    set_error(err, "ReLU forward: host to device copy failed.");
+    return -6;
+  }
+  gonn::launch_relu_forward(in->dptr, out->dptr, uint64_t(size), d.stream);
+  ++g_stats[3];
+  wrote(out);
+  return finish(d, err, -6, "ReLU forward");
+}
+
+int perform_activation_relu_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr, long size,
+                                     GPUPtr gradInputPtr, DevicePtr /*device*/, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* go = as_buffer(gradOutputPtr);
+  Buffer* act = as_buffer(activationOutputPtr);
+  Buffer* gi = as_buffer(gradInputPtr);
+  if (!go || !act || !gi || size < 0 || size_t(size) * 4 > go->bytes ||
+      size_t(size) * 4 > act->bytes || size_t(size) * 4 > gi->bytes || go->device != gi->device ||
+      act->device != gi->device) {
+    set_error(err, "Invalid buffer pointers for ReLU backward.");
+    return -1;
+  }
+  if (ensure_device(gi->device, err)) return -1;
+  Device& d = g_dev[gi->device];
+  if (!make_resident(d, go) || !make_resident(d, act)) {
+    cudaGetLastError();
+    set_error(err, "ReLU backward: host to device copy failed.");
+    return -6;
+  }
+  gonn::launch_relu_backward(go->dptr, act->dptr, gi->dptr, uint64_t(size), d.stream);
+  ++g_stats[3];
+  wrote(gi);
+  return finish(d, err, -6, "ReLU backward");
+}
+
+void* allocateSharedMemory(long size) {
+  if (size <= 0) return nullptr;
+  return gonngpu_host_alloc(size);
+}
+
+void* createGPUBufferFromSharedMemory(void* /*device*/, void* memory, long size) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!memory || size <= 0) return nullptr;
+  Buffer* b = nullptr;
+  if (new_buffer(g_current, static_cast<float*>(memory), size_t(size), nullptr, &b, nullptr))
+    return nullptr;
+  return b;
+}
+
+// =========================================================================
+// Part 2: additive entry points
+// =========================================================================
+
+int gonngpu_column_sum(GPUPtr inPtr, long rows, long cols, GPUPtr outPtr, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* in = as_buffer(inPtr);
+  Buffer* out = as_buffer(outPtr);
+  if (!in || !out) {
+    set_error(err, "Invalid input or output buffer pointers.");
+    return -2;
+  }
+  if (rows < 0 || cols < 0 || size_t(rows) * cols * 4 > in->bytes || size_t(cols) * 4 > out->bytes ||
+      in->device != out->device) {
+    set_error(err, "column sum: invalid dimensions.");
+    return -3;
+  }
+  if (ensure_device(out->device, err)) return -1;
+  Device& d = g_dev[out->device];
+  if (!make_resident(d, in)) {
+    cudaGetLastError();
+    set_error(err, "column sum: host to device copy failed.");
+    return -6;
+  }
+  gonn::launch_colsum(in->dptr, uint64_t(rows), uint64_t(cols), out->dptr, d.stream);
+  ++g_stats[3];
+  wrote(out);
+  return finish(d, err, -6, "column sum");
+}
+
+int gonngpu_alloc_device_buffer(long length_bytes, GPUPtr* out, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!out || length_bytes < 0) {
+    set_error(err, "Could not create buffer: invalid arguments.");
+    return -3;
+  }
+  Buffer* b = nullptr;
+  if (int rc = new_buffer(g_current, nullptr, size_t(length_bytes), nullptr, &b, err)) return rc;
+  *out = b;
+  return 0;
+}
+
+int gonngpu_wrap_device_memory(void* device_ptr, long length_bytes, GPUPtr* out, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!out || !device_ptr || length_bytes < 0) {
+    set_error(err, "Could not wrap device memory: invalid arguments.");
+    return -3;
+  }
+  Buffer* b = nullptr;
+  if (int rc = new_buffer(g_current, nullptr, size_t(length_bytes), device_ptr, &b, err)) return rc;
+  *out = b;
+  return 0;
+}
+
+void* gonngpu_device_address(GPUPtr buffer) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* b = as_buffer(buffer);
+  if (!b) return nullptr;
+  if (b->host_pending) {
+    if (ensure_device(b->device, nullptr)) return nullptr;
+    Device& d = g_dev[b->device];
+    if (!make_resident(d, b) || cudaStreamSynchronize(d.stream) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+  }
+  return b->dptr;
+}
+
+int gonngpu_upload(GPUPtr buffer, const float* data, long length_bytes, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* b = as_buffer(buffer);
+  if (!b) {
+    set_error(err, "Invalid GPU buffer pointer.");
+    return -1;
+  }
+  if (length_bytes < 0 || size_t(length_bytes) > b->bytes || (length_bytes > 0 && !data)) {
+    set_error(err, "Buffer length mismatch during upload.");
+    return -2;
+  }
+  if (ensure_device(b->device, err)) return -3;
+  Device& d = g_dev[b->device];
+  if (size_t(length_bytes) < b->bytes && !make_resident(d, b)) {
+    cudaGetLastError();
+    set_error(err, "Host to device copy failed.");
+    return -3;
+  }
+  if (!copy_h2d(d, b->dptr, data, size_t(length_bytes))) {
+    cudaGetLastError();
+    set_error(err, "Host to device copy failed.");
+    return -3;
+  }
+  wrote(b);
+  // Pageable sources were staged synchronously except for the last chunks in
+  // flight; blocking mode waits for them too.
+  if (g_blocking || !host_is_pinned(data)) {
+    if (cudaStreamSynchronize(d.stream) != cudaSuccess) {
+      cudaGetLastError();
+      set_error(err, "Host to device copy failed.");
+      return -3;
+    }
+  }
+  return 0;
+}
+
+int gonngpu_mark_modified(GPUPtr buffer) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* b = as_buffer(buffer);
+  if (!b) return -1;
+  wrote(b);
+  return 0;
+}
+
+void* gonngpu_host_alloc(long bytes) {
+  if (bytes <= 0) return nullptr;
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (ensure_device(g_current, nullptr)) return nullptr;
+  void* p = nullptr;
+  if (cudaHostAlloc(&p, size_t(bytes), cudaHostAllocPortable) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::memset(p, 0, size_t(bytes));
+  return p;
+}
+
+void gonngpu_host_free(void* p) {
+  if (!p) return;
+  cudaFreeHost(p);
+  cudaGetLastError();
+}
+
+int gonngpu_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int gonngpu_set_device(int ordinal) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (int rc = ensure_device(ordinal, nullptr)) return rc;
+  g_current = ordinal;
+  return 0;
+}
+
+int gonngpu_get_device(void) { return g_current; }
+
+void* gonngpu_stream(void) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (ensure_device(g_current, nullptr)) return nullptr;
+  return g_dev[g_current].stream;
+}
+
+int gonngpu_set_blocking(int blocking) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  g_blocking = blocking != 0;
+  return 0;
+}
+
+int gonngpu_synchronize(CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (int rc = ensure_device(g_current, err)) return rc;
+  Device& d = g_dev[g_current];
+  const bool was = g_blocking;
+  g_blocking = true;
+  const int rc = finish(d, err, -6, "synchronize");
+  g_blocking = was;
+  return rc;
+}
+
+int gonngpu_set_plane_cache(int enabled) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  g_plane_cache = enabled != 0;
+  return 0;
+}
+
+int gonngpu_set_gemm_tuning(int block_n, int max_ctas) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (block_n != 0 && block_n != 32 && block_n != 64 && block_n != 128 && block_n != 256) return -1;
+  g_tune.block_n = block_n;
+  g_tune.max_ctas = max_ctas < 0 ? 0 : max_ctas;
+  return 0;
+}
+
+void gonngpu_get_stats(long out[8]) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  for (int i = 0; i < 8; ++i) out[i] = g_stats[i];
+}
+
+void gonngpu_last_kernel_status(unsigned out[4]) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  const GemmStatus& s = g_dev[g_current].last_status;
+  out[0] = s.code;
+  out[1] = s.where;
+  out[2] = s.tile;
+  out[3] = s.kblock;
+}
+
+const char* gonngpu_version(void) { return "gonngpu-cuda 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,595 @@
+// Dense GEMM for sm_100a: C[M,N] = act(alpha * A.B + beta * C_in + bias).
+//
+// This is the kernel behind the reference's MatMul
+// (gpu/matrix/matrix.go:53-105 -> internal/cgo/metal_bridge_matrix.m:24-125),
+// its alpha/beta variant (internal/cgo/metal_bridge_kernels.m:417-486) and the
+// fused linear + bias + activation (internal/cgo/default.metal:459-509).
+//
+// Structure (one persistent CTA per SM, 6 warps):
+//   warp 0    TMA producer: cp.async.bulk.tensor boxes of 128-byte rows with the
+//             128-byte swizzle into a ring of shared-memory stages
+//   warp 1    TMEM owner and MMA issuer: one lane issues tcgen05.mma from
+//             shared-memory descriptors into one of two TMEM accumulators
+//   warps 2-5 epilogue: tcgen05.ld of the finished accumulator, alpha/beta/bias/
+//             activation in registers, stores to C; overlaps the next tile's
+//             main loop because the accumulators are double-buffered
+// Operands are fp16 (kind::f16) or pairs of tf32 planes (kind::tf32, three
+// MMAs per k step: lo.hi + hi.lo + hi.hi) and may be K-major or MN-major, so
+// A.B, At.B and A.Bt need no materialised transpose.
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace gonn {
+
+namespace {
+
+constexpr uint32_t BLOCK_M = 128;
+constexpr uint32_t SLAB_ROW_BYTES = 128;             // one swizzle row
+constexpr uint32_t A_TILE_BYTES = BLOCK_M * SLAB_ROW_BYTES;  // 16 KiB per plane per k block
+constexpr uint32_t KSTEPS = 4;                       // MMAs (per product) per k block
+constexpr uint32_t NUM_THREADS = 192;
+constexpr uint32_t SMEM_LIMIT = 227 * 1024;
+
+// How one operand's k-block tile is fetched by TMA and described to the MMA.
+struct OperandPlan {
+  uint32_t slabs;        // TMA boxes per tile per k block
+  uint32_t slab_bytes;   // shared-memory bytes per box
+  int32_t c0_tile, c0_slab, c0_k;  // box coordinate 0 = tile*c0_tile + slab*c0_slab + kb*c0_k
+  int32_t c1_tile, c1_k;           // box coordinate 1 = tile*c1_tile + kb*c1_k
+  uint32_t kstep_bytes;  // descriptor start-address advance per MMA k step
+  uint64_t desc;         // shared-memory descriptor without the start address
+};
+
+struct KernelParams {
+  OperandPlan a, b;
+  uint32_t M, N;
+  uint32_t tiles_m, tiles_n, num_tiles, num_kblocks, group_m;
+  uint32_t idesc;
+  float* C;
+  const float* c_in;
+  const float* bias;
+  uint64_t ldc;
+  float alpha, beta, act_param;
+  int act;
+  uint32_t vec_store;  // C base and pitch allow 16-byte stores
+  GemmStatus* status;
+};
+
+__device__ __forceinline__ void tile_coords(const KernelParams& p, uint32_t t, uint32_t& tm,
+                                            uint32_t& tn) {
+  // Groups of `group_m` row tiles sweep the columns together so that a wave of
+  // CTAs shares A rows and B columns in L2.
+  const uint32_t per_group = p.group_m * p.tiles_n;
+  const uint32_t g = t / per_group;
+  const uint32_t first_m = g * p.group_m;
+  const uint32_t gm = min(p.group_m, p.tiles_m - first_m);
+  const uint32_t r = t - g * per_group;
+  tm = first_m + r % gm;
+  tn = r / gm;
+}
+
+__device__ __forceinline__ float apply_act(float v, int act, float param) {
+  switch (act) {
+    case ACT_RELU: return fmaxf(v, 0.0f);
+    case ACT_LEAKY: return v > 0.0f ? v : v * param;
+    case ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
+    case ACT_TANH: return tanhf(v);
+    case ACT_GELU: return 0.5f * v * (1.0f + tanhf(0.7978845608f * (v + 0.044715f * v * v * v)));
+    default: return v;
+  }
+}
+
+__device__ __forceinline__ void report(GemmStatus* st, uint32_t code, uint32_t where,
+                                       uint32_t tile, uint32_t kb) {
+  // `st` may be page-locked host memory mapped into the device: plain stores
+  // only (the first reporter wins most of the time, which is all that is needed).
+  volatile GemmStatus* v = st;
+  if (v->code == 0u) {
+    v->where = where;
+    v->tile = tile;
+    v->kblock = kb;
+    v->code = code;
+  }
+}
+
+template <int KIND, int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
+                    const __grid_constant__ CUtensorMap tm_a1,
+                    const __grid_constant__ CUtensorMap tm_b0,
+                    const __grid_constant__ CUtensorMap tm_b1,
+                    const __grid_constant__ KernelParams p) {
+  constexpr uint32_t PLANES = (KIND == int(Kind::TF32x3)) ? 2 : 1;
+  constexpr uint32_t B_TILE_BYTES = BLOCK_N * SLAB_ROW_BYTES;
+  constexpr uint32_t STAGE_BYTES = PLANES * (A_TILE_BYTES + B_TILE_BYTES);
+  constexpr uint32_t TMEM_COLS = (2 * BLOCK_N < 32) ? 32 : 2 * BLOCK_N;
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
+
+  extern __shared__ uint8_t smem_raw[];
+  // Swizzled tiles need 1024-byte aligned bases.
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  // barrier slots: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&tm_a0);
+    ptx::prefetch_tmap(&tm_b0);
+    if (PLANES == 2) {
+      ptx::prefetch_tmap(&tm_a1);
+      ptx::prefetch_tmap(&tm_b1);
+    }
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    uint32_t stage = 0, phase = 0;
+    bool alive = true;
+    for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+      for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
+        bool ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 1, stage, t, kb);
+          }
+          alive = false;
+          break;
+        }
+        if (lane == 0) {
+          const uint32_t fb = full_bar(stage);
+          ptx::mbar_arrive_expect_tx(fb, STAGE_BYTES);
+          uint32_t dst = smem_base + stage * STAGE_BYTES;
+#pragma unroll
+          for (uint32_t pl = 0; pl < PLANES; ++pl) {
+            const CUtensorMap* ma = pl ? &tm_a1 : &tm_a0;
+            for (uint32_t s = 0; s < p.a.slabs; ++s) {
+              ptx::tma_load_2d(dst + s * p.a.slab_bytes, ma,
+                               int32_t(tm) * p.a.c0_tile + int32_t(s) * p.a.c0_slab +
+                                   int32_t(kb) * p.a.c0_k,
+                               int32_t(tm) * p.a.c1_tile + int32_t(kb) * p.a.c1_k, fb);
+            }
+            dst += A_TILE_BYTES;
+          }
+#pragma unroll
+          for (uint32_t pl = 0; pl < PLANES; ++pl) {
+            const CUtensorMap* mb = pl ? &tm_b1 : &tm_b0;
+            for (uint32_t s = 0; s < p.b.slabs; ++s) {
+              ptx::tma_load_2d(dst + s * p.b.slab_bytes, mb,
+                               int32_t(tn) * p.b.c0_tile + int32_t(s) * p.b.c0_slab +
+                                   int32_t(kb) * p.b.c0_k,
+                               int32_t(tn) * p.b.c1_tile + int32_t(kb) * p.b.c1_k, fb);
+            }
+            dst += B_TILE_BYTES;
+          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    uint32_t stage = 0, phase = 0;
+    uint32_t local = 0;
+    bool alive = true;
+    for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x, ++local) {
+      const uint32_t acc = local & 1u;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      bool ok = ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          report(p.status, 2, 0x100u | acc, t, 0);
+        }
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+      for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
+        ok = ptx::mbar_wait(full_bar(stage), phase, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 2, stage, t, kb);
+          }
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_addr = a_addr + PLANES * A_TILE_BYTES;
+#pragma unroll
+          for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+            const uint32_t accum = (kb | ks) ? 1u : 0u;
+            const uint64_t a_hi = ptx::smem_desc_at(p.a.desc, a_addr + ks * p.a.kstep_bytes);
+            const uint64_t b_hi = ptx::smem_desc_at(p.b.desc, b_addr + ks * p.b.kstep_bytes);
+            if (KIND == int(Kind::F16)) {
+              ptx::mma_f16(d_tmem, a_hi, b_hi, p.idesc, accum);
+            } else {
+              const uint64_t a_lo =
+                  ptx::smem_desc_at(p.a.desc, a_addr + A_TILE_BYTES + ks * p.a.kstep_bytes);
+              const uint64_t b_lo =
+                  ptx::smem_desc_at(p.b.desc, b_addr + B_TILE_BYTES + ks * p.b.kstep_bytes);
+              ptx::mma_tf32(d_tmem, a_lo, b_hi, p.idesc, accum);
+              ptx::mma_tf32(d_tmem, a_hi, b_lo, p.idesc, 1u);
+              ptx::mma_tf32(d_tmem, a_hi, b_hi, p.idesc, 1u);
+            }
+          }
+          ptx::mma_commit(empty_bar(stage));  // stage reusable once these MMAs retired
+          if (kb + 1 == p.num_kblocks) ptx::mma_commit(tfull_bar(acc));
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may read
+    uint32_t local = 0;
+    for (uint32_t t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++local) {
+      const uint32_t acc = local & 1u;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+      bool ok = ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          report(p.status, 3, acc, t, 0);
+        }
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t row = tm * BLOCK_M + quarter * 32u + lane;
+      const uint32_t col_tile = tn * BLOCK_N;
+      const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * BLOCK_N;
+      float* c_row = p.C + uint64_t(row) * p.ldc;
+      const float* cin_row = p.c_in ? p.c_in + uint64_t(row) * p.ldc : nullptr;
+#pragma unroll 1
+      for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
+        const uint32_t col0 = col_tile + ch * 32u;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + ch * 32u, r);
+        ptx::tmem_ld_wait();
+        if (row < p.M) {
+          const bool full_chunk = (col0 + 32u <= p.N);
+          if (full_chunk && p.vec_store) {
+#pragma unroll
+            for (uint32_t j = 0; j < 32; j += 4) {
+              float4 v;
+              v.x = __uint_as_float(r[j + 0]) * p.alpha;
+              v.y = __uint_as_float(r[j + 1]) * p.alpha;
+              v.z = __uint_as_float(r[j + 2]) * p.alpha;
+              v.w = __uint_as_float(r[j + 3]) * p.alpha;
+              if (cin_row) {
+                const float4 o = *reinterpret_cast<const float4*>(cin_row + col0 + j);
+                v.x += p.beta * o.x;
+                v.y += p.beta * o.y;
+                v.z += p.beta * o.z;
+                v.w += p.beta * o.w;
+              }
+              if (p.bias) {
+                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+                v.x += b.x;
+                v.y += b.y;
+                v.z += b.z;
+                v.w += b.w;
+              }
+              if (p.act >= 0) {
+                v.x = apply_act(v.x, p.act, p.act_param);
+                v.y = apply_act(v.y, p.act, p.act_param);
+                v.z = apply_act(v.z, p.act, p.act_param);
+                v.w = apply_act(v.w, p.act, p.act_param);
+              }
+              *reinterpret_cast<float4*>(c_row + col0 + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (uint32_t j = 0; j < 32; ++j) {
+              const uint32_t col = col0 + j;
+              if (col < p.N) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (cin_row) v += p.beta * cin_row[col];
+                if (p.bias) v += p.bias[col];
+                if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
+                c_row[col] = v;
+              }
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A role gave up: give copies and MMAs already in flight time to land
+    // before shared memory and TMEM are handed back.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
+      if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
+      __nanosleep(1000);
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------- host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  });
+  return fn;
+}
+
+// 2-D map over a row-major plane: `inner` contiguous elements per row, `outer`
+// rows, boxes of (128 bytes, box_rows) written with the 128-byte swizzle.
+bool make_map(CUtensorMap* map, bool f32, const void* base, uint64_t inner, uint64_t outer,
+              uint64_t pitch_elems, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return false;
+  const uint32_t esz = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_elems * esz};
+  cuuint32_t box[2] = {SLAB_ROW_BYTES / esz, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Plan for an operand whose tile spans `tile_mn` rows/columns of the output.
+OperandPlan plan_operand(bool f32, bool mn_major, uint32_t tile_mn, uint32_t block_k) {
+  const uint32_t esz = f32 ? 4 : 2;
+  const uint32_t row_elems = SLAB_ROW_BYTES / esz;  // == block_k
+  const uint32_t umma_k = 32 / esz;                 // 16 (f16) or 8 (tf32)
+  OperandPlan o{};
+  if (!mn_major) {
+    // rows = MN index, 128 bytes of K per row: one box; 8-row groups 1024 B apart.
+    o.slabs = 1;
+    o.slab_bytes = tile_mn * SLAB_ROW_BYTES;
+    o.c0_tile = 0;
+    o.c0_slab = 0;
+    o.c0_k = int32_t(block_k);
+    o.c1_tile = int32_t(tile_mn);
+    o.c1_k = 0;
+    o.kstep_bytes = umma_k * esz;  // 32 bytes inside the swizzled row
+    o.desc = ptx::smem_desc_sw128(16, 1024);
+  } else {
+    // rows = K index, 128 bytes of MN per row: one box per 128 bytes of MN.
+    o.slabs = tile_mn / row_elems;
+    o.slab_bytes = block_k * SLAB_ROW_BYTES;
+    o.c0_tile = int32_t(tile_mn);
+    o.c0_slab = int32_t(row_elems);
+    o.c0_k = 0;
+    o.c1_tile = 0;
+    o.c1_k = int32_t(block_k);
+    o.kstep_bytes = umma_k * SLAB_ROW_BYTES;  // umma_k rows down
+    o.desc = ptx::smem_desc_sw128(o.slab_bytes, 1024);
+  }
+  return o;
+}
+
+template <int KIND, int BLOCK_N>
+constexpr int stages_for() {
+  constexpr uint32_t planes = (KIND == int(Kind::TF32x3)) ? 2 : 1;
+  constexpr uint32_t stage = planes * (A_TILE_BYTES + BLOCK_N * SLAB_ROW_BYTES);
+  constexpr uint32_t avail = SMEM_LIMIT - 1024 /*align*/ - 256 /*barriers*/;
+  constexpr int s = int(avail / stage);
+  return s > 8 ? 8 : s;
+}
+
+template <int KIND, int BLOCK_N>
+const char* launch_variant(const CUtensorMap* maps, const KernelParams& kp, uint32_t grid,
+                           cudaStream_t stream) {
+  constexpr int STAGES = stages_for<KIND, BLOCK_N>();
+  constexpr uint32_t planes = (KIND == int(Kind::TF32x3)) ? 2 : 1;
+  constexpr uint32_t smem = STAGES * planes * (A_TILE_BYTES + BLOCK_N * SLAB_ROW_BYTES) + 1024 + 256;
+  static_assert(STAGES >= 2, "pipeline too shallow");
+  static_assert(smem <= SMEM_LIMIT, "shared memory");
+  auto kern = gemm_tcgen05_kernel<KIND, BLOCK_N, STAGES>;
+  static bool attr_done_dev[64] = {};  // per variant and device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool& attr_done = attr_done_dev[dev & 63];
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+        cudaSuccess) {
+      return "cudaFuncSetAttribute(max dynamic shared memory) failed";
+    }
+    attr_done = true;
+  }
+  kern<<<grid, NUM_THREADS, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], kp);
+  if (cudaGetLastError() != cudaSuccess) return "GEMM kernel launch failed";
+  return nullptr;
+}
+
+int choose_block_n(Kind kind, uint32_t M, uint32_t N, uint32_t K, int sms) {
+  // Cheapest estimated time: waves x per-tile cost, where a tile costs the
+  // larger of its tensor-pipe time and its shared-memory read time per k step,
+  // plus a fixed prologue/epilogue share.
+  const uint32_t tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
+  const double mma_per_step = (kind == Kind::TF32x3) ? 3.0 : 1.0;
+  const double rate = (kind == Kind::TF32x3) ? 0.5 : 1.0;  // tf32 runs at half the f16 rate
+  int best = 32;
+  double best_cost = 1e300;
+  const int cands[4] = {256, 128, 64, 32};
+  for (int bn : cands) {
+    if (bn > 32 && uint32_t(bn) >= 2 * ((N + 31) / 32) * 32) continue;  // mostly padding
+    const uint32_t tiles_n = (N + bn - 1) / bn;
+    const double tiles = double(tiles_m) * tiles_n;
+    const double waves = std::ceil(tiles / sms);
+    const double pipe = mma_per_step * (128.0 * bn * 32.0) / (8192.0 * rate);  // cycles / k step
+    const double smem = mma_per_step * (4096.0 + bn * 32.0) / 128.0;           // cycles / k step
+    const double ksteps = std::ceil(double(K) / (kind == Kind::TF32x3 ? 8.0 : 16.0));
+    const double cost = waves * (std::max(pipe, smem) * ksteps + 2000.0 + 8.0 * bn);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const GemmOperand& A,
+                        const GemmOperand& B, float* C, uint64_t ldc, const GemmEpilogue& epi,
+                        GemmStatus* status, int sm_count, const GemmTuning& tune,
+                        cudaStream_t stream) {
+  if (M == 0 || N == 0 || K == 0) return "GEMM dimensions must be positive";
+  const bool f32 = (kind == Kind::TF32x3);
+  const uint32_t esz = f32 ? 4 : 2;
+  const uint32_t block_k = SLAB_ROW_BYTES / esz;
+  if ((A.pitch * esz) % 16 || (B.pitch * esz) % 16) return "operand pitch must be a multiple of 16 bytes";
+  if (reinterpret_cast<uintptr_t>(A.plane0) % 16 || reinterpret_cast<uintptr_t>(B.plane0) % 16)
+    return "operand planes must be 16-byte aligned";
+  if (f32 && (!A.plane1 || !B.plane1)) return "TF32x3 needs the low planes";
+
+  int bn = tune.block_n ? tune.block_n : choose_block_n(kind, M, N, K, sm_count);
+  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return "unsupported BLOCK_N";
+  // An N-major fp16 tile narrower than one 128-byte swizzle row (64 columns)
+  // would need the 64-byte swizzle; use the 64-wide tile instead.
+  if (!f32 && B.mn_major && bn == 32) bn = 64;
+
+  KernelParams kp{};
+  kp.a = plan_operand(f32, A.mn_major, BLOCK_M, block_k);
+  kp.b = plan_operand(f32, B.mn_major, uint32_t(bn), block_k);
+  kp.M = M;
+  kp.N = N;
+  kp.tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
+  kp.tiles_n = (N + bn - 1) / bn;
+  kp.num_tiles = kp.tiles_m * kp.tiles_n;
+  kp.num_kblocks = (K + block_k - 1) / block_k;
+  kp.group_m = 16;
+  kp.idesc = ptx::make_idesc(f32 ? 2u : 0u, A.mn_major, B.mn_major, BLOCK_M, uint32_t(bn));
+  kp.C = C;
+  kp.c_in = (epi.beta != 0.f) ? epi.c_in : nullptr;
+  kp.bias = epi.bias;
+  kp.ldc = ldc;
+  kp.alpha = epi.alpha;
+  kp.beta = epi.beta;
+  kp.act = epi.act;
+  kp.act_param = epi.act_param;
+  kp.vec_store = (ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(C) % 16 == 0) &&
+                 (!kp.c_in || reinterpret_cast<uintptr_t>(kp.c_in) % 16 == 0) &&
+                 (!kp.bias || reinterpret_cast<uintptr_t>(kp.bias) % 16 == 0);
+  kp.status = status;
+
+  // Tensor maps: inner extent is the contiguous index, outer the row index.
+  CUtensorMap maps[4];
+  std::memset(maps, 0, sizeof(maps));
+  const uint32_t a_box_rows = A.mn_major ? block_k : BLOCK_M;
+  const uint32_t b_box_rows = B.mn_major ? block_k : uint32_t(bn);
+  const uint64_t a_inner = A.mn_major ? M : K, a_outer = A.mn_major ? K : M;
+  const uint64_t b_inner = B.mn_major ? N : K, b_outer = B.mn_major ? K : N;
+  if (!make_map(&maps[0], f32, A.plane0, a_inner, a_outer, A.pitch, a_box_rows) ||
+      !make_map(&maps[2], f32, B.plane0, b_inner, b_outer, B.pitch, b_box_rows))
+    return "cuTensorMapEncodeTiled failed";
+  if (f32) {
+    if (!make_map(&maps[1], f32, A.plane1, a_inner, a_outer, A.pitch, a_box_rows) ||
+        !make_map(&maps[3], f32, B.plane1, b_inner, b_outer, B.pitch, b_box_rows))
+      return "cuTensorMapEncodeTiled failed";
+  } else {
+    maps[1] = maps[0];
+    maps[3] = maps[2];
+  }
+
+  uint32_t grid = std::min<uint32_t>(kp.num_tiles, uint32_t(tune.max_ctas > 0 ? tune.max_ctas : sm_count));
+  if (kind == Kind::F16) {
+    switch (bn) {
+      case 256: return launch_variant<0, 256>(maps, kp, grid, stream);
+      case 128: return launch_variant<0, 128>(maps, kp, grid, stream);
+      case 64: return launch_variant<0, 64>(maps, kp, grid, stream);
+      default: return launch_variant<0, 32>(maps, kp, grid, stream);
+    }
+  } else {
+    switch (bn) {
+      case 256: return launch_variant<1, 256>(maps, kp, grid, stream);
+      case 128: return launch_variant<1, 128>(maps, kp, grid, stream);
+      case 64: return launch_variant<1, 64>(maps, kp, grid, stream);
+      default: return launch_variant<1, 32>(maps, kp, grid, stream);
+    }
+  }
+}
+
+}  // namespace gonn

@@ -1,0 +1,292 @@
+// HBM-bound kernels of the dense path: Transpose, the operand pre-passes
+// (fp32 -> fp16 plane, fp32 -> tf32 hi/lo planes), bias broadcast add, ReLU
+// forward/backward and the bias-gradient column sum.  All are pure streaming
+// kernels: coalesced 16-byte accesses where alignment allows, scalar edges.
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+
+namespace gonn {
+
+namespace {
+
+// ------------------------------------------------------------------ transpose
+// out[c, r] = in[r, c]; the element moves of
+// internal/cgo/metal_bridge_matrix.m:159-166, tiled through shared memory so
+// that both the read of `in` and the write of `out` are coalesced.
+constexpr int TT = 64;  // tile edge
+
+template <bool VEC_IN, bool VEC_OUT>
+__global__ void __launch_bounds__(256) transpose_kernel(const float* __restrict__ in,
+                                                        float* __restrict__ out, uint32_t rows,
+                                                        uint32_t cols, uint32_t tiles_c) {
+  __shared__ float tile[TT][TT + 1];  // tile[c][r]
+  const uint32_t tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
+  const uint32_t r0 = tr * TT, c0 = tc * TT;
+  const uint32_t tid = threadIdx.x;
+
+  if (VEC_IN) {
+    // 64 rows x 16 float4: thread -> (row = i / 16, c4 = i % 16)
+#pragma unroll
+    for (uint32_t it = 0; it < 4; ++it) {
+      const uint32_t i = tid + it * 256;
+      const uint32_t r = i >> 4, c = (i & 15u) << 2;
+      if (r0 + r < rows && c0 + c < cols) {  // cols % 4 == 0: the float4 is whole
+        const float4 v =
+            __ldcs(reinterpret_cast<const float4*>(in + uint64_t(r0 + r) * cols + c0 + c));
+        tile[c + 0][r] = v.x;
+        tile[c + 1][r] = v.y;
+        tile[c + 2][r] = v.z;
+        tile[c + 3][r] = v.w;
+      }
+    }
+  } else {
+#pragma unroll 4
+    for (uint32_t it = 0; it < 16; ++it) {
+      const uint32_t i = tid + it * 256;
+      const uint32_t r = i >> 6, c = i & 63u;
+      if (r0 + r < rows && c0 + c < cols) tile[c][r] = in[uint64_t(r0 + r) * cols + c0 + c];
+    }
+  }
+  __syncthreads();
+  if (VEC_OUT) {
+#pragma unroll
+    for (uint32_t it = 0; it < 4; ++it) {
+      const uint32_t i = tid + it * 256;
+      const uint32_t c = i >> 4, r = (i & 15u) << 2;
+      if (c0 + c < cols && r0 + r < rows) {  // rows % 4 == 0
+        float4 v;
+        v.x = tile[c][r + 0];
+        v.y = tile[c][r + 1];
+        v.z = tile[c][r + 2];
+        v.w = tile[c][r + 3];
+        __stcs(reinterpret_cast<float4*>(out + uint64_t(c0 + c) * rows + r0 + r), v);
+      }
+    }
+  } else {
+#pragma unroll 4
+    for (uint32_t it = 0; it < 16; ++it) {
+      const uint32_t i = tid + it * 256;
+      const uint32_t c = i >> 6, r = i & 63u;
+      if (c0 + c < cols && r0 + r < rows) out[uint64_t(c0 + c) * rows + r0 + r] = tile[c][r];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ pre-passes
+// fp32 -> fp16 by truncation, the bit recipe of Float32ToFloatMP16
+// (gpu/matrix/mixed-precision.go:106-151): mantissa bits are dropped, not
+// rounded; fp32 subnormals and anything below 2^-25 flush to signed zero;
+// overflow gives infinity.
+__device__ __forceinline__ uint16_t f32_to_f16_trunc(float f) {
+  const uint32_t bits = __float_as_uint(f);
+  const uint32_t sign = (bits >> 31) & 1u;
+  const uint32_t exp = (bits >> 23) & 0xFFu;
+  uint32_t mant = bits & 0x7FFFFFu;
+  if (exp == 0) return uint16_t(sign << 15);
+  if (exp == 0xFF) {
+    return mant == 0 ? uint16_t((sign << 15) | 0x7C00u)
+                     : uint16_t((sign << 15) | 0x7C00u | (mant >> 13));
+  }
+  const int32_t e = int32_t(exp) - 127 + 15;
+  if (e >= 31) return uint16_t((sign << 15) | 0x7C00u);
+  if (e <= 0) {
+    if (e < -10) return uint16_t(sign << 15);
+    mant = (mant | 0x800000u) >> uint32_t(1 - e);
+    return uint16_t((sign << 15) | (mant >> 13));
+  }
+  return uint16_t((sign << 15) | (uint32_t(e) << 10) | (mant >> 13));
+}
+
+__device__ __forceinline__ uint16_t f32_to_f16(float f, int mode) {
+  return mode == F16_TRUNC ? f32_to_f16_trunc(f) : __half_as_ushort(__float2half_rn(f));
+}
+
+__global__ void __launch_bounds__(256) cvt_f16_kernel(const float* __restrict__ src, uint64_t rows,
+                                                      uint64_t cols, uint16_t* __restrict__ dst,
+                                                      uint64_t pitch, int mode, int vec) {
+  if (vec) {  // cols % 4 == 0 and both bases 16-byte aligned; pitch % 8 == 0 always
+    const uint64_t q = cols >> 2, total = rows * q;
+    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
+         i += uint64_t(gridDim.x) * blockDim.x) {
+      const uint64_t r = i / q, c = (i - r * q) << 2;
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * cols + c));
+      uint2 o;
+      o.x = uint32_t(f32_to_f16(v.x, mode)) | (uint32_t(f32_to_f16(v.y, mode)) << 16);
+      o.y = uint32_t(f32_to_f16(v.z, mode)) | (uint32_t(f32_to_f16(v.w, mode)) << 16);
+      *reinterpret_cast<uint2*>(dst + r * pitch + c) = o;
+    }
+  } else {
+    const uint64_t total = rows * cols;
+    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
+         i += uint64_t(gridDim.x) * blockDim.x) {
+      const uint64_t r = i / cols, c = i - r * cols;
+      dst[r * pitch + c] = f32_to_f16(src[i], mode);
+    }
+  }
+}
+
+__device__ __forceinline__ float rna_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ src,
+                                                         uint64_t rows, uint64_t cols,
+                                                         float* __restrict__ hi,
+                                                         float* __restrict__ lo, uint64_t pitch,
+                                                         int vec) {
+  if (vec) {
+    const uint64_t q = cols >> 2, total = rows * q;
+    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
+         i += uint64_t(gridDim.x) * blockDim.x) {
+      const uint64_t r = i / q, c = (i - r * q) << 2;
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * cols + c));
+      float4 h, l;
+      h.x = rna_tf32(v.x); l.x = rna_tf32(v.x - h.x);
+      h.y = rna_tf32(v.y); l.y = rna_tf32(v.y - h.y);
+      h.z = rna_tf32(v.z); l.z = rna_tf32(v.z - h.z);
+      h.w = rna_tf32(v.w); l.w = rna_tf32(v.w - h.w);
+      *reinterpret_cast<float4*>(hi + r * pitch + c) = h;
+      *reinterpret_cast<float4*>(lo + r * pitch + c) = l;
+    }
+  } else {
+    const uint64_t total = rows * cols;
+    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
+         i += uint64_t(gridDim.x) * blockDim.x) {
+      const uint64_t r = i / cols, c = i - r * cols;
+      const float x = src[i];
+      const float h = rna_tf32(x);
+      hi[r * pitch + c] = h;
+      lo[r * pitch + c] = rna_tf32(x - h);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ elementwise
+// Bias broadcast add, the four patterns of
+// internal/cgo/metal_bridge_matrix.m:273-312.
+__global__ void __launch_bounds__(256) add_broadcast_kernel(const float* __restrict__ a,
+                                                            const float* __restrict__ b,
+                                                            float* __restrict__ c, uint64_t rows,
+                                                            uint64_t cols, int mode) {
+  const uint64_t total = rows * cols;
+  for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
+       i += uint64_t(gridDim.x) * blockDim.x) {
+    const uint64_t r = i / cols, col = i - r * cols;
+    float v;
+    switch (mode) {
+      case 0: v = a[i] + b[col]; break;
+      case 1: v = a[col] + b[i]; break;
+      case 2: v = a[i] + b[r]; break;
+      default: v = a[r] + b[i]; break;
+    }
+    c[i] = v;
+  }
+}
+
+// ReLU forward / backward: internal/cgo/metal_bridge_activation.m:44-47, 74-77.
+__global__ void __launch_bounds__(256) relu_fwd_kernel(const float* __restrict__ in,
+                                                       float* __restrict__ out, uint64_t n) {
+  for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < n;
+       i += uint64_t(gridDim.x) * blockDim.x)
+    out[i] = fmaxf(0.0f, in[i]);
+}
+__global__ void __launch_bounds__(256) relu_bwd_kernel(const float* __restrict__ go,
+                                                       const float* __restrict__ act,
+                                                       float* __restrict__ gi, uint64_t n) {
+  for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < n;
+       i += uint64_t(gridDim.x) * blockDim.x)
+    gi[i] = (act[i] > 0.0f) ? go[i] : 0.0f;
+}
+
+// Column sum (bias gradient, gpu/matrix/layers.go:281-294): rows are added in
+// index order per partial, partials in order, so the result is deterministic.
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ in, uint64_t rows,
+                                                     uint64_t cols, float* __restrict__ out) {
+  __shared__ float part[8][33];
+  const uint32_t cx = threadIdx.x & 31u, ry = threadIdx.x >> 5;
+  const uint64_t col = blockIdx.x * 32ull + cx;
+  float s = 0.f;
+  if (col < cols)
+    for (uint64_t r = ry; r < rows; r += 8) s += in[r * cols + col];
+  part[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && col < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += part[k][cx];
+    out[col] = t;
+  }
+}
+
+inline uint32_t stream_grid(uint64_t work_items, uint32_t threads, uint32_t cap) {
+  uint64_t g = (work_items + threads - 1) / threads;
+  if (g < 1) g = 1;
+  return uint32_t(g < cap ? g : cap);
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+void launch_transpose(const float* in, uint64_t rows, uint64_t cols, float* out, int /*sm_count*/,
+                      cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return;
+  const uint32_t tiles_r = uint32_t((rows + TT - 1) / TT), tiles_c = uint32_t((cols + TT - 1) / TT);
+  const uint32_t grid = tiles_r * tiles_c;
+  const bool vin = (cols % 4 == 0) && aligned16(in);
+  const bool vout = (rows % 4 == 0) && aligned16(out);
+  if (vin && vout)
+    transpose_kernel<true, true><<<grid, 256, 0, stream>>>(in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+  else if (vin)
+    transpose_kernel<true, false><<<grid, 256, 0, stream>>>(in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+  else if (vout)
+    transpose_kernel<false, true><<<grid, 256, 0, stream>>>(in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+  else
+    transpose_kernel<false, false><<<grid, 256, 0, stream>>>(in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+}
+
+void launch_cvt_f16(const float* src, uint64_t rows, uint64_t cols, void* dst, uint64_t pitch,
+                    int mode, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return;
+  const int vec = (cols % 4 == 0) && aligned16(src) && aligned16(dst) && (pitch % 4 == 0);
+  const uint64_t items = vec ? rows * (cols / 4) : rows * cols;
+  cvt_f16_kernel<<<stream_grid(items, 256, 148 * 16), 256, 0, stream>>>(
+      src, rows, cols, static_cast<uint16_t*>(dst), pitch, mode, vec);
+}
+
+void launch_split_tf32(const float* src, uint64_t rows, uint64_t cols, float* hi, float* lo,
+                       uint64_t pitch, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return;
+  const int vec = (cols % 4 == 0) && aligned16(src) && aligned16(hi) && aligned16(lo) && (pitch % 4 == 0);
+  const uint64_t items = vec ? rows * (cols / 4) : rows * cols;
+  split_tf32_kernel<<<stream_grid(items, 256, 148 * 16), 256, 0, stream>>>(src, rows, cols, hi, lo,
+                                                                           pitch, vec);
+}
+
+void launch_add_broadcast(const float* a, const float* b, float* c, uint64_t rows, uint64_t cols,
+                          int mode, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return;
+  add_broadcast_kernel<<<stream_grid(rows * cols, 256, 148 * 16), 256, 0, stream>>>(a, b, c, rows,
+                                                                                    cols, mode);
+}
+
+void launch_relu_forward(const float* in, float* out, uint64_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  relu_fwd_kernel<<<stream_grid(n, 256, 148 * 16), 256, 0, stream>>>(in, out, n);
+}
+
+void launch_relu_backward(const float* grad_out, const float* act_out, float* grad_in, uint64_t n,
+                          cudaStream_t stream) {
+  if (n == 0) return;
+  relu_bwd_kernel<<<stream_grid(n, 256, 148 * 16), 256, 0, stream>>>(grad_out, act_out, grad_in, n);
+}
+
+void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream) {
+  if (cols == 0) return;
+  colsum_kernel<<<uint32_t((cols + 31) / 32), 256, 0, stream>>>(in, rows, cols, out);
+}
+
+}  // namespace gonn

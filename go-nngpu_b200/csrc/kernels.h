@@ -1,0 +1,84 @@
+// Internal C++ interface between the C-ABI bridge and the sm_100a kernels.
+// Nothing here is exported from the shared library.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace gonn {
+
+// ---- dense GEMM on the 5th-generation tensor cores -------------------------
+enum class Kind : int {
+  F16 = 0,     // fp16 operands, fp32 accumulate in TMEM
+  TF32x3 = 1,  // fp32 operands split hi+lo into two tf32 planes, 3 MMAs per k step
+};
+
+// Activation codes of the fused epilogue.  They are the codes the reference's
+// fused_linear_activation kernel decodes (internal/cgo/default.metal:488-506);
+// every other value means identity, as in its `default:` branch.
+enum Act : int { ACT_RELU = 0, ACT_LEAKY = 1, ACT_SIGMOID = 2, ACT_TANH = 3, ACT_GELU = 4,
+                 ACT_NONE = -1 };
+
+// One GEMM operand as it lies in HBM.  `mn_major == false`: rows are the M (or
+// N) index and K is contiguous ("K-major").  `mn_major == true`: rows are the K
+// index and M (or N) is contiguous.  `pitch` is in elements and must make the
+// row pitch a multiple of 16 bytes; `plane1` is the low tf32 plane (TF32x3 only).
+struct GemmOperand {
+  const void* plane0 = nullptr;
+  const void* plane1 = nullptr;
+  uint64_t pitch = 0;
+  bool mn_major = false;
+};
+
+// C = act(alpha * A.B + beta * C_in + bias[n])
+struct GemmEpilogue {
+  float alpha = 1.f;
+  float beta = 0.f;          // when non-zero, c_in is read with the same pitch as C
+  const float* c_in = nullptr;
+  const float* bias = nullptr;  // length N or null
+  int act = ACT_NONE;
+  float act_param = 0.f;
+};
+
+// Status words a kernel writes when a bounded wait ran out (all zero = fine).
+struct GemmStatus {
+  uint32_t code;   // 0 ok, 1 producer, 2 mma issuer, 3 epilogue gave up
+  uint32_t where;  // stage / accumulator index
+  uint32_t tile;
+  uint32_t kblock;
+};
+
+struct GemmTuning {
+  int block_n = 0;   // 0 = choose; else 32/64/128/256
+  int max_ctas = 0;  // 0 = one per SM
+};
+
+// Enqueues the GEMM on `stream`.  Returns nullptr on success, else a static
+// message.  `status` is device memory holding one GemmStatus, zeroed by the
+// caller before the launch.
+const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const GemmOperand& A,
+                        const GemmOperand& B, float* C, uint64_t ldc, const GemmEpilogue& epi,
+                        GemmStatus* status, int sm_count, const GemmTuning& tune,
+                        cudaStream_t stream);
+
+// ---- pre-pass: operand planes ---------------------------------------------
+enum F16Mode : int { F16_RN = 0, F16_TRUNC = 1 };
+// fp32 [rows, cols] (pitch cols) -> fp16 plane with `pitch` elements per row.
+void launch_cvt_f16(const float* src, uint64_t rows, uint64_t cols, void* dst, uint64_t pitch,
+                    int mode, cudaStream_t stream);
+// fp32 -> (hi, lo) tf32 planes: hi = rna_tf32(x), lo = rna_tf32(x - hi).
+void launch_split_tf32(const float* src, uint64_t rows, uint64_t cols, float* hi, float* lo,
+                       uint64_t pitch, cudaStream_t stream);
+
+// ---- HBM-bound kernels -----------------------------------------------------
+void launch_transpose(const float* in, uint64_t rows, uint64_t cols, float* out, int sm_count,
+                      cudaStream_t stream);
+// mode 0: c[i,j] = a[i,j] + b[j]; 1: c = a[j] + b[i,j]; 2: c = a[i,j] + b[i]; 3: c = a[i] + b[i,j]
+void launch_add_broadcast(const float* a, const float* b, float* c, uint64_t rows, uint64_t cols,
+                          int mode, cudaStream_t stream);
+void launch_relu_forward(const float* in, float* out, uint64_t n, cudaStream_t stream);
+void launch_relu_backward(const float* grad_out, const float* act_out, float* grad_in, uint64_t n,
+                          cudaStream_t stream);
+// out[j] = sum_i in[i, j]   (bias gradient)
+void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream);
+
+}  // namespace gonn

@@ -1,0 +1,251 @@
+"""ctypes binding of libgonngpu_cuda.so, used by the tests and by bench.py.
+
+It is deliberately thin: every function below is one call through the C ABI
+declared in include/gonngpu.h, with numpy arrays as the host buffers.  There is
+no fallback: if the library is missing, or no B200 is visible, calls fail.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libgonngpu_cuda.so")
+
+FP32_3XTF32, FP16_RN, FP16_TRUNC = 0, 1, 2
+ACT_NONE, ACT_RELU, ACT_LEAKY, ACT_SIGMOID, ACT_TANH, ACT_GELU = -1, 0, 1, 2, 3, 4
+
+
+class CError(ctypes.Structure):
+    _fields_ = [("message", ctypes.c_void_p)]
+
+
+class GonnError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+_lib = None
+
+_c_long, _c_int, _c_float, _vp = ctypes.c_long, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+_errp = ctypes.POINTER(CError)
+
+# name -> (restype, argtypes); the list mirrors include/gonngpu.h one to one.
+SIGNATURES = {
+    "create_gpu_buffer": (_c_int, [_vp, _c_long, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _errp]),
+    "retrieve_gpu_buffer_data": (_c_int, [_vp, _vp, _c_long, _errp]),
+    "release_gpu_buffer": (_c_int, [_vp]),
+    "free_c_error_message": (None, [_vp]),
+    "perform_mps_matrix_multiplication": (
+        _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _errp]),
+    "perform_mps_matrix_transpose": (_c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _errp]),
+    "perform_mps_matrix_add_broadcast": (
+        _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _errp]),
+    "perform_activation_relu_forward": (_c_int, [_vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_relu_backward": (_c_int, [_vp, _vp, _c_long, _vp, _vp, _errp]),
+    "perform_fused_linear_activation": (
+        _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _vp, _c_int, _c_float, _vp, _vp, _errp]),
+    "perform_optimized_gemm": (
+        _c_int, [_vp, _vp, _vp, _c_long, _c_long, _c_long, _c_float, _c_float, _vp, _errp]),
+    "allocateSharedMemory": (_vp, [_c_long]),
+    "createGPUBufferFromSharedMemory": (_vp, [_vp, _vp, _c_long]),
+    "gonngpu_matmul_ex": (
+        _c_int, [_vp, _c_long, _c_long, _c_int, _vp, _c_long, _c_long, _c_int, _vp, _c_long, _c_long,
+                 _c_int, _c_float, _c_float, _vp, _c_int, _c_float, _errp]),
+    "gonngpu_column_sum": (_c_int, [_vp, _c_long, _c_long, _vp, _errp]),
+    "gonngpu_alloc_device_buffer": (_c_int, [_c_long, ctypes.POINTER(_vp), _errp]),
+    "gonngpu_wrap_device_memory": (_c_int, [_vp, _c_long, ctypes.POINTER(_vp), _errp]),
+    "gonngpu_device_address": (_vp, [_vp]),
+    "gonngpu_upload": (_c_int, [_vp, _vp, _c_long, _errp]),
+    "gonngpu_mark_modified": (_c_int, [_vp]),
+    "gonngpu_host_alloc": (_vp, [_c_long]),
+    "gonngpu_host_free": (None, [_vp]),
+    "gonngpu_device_count": (_c_int, []),
+    "gonngpu_set_device": (_c_int, [_c_int]),
+    "gonngpu_get_device": (_c_int, []),
+    "gonngpu_stream": (_vp, []),
+    "gonngpu_set_blocking": (_c_int, [_c_int]),
+    "gonngpu_synchronize": (_c_int, [_errp]),
+    "gonngpu_set_plane_cache": (_c_int, [_c_int]),
+    "gonngpu_set_gemm_tuning": (_c_int, [_c_int, _c_int]),
+    "gonngpu_get_stats": (None, [ctypes.POINTER(_c_long)]),
+    "gonngpu_last_kernel_status": (None, [ctypes.POINTER(ctypes.c_uint)]),
+    "gonngpu_version": (ctypes.c_char_p, []),
+}
+
+
+def lib():
+    """Loads the shared library once and types every exported function."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise OSError(f"{LIB_PATH} is not built; run python go-nngpu_b200/build.py")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def _check(code, err):
+    if code != 0:
+        msg = ""
+        if err.message:
+            msg = ctypes.string_at(err.message).decode("utf-8", "replace")
+            lib().free_c_error_message(err.message)
+        raise GonnError(code, msg)
+
+
+def _np_ptr(a):
+    return a.ctypes.data_as(_vp)
+
+
+class Buffer:
+    """A GPUPtr handle.  `host` keeps the registered numpy array alive."""
+
+    def __init__(self, handle, nbytes, host=None):
+        self.handle = handle
+        self.nbytes = nbytes
+        self.host = host
+
+    @classmethod
+    def from_host(cls, array):
+        """create_gpu_buffer over a C-contiguous float32 array (lazy upload)."""
+        a = np.ascontiguousarray(array, dtype=np.float32)
+        h, dev, err = _vp(), _vp(), CError()
+        _check(lib().create_gpu_buffer(_np_ptr(a), a.nbytes, ctypes.byref(h), ctypes.byref(dev),
+                                       ctypes.byref(err)), err)
+        return cls(h, a.nbytes, a)
+
+    @classmethod
+    def empty(cls, nbytes):
+        h, err = _vp(), CError()
+        _check(lib().gonngpu_alloc_device_buffer(int(nbytes), ctypes.byref(h), ctypes.byref(err)), err)
+        return cls(h, int(nbytes))
+
+    @classmethod
+    def wrap(cls, device_ptr, nbytes, keepalive=None):
+        h, err = _vp(), CError()
+        _check(lib().gonngpu_wrap_device_memory(_vp(device_ptr), int(nbytes), ctypes.byref(h),
+                                                ctypes.byref(err)), err)
+        return cls(h, int(nbytes), keepalive)
+
+    def upload(self, array):
+        a = np.ascontiguousarray(array, dtype=np.float32)
+        err = CError()
+        _check(lib().gonngpu_upload(self.handle, _np_ptr(a), a.nbytes, ctypes.byref(err)), err)
+
+    def retrieve(self, shape):
+        out = np.empty(shape, dtype=np.float32)
+        self.retrieve_into(out)
+        return out
+
+    def retrieve_into(self, out):
+        err = CError()
+        _check(lib().retrieve_gpu_buffer_data(self.handle, _np_ptr(out), out.nbytes, ctypes.byref(err)), err)
+
+    def device_address(self):
+        return lib().gonngpu_device_address(self.handle)
+
+    def release(self):
+        if self.handle:
+            lib().release_gpu_buffer(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+def matmul(a, a_shape, b, b_shape, c, c_shape):
+    err = CError()
+    _check(lib().perform_mps_matrix_multiplication(
+        a.handle, a_shape[0], a_shape[1], b.handle, b_shape[0], b_shape[1], c.handle, c_shape[0],
+        c_shape[1], None, ctypes.byref(err)), err)
+
+
+def matmul_ex(a, a_shape, trans_a, b, b_shape, trans_b, c, c_shape, precision=FP32_3XTF32,
+              alpha=1.0, beta=0.0, bias=None, act=ACT_NONE, act_param=0.0):
+    err = CError()
+    _check(lib().gonngpu_matmul_ex(
+        a.handle, a_shape[0], a_shape[1], int(trans_a), b.handle, b_shape[0], b_shape[1],
+        int(trans_b), c.handle, c_shape[0], c_shape[1], precision, alpha, beta,
+        bias.handle if bias is not None else None, act, act_param, ctypes.byref(err)), err)
+
+
+def transpose(inp, in_shape, out):
+    err = CError()
+    _check(lib().perform_mps_matrix_transpose(inp.handle, in_shape[0], in_shape[1], out.handle,
+                                              in_shape[1], in_shape[0], None, ctypes.byref(err)), err)
+
+
+def add_broadcast(a, a_shape, b, b_shape, c, c_shape):
+    err = CError()
+    _check(lib().perform_mps_matrix_add_broadcast(
+        a.handle, a_shape[0], a_shape[1], b.handle, b_shape[0], b_shape[1], c.handle, c_shape[0],
+        c_shape[1], None, ctypes.byref(err)), err)
+
+
+def relu_forward(inp, size, out):
+    err = CError()
+    _check(lib().perform_activation_relu_forward(inp.handle, size, out.handle, None, ctypes.byref(err)), err)
+
+
+def relu_backward(grad_out, act_out, size, grad_in):
+    err = CError()
+    _check(lib().perform_activation_relu_backward(grad_out.handle, act_out.handle, size,
+                                                  grad_in.handle, None, ctypes.byref(err)), err)
+
+
+def fused_linear_activation(x, batch, in_size, w, out_size, bias, act, alpha, y):
+    err = CError()
+    _check(lib().perform_fused_linear_activation(
+        x.handle, batch, in_size, w.handle, out_size, bias.handle if bias is not None else None,
+        act, alpha, y.handle, None, ctypes.byref(err)), err)
+
+
+def optimized_gemm(a, b, c, m, n, k, alpha, beta):
+    err = CError()
+    _check(lib().perform_optimized_gemm(a.handle, b.handle, c.handle, m, n, k, alpha, beta, None,
+                                        ctypes.byref(err)), err)
+
+
+def column_sum(inp, rows, cols, out):
+    err = CError()
+    _check(lib().gonngpu_column_sum(inp.handle, rows, cols, out.handle, ctypes.byref(err)), err)
+
+
+def synchronize():
+    err = CError()
+    _check(lib().gonngpu_synchronize(ctypes.byref(err)), err)
+
+
+def stats():
+    out = (_c_long * 8)()
+    lib().gonngpu_get_stats(out)
+    keys = ["hbm_bytes", "h2d_bytes", "d2h_bytes", "kernel_launches", "gemm_launches", "buffers",
+            "plane_bytes", "reserved"]
+    return dict(zip(keys, list(out)))
+
+
+def last_kernel_status():
+    out = (ctypes.c_uint * 4)()
+    lib().gonngpu_last_kernel_status(out)
+    return list(out)
+
+
+def pinned_array(shape, dtype=np.float32):
+    """numpy array over page-locked memory from gonngpu_host_alloc."""
+    n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+    p = lib().gonngpu_host_alloc(max(n, 1))
+    if not p:
+        raise MemoryError("gonngpu_host_alloc failed")
+    buf = (ctypes.c_char * max(n, 1)).from_address(p)
+    arr = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+    return arr, p

@@ -1,0 +1,197 @@
+/* C ABI of libgonngpu_cuda.so: the dense-GEMM hot path of tsawler/go-nngpu on
+ * NVIDIA B200 (sm_100a).
+ *
+ * Part 1 re-declares, with unchanged names, argument order and error
+ * convention, the entry points of the reference's cgo bridge
+ * (internal/cgo/metal_bridge.h) that its MatMul / Transpose / fused
+ * linear+activation path binds; each declaration cites the reference line it
+ * replaces.  A Go build of the reference links this library in place of the
+ * Objective-C/Metal objects without touching its Go callers.
+ *
+ * Part 2 is additive: entry points (prefix gonngpu_) the reference has no
+ * counterpart for - transposed operands, the fp16 path, device selection,
+ * pinned staging, statistics.
+ *
+ * Conventions (same as the reference bridge):
+ *   - every function returns 0 on success and a small negative int naming the
+ *     failing step otherwise; on failure, when `err` is non-NULL,
+ *     err->message is a malloc'ed C string the CALLER frees with
+ *     free_c_error_message(); on success err is not touched;
+ *   - dimensions are `long`; buffer sizes are in bytes; activation sizes are in
+ *     elements; all matrix data is row-major float32;
+ *   - every call is blocking: when it returns, the result is complete on the
+ *     device (gonngpu_set_blocking(0) lifts that for pipelined callers);
+ *   - a NULL DevicePtr means "the calling thread's current device".
+ *
+ * There is no CPU fallback: without a usable CUDA device every compute entry
+ * point fails with -1.
+ */
+#ifndef GONNGPU_H_
+#define GONNGPU_H_
+
+#include <stdbool.h>
+#include <stddef.h>
+
+#if defined(__GNUC__)
+#define GONNGPU_API __attribute__((visibility("default")))
+#else
+#define GONNGPU_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- Part 1: the reference bridge's hot-path subset ---------------------- */
+
+typedef void *GPUPtr;          /* metal_bridge.h:9  - opaque buffer handle   */
+typedef void *DevicePtr;       /* metal_bridge.h:10 - opaque device handle   */
+typedef void *CommandQueuePtr; /* metal_bridge.h:11 - unused, kept for cgo   */
+
+typedef struct {
+  char *message;
+} CError; /* metal_bridge.h:14-16 */
+
+/* metal_bridge.h:23.  Registers `length_bytes` of caller memory at `data` as a
+ * buffer.  The reference aliases that memory (zero copy); here the buffer owns
+ * HBM of the same size and remembers `data`: the bytes are copied to the
+ * device when the buffer is first used as an input (never, if it is only ever
+ * written), so `data` must stay valid until then, as the reference requires
+ * for the buffer's whole life.  Errors: -1 no device, -2 stream set-up,
+ * -3 allocation. */
+GONNGPU_API int create_gpu_buffer(float *data, long length_bytes, GPUPtr *outGPUPtr, DevicePtr *outDevicePtr,
+                      CError *err);
+
+/* metal_bridge.h:24.  Copies the buffer's current contents to `data`.
+ * Errors: -1 bad handle, -2 length_bytes larger than the buffer, -3 copy. */
+GONNGPU_API int retrieve_gpu_buffer_data(GPUPtr gpuPtr, float *data, long length_bytes, CError *err);
+
+/* metal_bridge.h:25.  Frees the buffer; NULL is a no-op returning 0. */
+GONNGPU_API int release_gpu_buffer(GPUPtr gpuPtr);
+
+/* metal_bridge.h:250. */
+GONNGPU_API void free_c_error_message(char *message);
+
+/* metal_bridge.h:28-34.  C[M,N] = A[M,K] . B[K,N], fp32 in and out, computed
+ * on the tensor cores as three tf32 products of hi/lo splits (fp32-level
+ * accuracy).  Errors: -1 device, -2 bad buffer, -3 dimension/size mismatch,
+ * -4 kernel set-up, -5 scratch allocation, -6 execution. */
+GONNGPU_API int perform_mps_matrix_multiplication(GPUPtr aMatrixPtr, long aRows, long aCols, GPUPtr bMatrixPtr,
+                                      long bRows, long bCols, GPUPtr resultMatrixPtr,
+                                      long resultRows, long resultCols, DevicePtr mtlDevicePtr,
+                                      CError *err);
+
+/* metal_bridge.h:36-41.  out[j,i] = in[i,j], bit-exact.  Errors: -1 device,
+ * -2 dimensions, -3 bad buffer, -6 execution. */
+GONNGPU_API int perform_mps_matrix_transpose(GPUPtr inputMatrixPtr, long inputRows, long inputCols,
+                                 GPUPtr outputMatrixPtr, long outputRows, long outputCols,
+                                 DevicePtr mtlDevicePtr, CError *err);
+
+/* metal_bridge.h:52-58.  The four bias-broadcast patterns [M,N]+[1,N],
+ * [1,N]+[M,N], [M,N]+[M,1], [M,1]+[M,N].  Errors: -3 bad buffer, -2 any other
+ * shape combination, -6 execution. */
+GONNGPU_API int perform_mps_matrix_add_broadcast(GPUPtr aMatrixPtr, long aRows, long aCols, GPUPtr bMatrixPtr,
+                                     long bRows, long bCols, GPUPtr resultMatrixPtr,
+                                     long resultRows, long resultCols, DevicePtr mtlDevicePtr,
+                                     CError *err);
+
+/* metal_bridge.h:259-264.  out[i] = max(0, in[i]).  Errors: -1 bad buffer. */
+GONNGPU_API int perform_activation_relu_forward(GPUPtr inputPtr, long size, GPUPtr outputPtr,
+                                    DevicePtr mtlDevicePtr, CError *err);
+
+/* metal_bridge.h:266-271.  gradIn[i] = actOut[i] > 0 ? gradOut[i] : 0. */
+GONNGPU_API int perform_activation_relu_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr, long size,
+                                     GPUPtr gradInputPtr, DevicePtr mtlDevicePtr, CError *err);
+
+/* metal_bridge.h:1348-1353.  output[b,o] = act(sum_i input[b,i]*weight[i,o] +
+ * bias[o]); `bias` may be NULL.  activation_type is decoded as the reference's
+ * kernel decodes it (default.metal:488-506): 0 ReLU, 1 LeakyReLU(alpha),
+ * 2 Sigmoid, 3 Tanh, 4 tanh-GELU, anything else identity.  Bias and activation
+ * run in the GEMM epilogue.  Errors: -1 device or bad buffer, -3 sizes,
+ * -4/-5/-6 as for the multiplication. */
+GONNGPU_API int perform_fused_linear_activation(GPUPtr input, long batch_size, long input_size, GPUPtr weight,
+                                    long output_size, GPUPtr bias, int activation_type, float alpha,
+                                    GPUPtr output, DevicePtr device, CError *error);
+
+/* metal_bridge.h:1423-1429.  C = alpha * A[M,K].B[K,N] + beta * C.
+ * Errors: -1 device, -2 bad buffer, -3 sizes/kernel set-up, -6 execution. */
+GONNGPU_API int perform_optimized_gemm(GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long M, long N, long K,
+                           float alpha, float beta, DevicePtr mtlDevicePtr, CError *err);
+
+/* metal_bridge.h:1803.  Host memory for the reference's unified-memory
+ * adapter: page-locked, zero-filled, 16 KiB aligned; NULL on failure.  Freed by
+ * gonngpu_host_free(). */
+GONNGPU_API void *allocateSharedMemory(long size);
+
+/* metal_bridge.h:1804.  A buffer handle over memory from allocateSharedMemory
+ * (same lazy-upload rule as create_gpu_buffer); NULL on failure. */
+GONNGPU_API void *createGPUBufferFromSharedMemory(void *device, void *memory, long size);
+
+/* ---- Part 2: additive entry points (no counterpart in the reference) ----- */
+
+/* Precision of gonngpu_matmul_ex. */
+#define GONNGPU_FP32_3XTF32 0 /* fp32 accuracy: three tf32 MMAs on hi/lo splits     */
+#define GONNGPU_FP16_RN 1     /* inputs rounded to fp16 (nearest even), fp32 accum. */
+#define GONNGPU_FP16_TRUNC 2  /* inputs truncated to fp16 exactly as the reference's \
+                                 Float32ToFloatMP16 (mixed-precision.go:106-151)    */
+#define GONNGPU_ACT_NONE (-1)
+
+/* C[M,N] = act(alpha * op(A).op(B) + beta * C + bias[N]) with op(X) = X or its
+ * transpose (transX != 0; no transposed copy is made), any precision above.
+ * `bias` may be NULL.  Replaces the Transpose+MatMul pairs of the reference's
+ * backward passes (gpu/matrix/layers.go:77-96) and its ForwardFloat16
+ * (gpu/matrix/mixed-precision.go:315-358).  Errors as
+ * perform_mps_matrix_multiplication. */
+GONNGPU_API int gonngpu_matmul_ex(GPUPtr a, long aRows, long aCols, int transA, GPUPtr b, long bRows,
+                      long bCols, int transB, GPUPtr c, long cRows, long cCols, int precision,
+                      float alpha, float beta, GPUPtr bias, int activation_type,
+                      float activation_param, CError *err);
+
+/* out[j] = sum_i in[i,j] (bias gradient, gpu/matrix/layers.go:281-294). */
+GONNGPU_API int gonngpu_column_sum(GPUPtr in, long rows, long cols, GPUPtr out, CError *err);
+
+/* Device-only buffer of `length_bytes` (contents undefined). */
+GONNGPU_API int gonngpu_alloc_device_buffer(long length_bytes, GPUPtr *out, CError *err);
+/* Handle over device memory the caller owns (for example a torch tensor). */
+GONNGPU_API int gonngpu_wrap_device_memory(void *device_ptr, long length_bytes, GPUPtr *out, CError *err);
+/* Device address behind a handle (after any pending upload), or NULL. */
+GONNGPU_API void *gonngpu_device_address(GPUPtr buffer);
+/* Copies `length_bytes` from host `data` into the buffer now. */
+GONNGPU_API int gonngpu_upload(GPUPtr buffer, const float *data, long length_bytes, CError *err);
+/* Tells the library the caller changed the device contents behind a wrapped
+ * handle, so cached operand planes are rebuilt. */
+GONNGPU_API int gonngpu_mark_modified(GPUPtr buffer);
+
+/* Page-locked host memory (fast, asynchronous copies). */
+GONNGPU_API void *gonngpu_host_alloc(long bytes);
+GONNGPU_API void gonngpu_host_free(void *p);
+
+GONNGPU_API int gonngpu_device_count(void);
+GONNGPU_API int gonngpu_set_device(int ordinal); /* device used by later calls of this process */
+GONNGPU_API int gonngpu_get_device(void);
+/* cudaStream_t every kernel and copy of the current device is enqueued on. */
+GONNGPU_API void *gonngpu_stream(void);
+/* 1 (default): every entry point waits for its work.  0: work is only enqueued;
+ * call gonngpu_synchronize() before reading results. */
+GONNGPU_API int gonngpu_set_blocking(int blocking);
+GONNGPU_API int gonngpu_synchronize(CError *err);
+/* Keeps (1, default) or drops (0) the converted operand planes of a buffer
+ * between calls while its contents are unchanged. */
+GONNGPU_API int gonngpu_set_plane_cache(int enabled);
+/* GEMM tile override for experiments: block_n in {0 = auto, 32, 64, 128, 256},
+ * max_ctas 0 = one per SM. */
+GONNGPU_API int gonngpu_set_gemm_tuning(int block_n, int max_ctas);
+
+/* out[0] bytes of HBM held, [1] host->device bytes, [2] device->host bytes,
+ * [3] kernels launched, [4] GEMM kernels launched, [5] buffers alive,
+ * [6] scratch (operand plane) bytes held, [7] reserved. */
+GONNGPU_API void gonngpu_get_stats(long out[8]);
+/* Status words of the last GEMM kernel on the current device: code (0 fine,
+ * 1 producer / 2 MMA issuer / 3 epilogue wait ran out), where, tile, k block. */
+GONNGPU_API void gonngpu_last_kernel_status(unsigned out[4]);
+GONNGPU_API const char *gonngpu_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GONNGPU_H_ */
