@@ -402,7 +402,7 @@ EncodeTiledFn encode_tiled() {
 // 2-D map over a row-major plane: `inner` contiguous elements per row, `outer`
 // rows, boxes of (128 bytes, box_rows) written with the 128-byte swizzle.
 bool make_map(CUtensorMap* map, bool f32, const void* base, uint64_t inner, uint64_t outer,
-              uint64_t pitch_elems, uint32_t box_rows) {
+              uint64_t pitch_elems, uint32_t box_rows, bool mn_major) {
   EncodeTiledFn fn = encode_tiled();
   if (!fn) return false;
   const uint32_t esz = f32 ? 4 : 2;
@@ -412,7 +412,10 @@ bool make_map(CUtensorMap* map, bool f32, const void* base, uint64_t inner, uint
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  // MN-major tf32 tiles must use the 32-byte-chunk flavour of the swizzle.
+                  (f32 && mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                    : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -433,7 +436,7 @@ OperandPlan plan_operand(bool f32, bool mn_major, uint32_t tile_mn, uint32_t blo
     o.c1_tile = int32_t(tile_mn);
     o.c1_k = 0;
     o.kstep_bytes = umma_k * esz;  // 32 bytes inside the swizzled row
-    o.desc = ptx::smem_desc_sw128(16, 1024);
+    o.desc = ptx::smem_desc(2, 16, 1024);
   } else {
     // rows = K index, 128 bytes of MN per row: one box per 128 bytes of MN.
     o.slabs = tile_mn / row_elems;
@@ -444,7 +447,9 @@ OperandPlan plan_operand(bool f32, bool mn_major, uint32_t tile_mn, uint32_t blo
     o.c1_tile = 0;
     o.c1_k = int32_t(block_k);
     o.kstep_bytes = umma_k * SLAB_ROW_BYTES;  // umma_k rows down
-    o.desc = ptx::smem_desc_sw128(o.slab_bytes, 1024);
+    // fp16: groups of 8 k rows are 1024 B apart (16-byte-chunk swizzle).  tf32:
+    // the 32-byte-chunk swizzle repeats every 4 k rows, 512 B apart.
+    o.desc = f32 ? ptx::smem_desc(1, o.slab_bytes, 512) : ptx::smem_desc(2, o.slab_bytes, 1024);
   }
   return o;
 }
@@ -562,12 +567,12 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
   const uint32_t b_box_rows = B.mn_major ? block_k : uint32_t(bn);
   const uint64_t a_inner = A.mn_major ? M : K, a_outer = A.mn_major ? K : M;
   const uint64_t b_inner = B.mn_major ? N : K, b_outer = B.mn_major ? K : N;
-  if (!make_map(&maps[0], f32, A.plane0, a_inner, a_outer, A.pitch, a_box_rows) ||
-      !make_map(&maps[2], f32, B.plane0, b_inner, b_outer, B.pitch, b_box_rows))
+  if (!make_map(&maps[0], f32, A.plane0, a_inner, a_outer, A.pitch, a_box_rows, A.mn_major) ||
+      !make_map(&maps[2], f32, B.plane0, b_inner, b_outer, B.pitch, b_box_rows, B.mn_major))
     return "cuTensorMapEncodeTiled failed";
   if (f32) {
-    if (!make_map(&maps[1], f32, A.plane1, a_inner, a_outer, A.pitch, a_box_rows) ||
-        !make_map(&maps[3], f32, B.plane1, b_inner, b_outer, B.pitch, b_box_rows))
+    if (!make_map(&maps[1], f32, A.plane1, a_inner, a_outer, A.pitch, a_box_rows, A.mn_major) ||
+        !make_map(&maps[3], f32, B.plane1, b_inner, b_outer, B.pitch, b_box_rows, B.mn_major))
       return "cuTensorMapEncodeTiled failed";
   } else {
     maps[1] = maps[0];

@@ -182,10 +182,13 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // ------------------------------------------------- descriptors (host+device)
 // Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle:
 //   [0,14) start address >> 4, [16,30) leading byte offset >> 4,
-//   [32,46) stride byte offset >> 4, [46,48) version = 1, [61,64) layout = 2.
-__host__ __device__ constexpr uint64_t smem_desc_sw128(uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   [32,46) stride byte offset >> 4, [46,48) version = 1, [61,64) layout.
+// `layout`: 2 = 128-byte swizzle of 16-byte chunks; 1 = 128-byte swizzle of
+// 32-byte chunks, the only layout tf32 operands may use when MN-major.
+__host__ __device__ constexpr uint64_t smem_desc(uint32_t layout, uint32_t lbo_bytes,
+                                                 uint32_t sbo_bytes) {
   return (uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16) | (uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32) |
-         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+         (uint64_t(1) << 46) | (uint64_t(layout) << 61);
 }
 __device__ __forceinline__ uint64_t smem_desc_at(uint64_t templ, uint32_t smem_addr) {
   return templ | uint64_t((smem_addr >> 4) & 0x3FFF);

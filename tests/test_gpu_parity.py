@@ -1,0 +1,342 @@
+"""Parity of the CUDA path against the CPU oracle, through the C ABI.
+
+Tolerances (stated by the benchmark contract): fp32 path relative Frobenius
+error <= 1e-5 against the float64 reference; fp16 path <= 1e-2; Transpose and
+the other element-moving / exact-integer cases bit-exact.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5
+FP16_TOL = 1e-2
+
+
+def run_matmul(g, A, B, trans_a=False, trans_b=False, precision=0, alpha=1.0, beta=0.0, C0=None,
+               bias=None, act=-1, act_param=0.0, entry="ex"):
+    """A and B are given as STORED; returns the float32 result."""
+    M = A.shape[1] if trans_a else A.shape[0]
+    N = B.shape[0] if trans_b else B.shape[1]
+    a, b = g.Buffer.from_host(A), g.Buffer.from_host(B)
+    c = g.Buffer.from_host(C0 if C0 is not None else np.full((M, N), np.float32(-123.0), np.float32))
+    bb = g.Buffer.from_host(bias) if bias is not None else None
+    try:
+        if entry == "mps":
+            g.matmul(a, A.shape, b, B.shape, c, (M, N))
+        else:
+            g.matmul_ex(a, A.shape, trans_a, b, B.shape, trans_b, c, (M, N), precision=precision,
+                        alpha=alpha, beta=beta, bias=bb, act=act, act_param=act_param)
+        return c.retrieve((M, N))
+    finally:
+        for x in (a, b, c, bb):
+            if x is not None:
+                x.release()
+
+
+# ------------------------------------------------------------------ known answers
+def test_golden_integer_and_permutation_gemms_are_exact(gpu, golden):
+    _, k = golden
+    for name in ("int_a", "int_b", "int_c"):
+        for prec in (gpu.FP32_3XTF32, gpu.FP16_RN, gpu.FP16_TRUNC):
+            C = run_matmul(gpu, k[f"{name}_A"], k[f"{name}_B"], precision=prec)
+            assert np.array_equal(C, k[f"{name}_C"]), (name, prec)
+    C = run_matmul(gpu, k["perm_P"], k["perm_V"], entry="mps")
+    assert np.array_equal(C, k["perm_C"])
+    # the same products with transposed storage (no materialised transpose inside)
+    A, B = k["int_b_A"], k["int_b_B"]
+    for ta in (False, True):
+        for tb in (False, True):
+            for prec in (gpu.FP32_3XTF32, gpu.FP16_RN):
+                As = np.ascontiguousarray(A.T) if ta else A
+                Bs = np.ascontiguousarray(B.T) if tb else B
+                assert np.array_equal(run_matmul(gpu, As, Bs, ta, tb, precision=prec), k["int_b_C"])
+
+
+def test_reference_activation_kats(gpu, golden):
+    ref, _ = golden
+    k = ref["relu_forward"]
+    x = np.array(k["input"], np.float32)
+    i, o = gpu.Buffer.from_host(x), gpu.Buffer.empty(x.nbytes)
+    gpu.relu_forward(i, x.size, o)
+    assert np.allclose(o.retrieve(x.shape), k["expected"], atol=1e-6)
+    k = ref["relu_backward"]
+    go = gpu.Buffer.from_host(np.array(k["grad_output"], np.float32))
+    ao = gpu.Buffer.from_host(np.array(k["activation_output"], np.float32))
+    gi = gpu.Buffer.empty(24)
+    gpu.relu_backward(go, ao, 6, gi)
+    assert np.allclose(gi.retrieve((6,)), k["expected"], atol=1e-6)
+    # the other activation vectors go through the fused epilogue with W = I
+    eye = np.eye(4, dtype=np.float32)
+    k = ref["leaky_relu_forward"]
+    got = run_matmul(gpu, np.array([k["input"]], np.float32), eye, act=1, act_param=k["alpha"])
+    assert np.allclose(got[0], k["expected"], atol=1e-6)
+    for name, code in (("sigmoid_forward", 2), ("tanh_forward", 3)):
+        k = ref[name]
+        got = run_matmul(gpu, np.array([k["input"]], np.float32), eye, act=code)[0]
+        assert abs(got[k["index_of_zero"]] - k["expected_at_zero"]) <= 1e-6
+        assert (got >= k["range"][0]).all() and (got <= k["range"][1]).all()
+
+
+# ------------------------------------------------------------------ seeded parity
+@pytest.mark.parametrize("shape", [(1, 1, 1), (2, 3, 4), (31, 33, 35), (128, 128, 128), (129, 257, 65),
+                                   (200, 300, 136), (257, 10, 784), (512, 1024, 784), (1000, 1000, 1000),
+                                   (64, 2048, 96), (3000, 40, 520)])
+@pytest.mark.parametrize("layout", ["nn", "tn", "nt", "tt"])
+def test_fp32_path_matches_float64_reference(gpu, shape, layout):
+    m, n, k = shape
+    rng = np.random.default_rng(m * 1000003 + n * 1009 + k)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    ta, tb = layout[0] == "t", layout[1] == "t"
+    As = np.ascontiguousarray(A.T) if ta else A
+    Bs = np.ascontiguousarray(B.T) if tb else B
+    C = run_matmul(gpu, As, Bs, ta, tb, precision=gpu.FP32_3XTF32)
+    ref = oracle.gemm_f64(As, Bs, ta, tb)
+    assert oracle.rel_frobenius(C, ref) <= FP32_TOL
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (5, 7, 3), (128, 64, 64), (129, 257, 65), (200, 300, 136),
+                                   (257, 10, 784), (1024, 1024, 1024), (96, 4096, 160)])
+@pytest.mark.parametrize("layout", ["nn", "tn", "nt", "tt"])
+@pytest.mark.parametrize("mode", ["rn", "trunc"])
+def test_fp16_path_matches_float64_reference(gpu, shape, layout, mode):
+    m, n, k = shape
+    rng = np.random.default_rng(m * 7919 + n * 104729 + k)
+    A = (rng.standard_normal((m, k)) / np.sqrt(k)).astype(np.float32)
+    B = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32)
+    ta, tb = layout[0] == "t", layout[1] == "t"
+    As = np.ascontiguousarray(A.T) if ta else A
+    Bs = np.ascontiguousarray(B.T) if tb else B
+    prec = gpu.FP16_RN if mode == "rn" else gpu.FP16_TRUNC
+    C = run_matmul(gpu, As, Bs, ta, tb, precision=prec)
+    rnd = oracle.f16_rn if mode == "rn" else oracle.f16_trunc
+    # against the float64 product of the fp16-rounded inputs the only error left is
+    # the fp32 accumulation; against the unrounded inputs it is the fp16 tolerance
+    assert oracle.rel_frobenius(C, oracle.gemm_f64(rnd(As), rnd(Bs), ta, tb)) <= 2e-5
+    assert oracle.rel_frobenius(C, oracle.gemm_f64(As, Bs, ta, tb)) <= FP16_TOL
+
+
+def test_every_small_shape_fp32_and_fp16(gpu):
+    """All M, N, K in a ragged set: tile edges, K tails, single rows/columns."""
+    sizes = [1, 2, 3, 7, 8, 15, 16, 17, 31, 33, 63, 64, 65, 127, 129]
+    rng = np.random.default_rng(11)
+    bad = []
+    for m in sizes:
+        for n in sizes:
+            for k in (1, 5, 8, 31, 32, 33, 64, 65, 130):
+                A = rng.integers(-3, 4, (m, k)).astype(np.float32)
+                B = rng.integers(-3, 4, (k, n)).astype(np.float32)
+                ref = (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32)
+                prec = gpu.FP32_3XTF32 if (m + n + k) % 2 else gpu.FP16_RN
+                if not np.array_equal(run_matmul(gpu, A, B, precision=prec), ref):
+                    bad.append((m, n, k, prec))
+    assert not bad, bad[:10]
+
+
+def test_tile_overrides_agree(gpu):
+    rng = np.random.default_rng(12)
+    A = rng.standard_normal((300, 200)).astype(np.float32)
+    B = rng.standard_normal((200, 700)).astype(np.float32)
+    ref = oracle.gemm_f64(A, B)
+    try:
+        for bn in (32, 64, 128, 256):
+            assert gpu.lib().gonngpu_set_gemm_tuning(bn, 0) == 0
+            assert oracle.rel_frobenius(run_matmul(gpu, A, B, precision=gpu.FP32_3XTF32), ref) <= FP32_TOL
+            assert oracle.rel_frobenius(run_matmul(gpu, A, B, precision=gpu.FP16_RN),
+                                        oracle.gemm_f64(oracle.f16_rn(A), oracle.f16_rn(B))) <= 2e-5
+        # fewer CTAs than tiles: every CTA walks several tiles (persistent loop, both accumulators)
+        assert gpu.lib().gonngpu_set_gemm_tuning(64, 3) == 0
+        assert oracle.rel_frobenius(run_matmul(gpu, A, B, precision=gpu.FP32_3XTF32), ref) <= FP32_TOL
+    finally:
+        gpu.lib().gonngpu_set_gemm_tuning(0, 0)
+
+
+# ------------------------------------------------------------------ epilogues
+def test_fused_linear_activation_matches_oracle(gpu, golden):
+    _, k = golden
+    X, W, b = k["fl_X"], k["fl_W"], k["fl_b"]
+    x, w, bb = gpu.Buffer.from_host(X), gpu.Buffer.from_host(W), gpu.Buffer.from_host(b)
+    y = gpu.Buffer.empty(X.shape[0] * W.shape[1] * 4)
+    for act in (0, 1, 2, 3, 4, 9):
+        gpu.fused_linear_activation(x, X.shape[0], X.shape[1], w, W.shape[1], bb, act, 0.25, y)
+        got = y.retrieve((X.shape[0], W.shape[1]))
+        assert oracle.rel_frobenius(got, k[f"fl_act{act}_f64"]) <= FP32_TOL, act
+        assert np.allclose(got, k[f"fl_act{act}_f32"], rtol=0, atol=2e-5), act
+    # bias is optional
+    gpu.fused_linear_activation(x, X.shape[0], X.shape[1], w, W.shape[1], None, 0, 0.0, y)
+    ref = oracle.fused_linear_activation_f64(X, W, None, 0, 0.0)
+    assert oracle.rel_frobenius(y.retrieve(ref.shape), ref) <= FP32_TOL
+
+
+def test_fused_linear_seeded_ragged(gpu):
+    rng = np.random.default_rng(13)
+    for (bsz, fin, fout) in [(1, 1, 1), (33, 70, 10), (512, 784, 1024), (130, 257, 999)]:
+        X = rng.uniform(0, 1, (bsz, fin)).astype(np.float32)
+        W = (rng.standard_normal((fin, fout)) * np.sqrt(2.0 / fin)).astype(np.float32)
+        b = rng.standard_normal(fout).astype(np.float32)
+        for act in (0, 4):
+            got = run_matmul(gpu, X, W, bias=b, act=act)
+            assert oracle.rel_frobenius(got, oracle.fused_linear_activation_f64(X, W, b, act, 0.0)) <= FP32_TOL
+
+
+def test_alpha_beta_gemm(gpu, golden):
+    _, k = golden
+    a, b = gpu.Buffer.from_host(k["ab_A"]), gpu.Buffer.from_host(k["ab_B"])
+    c = gpu.Buffer.from_host(k["ab_C0"].copy())
+    gpu.optimized_gemm(a, b, c, 17, 21, 12, 0.5, -2.0)
+    assert np.array_equal(c.retrieve((17, 21)), k["ab_out"])  # small integers and halves: exact
+    rng = np.random.default_rng(14)
+    A = rng.standard_normal((150, 90)).astype(np.float32)
+    B = rng.standard_normal((90, 260)).astype(np.float32)
+    C0 = rng.standard_normal((150, 260)).astype(np.float32)
+    got = run_matmul(gpu, A, B, alpha=1.5, beta=0.75, C0=C0.copy())
+    ref = 1.5 * oracle.gemm_f64(A, B) + 0.75 * C0.astype(np.float64)
+    assert oracle.rel_frobenius(got, ref) <= FP32_TOL
+
+
+# ------------------------------------------------------------------ HBM-bound kernels
+@pytest.mark.parametrize("shape", [(1, 1), (1, 9), (9, 1), (37, 101), (64, 64), (65, 63), (130, 260),
+                                   (1000, 36), (4096, 4096), (2051, 4099)])
+def test_transpose_is_bit_exact(gpu, shape):
+    rng = np.random.default_rng(shape[0] * 31 + shape[1])
+    X = rng.standard_normal(shape).astype(np.float32)
+    flat = X.reshape(-1)
+    flat[0] = np.float32("nan")
+    flat[-1] = np.float32("-0.0")
+    i, o = gpu.Buffer.from_host(X), gpu.Buffer.empty(X.nbytes)
+    gpu.transpose(i, X.shape, o)
+    got = o.retrieve((shape[1], shape[0]))
+    assert np.array_equal(got.view(np.uint32), oracle.transpose(X).view(np.uint32))
+    # involution: transposing back restores the input bit for bit
+    o2 = gpu.Buffer.empty(X.nbytes)
+    gpu.transpose(o, (shape[1], shape[0]), o2)
+    assert np.array_equal(o2.retrieve(shape).view(np.uint32), X.view(np.uint32))
+
+
+def test_golden_transpose_broadcast_colsum_f16(gpu, golden):
+    _, k = golden
+    i, o = gpu.Buffer.from_host(k["tr_in"]), gpu.Buffer.empty(k["tr_in"].nbytes)
+    gpu.transpose(i, k["tr_in"].shape, o)
+    assert np.array_equal(o.retrieve(k["tr_out"].shape).view(np.uint32), k["tr_out"].view(np.uint32))
+    M, row, col = k["bc_M"], k["bc_row"], k["bc_col"]
+    m, r, c = gpu.Buffer.from_host(M), gpu.Buffer.from_host(row), gpu.Buffer.from_host(col)
+    out = gpu.Buffer.empty(M.nbytes)
+    for (x, xs, y, ys, key) in [(m, M.shape, r, row.shape, "bc_m_row"), (r, row.shape, m, M.shape, "bc_row_m"),
+                                (m, M.shape, c, col.shape, "bc_m_col"), (c, col.shape, m, M.shape, "bc_col_m")]:
+        gpu.add_broadcast(x, xs, y, ys, out, M.shape)
+        assert np.array_equal(out.retrieve(M.shape), k[key])
+    with pytest.raises(gpu.GonnError) as e:
+        gpu.add_broadcast(m, M.shape, m, (2, 2), out, M.shape)
+    assert e.value.code == -2 and "Unsupported broadcasting pattern" in e.value.message
+    cs = gpu.Buffer.empty(M.shape[1] * 4)
+    gpu.column_sum(m, M.shape[0], M.shape[1], cs)
+    assert np.allclose(cs.retrieve((M.shape[1],)), k["colsum_out"], rtol=1e-6, atol=1e-6)
+    # the truncating fp16 conversion is exercised through a product with the identity:
+    # C = trunc16(x) exactly (fp16 values times 1, fp32 accumulate)
+    x = k["f16_in"][np.isfinite(k["f16_trunc_out"]) & np.isfinite(k["f16_in"])][:1024].reshape(16, 64)
+    got = run_matmul(gpu, x, np.eye(64, dtype=np.float32), precision=gpu.FP16_TRUNC)
+    assert np.array_equal(got, oracle.f16_trunc(x))  # float compare: -0 == +0
+    got = run_matmul(gpu, x, np.eye(64, dtype=np.float32), precision=gpu.FP16_RN)
+    assert np.array_equal(got, oracle.f16_rn(x))
+
+
+# ------------------------------------------------------------------ the benchmark configurations
+def test_config1_fp32_1024(gpu):
+    A, B = oracle.config1()
+    C = run_matmul(gpu, A, B, entry="mps")
+    assert oracle.rel_frobenius(C, oracle.gemm_f64(A, B)) <= FP32_TOL
+
+
+def test_config2_fp32_4096_all_layouts_and_transpose(gpu):
+    A, B = oracle.config2()
+    ref = oracle.gemm_f64(A, B)
+    assert oracle.rel_frobenius(run_matmul(gpu, A, B, entry="mps"), ref) <= FP32_TOL
+    At = np.ascontiguousarray(A.T)
+    assert oracle.rel_frobenius(run_matmul(gpu, At, B, True, False), ref) <= FP32_TOL
+    Bt = np.ascontiguousarray(B.T)
+    assert oracle.rel_frobenius(run_matmul(gpu, A, Bt, False, True), ref) <= FP32_TOL
+    i, o = gpu.Buffer.from_host(A), gpu.Buffer.empty(A.nbytes)
+    gpu.transpose(i, A.shape, o)
+    assert np.array_equal(o.retrieve(At.shape).view(np.uint32), At.view(np.uint32))
+
+
+def test_config3_mlp_training_step_gemm_set(gpu):
+    X, Ws, bs, dYs = oracle.config3()
+    h = X
+    for layer in range(3):
+        act = 0 if layer < 2 else -1
+        y = run_matmul(gpu, h, Ws[layer], bias=bs[layer], act=act)
+        ref = oracle.apply_act_f64(oracle.gemm_f64(h, Ws[layer]) + bs[layer].astype(np.float64), act)
+        assert oracle.rel_frobenius(y, ref) <= FP32_TOL, ("fwd", layer)
+        # backward GEMMs on the given dY: dW = h^T . dY, dX = dY . W^T
+        dW = run_matmul(gpu, h, dYs[layer], True, False)
+        assert oracle.rel_frobenius(dW, oracle.gemm_f64(h, dYs[layer], True, False)) <= FP32_TOL, ("dW", layer)
+        dX = run_matmul(gpu, dYs[layer], Ws[layer], False, True)
+        assert oracle.rel_frobenius(dX, oracle.gemm_f64(dYs[layer], Ws[layer], False, True)) <= FP32_TOL, ("dX", layer)
+        h = y
+
+
+def _row_sample(m, shards=8, per_shard=24, seed=0):
+    rng = np.random.default_rng(seed)
+    rows = set()
+    for s in range(shards):
+        lo, hi = s * m // shards, (s + 1) * m // shards
+        rows.update([lo, hi - 1])
+        rows.update(rng.integers(lo, hi, per_shard).tolist())
+    return np.array(sorted(rows))
+
+
+def test_config4_fp16_8192_sampled_rows_and_checksum(gpu):
+    A, B = oracle.config4()
+    C = run_matmul(gpu, A, B, precision=gpu.FP16_RN)
+    rows = _row_sample(A.shape[0])
+    ref_rows = oracle.gemm_f64(A[rows], B)
+    assert oracle.rel_frobenius(C[rows], ref_rows) <= FP16_TOL
+    assert oracle.rel_frobenius(C[rows], oracle.gemm_f64(oracle.f16_rn(A[rows]), oracle.f16_rn(B))) <= 5e-5
+    # full-size property: C.1 == A16.(B16.1) in float64 (a checksum over every output)
+    A16, B16 = oracle.f16_rn(A).astype(np.float64), oracle.f16_rn(B).astype(np.float64)
+    want = A16 @ (B16 @ np.ones(B.shape[1]))
+    got = C.astype(np.float64) @ np.ones(B.shape[1])
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-4
+
+
+def test_buffer_protocol(gpu):
+    """Lazy upload, retrieval of an untouched buffer, size checks, release."""
+    x = np.arange(12, dtype=np.float32)
+    b = gpu.Buffer.from_host(x)
+    assert np.array_equal(b.retrieve((12,)), x)          # never uploaded: host bytes are the contents
+    with pytest.raises(gpu.GonnError) as e:
+        b.retrieve((13,))
+    assert e.value.code == -2 and "length mismatch" in e.value.message
+    b.upload(x * 2)
+    assert np.array_equal(b.retrieve((12,)), x * 2)
+    before = gpu.stats()["buffers"]
+    b.release()
+    assert gpu.stats()["buffers"] == before - 1
+    # dimension errors keep the reference's codes
+    a, c = gpu.Buffer.from_host(np.zeros((2, 3), np.float32)), gpu.Buffer.empty(16)
+    with pytest.raises(gpu.GonnError) as e:
+        gpu.matmul(a, (2, 3), a, (2, 3), c, (2, 2))
+    assert e.value.code == -3
+    with pytest.raises(gpu.GonnError) as e:
+        gpu.transpose(a, (2, 3), gpu.Buffer.empty(8))
+    assert e.value.code == -2
+    # memory from the unified-memory adapter's allocator works as a buffer
+    p = gpu.lib().allocateSharedMemory(64)
+    assert p
+    arr = np.frombuffer((ctypes.c_char * 64).from_address(p), dtype=np.float32)
+    assert (arr == 0).all()
+    arr[:] = np.arange(16)
+    h = gpu.lib().createGPUBufferFromSharedMemory(None, p, 64)
+    assert h
+    hb = gpu.Buffer(ctypes.c_void_p(h), 64)
+    out = gpu.Buffer.empty(64)
+    gpu.transpose(hb, (4, 4), out)
+    assert np.array_equal(out.retrieve((4, 4)), np.arange(16, dtype=np.float32).reshape(4, 4).T)
+    hb.release()
+    gpu.lib().gonngpu_host_free(p)

@@ -1,0 +1,103 @@
+"""CPU tests of the oracle itself: against the reference's own known-answer
+vectors, against the committed golden file, and against independent numpy
+restatements."""
+import numpy as np
+
+from oracle import oracle
+
+
+def test_relu_kats_from_reference(golden):
+    ref, _ = golden
+    k = ref["relu_forward"]
+    got = oracle.relu_forward(np.array(k["input"], np.float32))
+    assert np.allclose(got, k["expected"], atol=1e-6)
+    k = ref["relu_backward"]
+    got = oracle.relu_backward(np.array(k["grad_output"], np.float32),
+                               np.array(k["activation_output"], np.float32))
+    assert np.allclose(got, k["expected"], atol=1e-6)
+
+
+def test_activation_kats_through_fused_oracle(golden):
+    """The reference's activation tests, driven through the fused-linear oracle
+    with an identity weight so that the pre-activation equals the input."""
+    ref, _ = golden
+    eye = np.eye(4, dtype=np.float32)
+    k = ref["leaky_relu_forward"]
+    got = oracle.fused_linear_activation(np.array([k["input"]], np.float32), eye, None, 1, k["alpha"])
+    assert np.allclose(got[0], k["expected"], atol=1e-6)
+    for name, code in (("sigmoid_forward", 2), ("tanh_forward", 3)):
+        k = ref[name]
+        got = oracle.fused_linear_activation(np.array([k["input"]], np.float32), eye, None, code, 0.0)[0]
+        assert abs(got[k["index_of_zero"]] - k["expected_at_zero"]) <= 1e-6
+        assert (got >= k["range"][0]).all() and (got <= k["range"][1]).all()
+
+
+def test_oracle_matches_committed_golden(golden):
+    _, g = golden
+    for name in ("int_a", "int_b", "int_c"):
+        C = oracle.gemm_f64_naive(g[f"{name}_A"], g[f"{name}_B"])
+        assert np.array_equal(C.astype(np.float32), g[f"{name}_C"])
+    assert np.array_equal(oracle.gemm_f64_naive(g["perm_P"], g["perm_V"]).astype(np.float32), g["perm_C"])
+    assert np.array_equal(oracle.transpose(g["tr_in"]).view(np.uint32), g["tr_out"].view(np.uint32))
+    assert np.array_equal(oracle.f16_trunc(g["f16_in"]).view(np.uint32), g["f16_trunc_out"].view(np.uint32))
+    for act in (0, 1, 2, 3, 4, 9):
+        got = oracle.fused_linear_activation(g["fl_X"], g["fl_W"], g["fl_b"], act, 0.25)
+        assert np.allclose(got, g[f"fl_act{act}_f32"], rtol=0, atol=1e-6)
+        assert oracle.rel_frobenius(got, g[f"fl_act{act}_f64"]) < 1e-6
+    assert np.array_equal(oracle.gemm_alpha_beta(g["ab_A"], g["ab_B"], g["ab_C0"], 0.5, -2.0), g["ab_out"])
+    assert np.array_equal(oracle.add_broadcast(g["bc_M"], g["bc_row"], (6, 11))[1], g["bc_m_row"])
+    assert np.array_equal(oracle.add_broadcast(g["bc_col"], g["bc_M"], (6, 11))[1], g["bc_col_m"])
+    assert np.array_equal(oracle.column_sum(g["colsum_in"]), g["colsum_out"])
+
+
+def test_naive_c_gemm_agrees_with_numpy_float64():
+    rng = np.random.default_rng(5)
+    for (m, n, k) in [(1, 1, 1), (33, 17, 129), (128, 96, 200)]:
+        A = rng.standard_normal((m, k)).astype(np.float32)
+        B = rng.standard_normal((k, n)).astype(np.float32)
+        ref = oracle.gemm_f64(A, B)
+        assert oracle.rel_frobenius(oracle.gemm_f64_naive(A, B), ref) < 1e-14
+        assert oracle.rel_frobenius(oracle.gemm_f64_naive(np.ascontiguousarray(A.T), B, True, False), ref) < 1e-14
+        assert oracle.rel_frobenius(oracle.gemm_f64_naive(A, np.ascontiguousarray(B.T), False, True), ref) < 1e-14
+
+
+def test_transpose_index_formula():
+    X = np.arange(12, dtype=np.float32).reshape(3, 4)
+    assert np.array_equal(oracle.transpose(X), X.T)
+    assert oracle.lib().oracle_transpose(None, 3, 4, None, 3, 4) == -2  # dimension check comes first
+
+
+def test_f16_truncation_properties():
+    rng = np.random.default_rng(6)
+    x = (rng.standard_normal(50000) * 10.0 ** rng.integers(-9, 6, 50000)).astype(np.float32)
+    t = oracle.f16_trunc(x)
+    assert np.array_equal(t.view(np.uint32), oracle.f16_trunc_numpy(x).view(np.uint32))
+    # truncation never increases magnitude; results are fp16-representable
+    fin = np.isfinite(t)
+    assert (np.abs(t[fin]) <= np.abs(x[fin])).all()
+    assert np.array_equal(t[fin].astype(np.float16).astype(np.float32), t[fin])
+    # idempotent
+    assert np.array_equal(oracle.f16_trunc(t).view(np.uint32), t.view(np.uint32))
+    # overflow goes to infinity, tiny values flush to signed zero
+    assert np.isinf(oracle.f16_trunc(np.array([70000.0], np.float32))[0])
+    z = oracle.f16_trunc(np.array([-1e-9], np.float32))
+    assert z[0] == 0.0 and np.signbit(z[0])
+
+
+def test_add_broadcast_rejects_other_shapes():
+    a = np.zeros((2, 3), np.float32)
+    rc, _ = oracle.add_broadcast(a, np.zeros((2, 2), np.float32), (2, 3))
+    assert rc == -2
+
+
+def test_config_generators_are_seeded_and_shaped():
+    A, B = oracle.config1(64)
+    A2, B2 = oracle.config1(64)
+    assert np.array_equal(A, A2) and np.array_equal(B, B2)
+    assert A.dtype == np.float32 and A.min() >= -1 and A.max() < 1
+    X, Ws, bs, dYs = oracle.config3(8)
+    assert X.shape == (8, 784) and [w.shape for w in Ws] == [(784, 1024), (1024, 1024), (1024, 10)]
+    assert all((b == 0).all() for b in bs) and [d.shape for d in dYs] == [(8, 1024), (8, 1024), (8, 10)]
+    A, B = oracle.config5(256, 64, 32)
+    assert A.shape == (256, 64) and B.shape == (64, 32)
+    assert abs(A.std() - 1 / 8) < 0.01
