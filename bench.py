@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-GEMM hot path.
+
+    python bench.py --gpus N --steps K --warmup W            (our CUDA path)
+    python bench.py --impl reference --gpus N --steps K ...  (CPU baseline arm)
+
+Workload: the row-sharded tall GEMM of the benchmark configurations, fp16
+inputs / fp32 accumulate / fp32 C, M=131072, K=4096, N=4096, A split by rows
+across the N ranks (one process per GPU), B replicated from rank 0 over
+NVLink (NCCL broadcast) inside every step when N > 1.  Inputs are seeded
+synthetic normal(0, 1/sqrt(K)) values.  One "step" is one full product.
+
+`value` is device-timed with the operands already resident in HBM as fp16;
+`e2e` is the same product through the handle-based C ABI from page-locked host
+memory (float32 in, float32 out, copies and the fp32->fp16 pre-pass included).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "go-nngpu_b200"))
+sys.path.insert(0, ROOT)
+
+M_TOTAL, K_DIM, N_DIM = 131072, 4096, 4096
+WORKLOAD = "row-sharded GEMM fp16-in/fp32-acc M=131072 K=4096 N=4096 (A rows split, B replicated)"
+METRIC = "GEMM TFLOP/s"
+
+
+def shard_rows(m_total, world, rank, align=128):
+    """Contiguous row block of rank `rank`: blocks are multiples of `align`
+    (the GEMM's tile height) except possibly the last."""
+    per = -(-m_total // world)
+    per = -(-per // align) * align
+    lo = min(rank * per, m_total)
+    hi = min(lo + per, m_total)
+    return lo, hi
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"burst": float(p["bf16_tflops"]), "sustained": float(p["bf16_tflops_sustained"]),
+                "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def result(self):
+        self.stop_flag = True
+        self.join(timeout=1.0)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def cpu_gemm_rate(rows, seconds_hint=None):
+    """float64 product of a `rows`-row slice of the workload on the host cores
+    (numpy / OpenBLAS): the stand-in for gonum's mat.Dense.Mul, which is not
+    installable here.  Returns (TFLOP/s, seconds, threads)."""
+    rng = np.random.default_rng(4)
+    s = 1.0 / np.sqrt(K_DIM)
+    A = (rng.standard_normal((rows, K_DIM)) * s).astype(np.float32).astype(np.float16).astype(np.float64)
+    B = (rng.standard_normal((K_DIM, N_DIM)) * s).astype(np.float32).astype(np.float16).astype(np.float64)
+    t0 = time.perf_counter()
+    C = A @ B
+    dt = time.perf_counter() - t0
+    assert np.isfinite(C[0, 0])
+    return 2.0 * rows * K_DIM * N_DIM / dt / 1e12, dt, blas_threads()
+
+
+def blas_threads():
+    try:
+        from threadpoolctl import threadpool_info
+        n = [p.get("num_threads", 0) for p in threadpool_info() if p.get("user_api") == "blas"]
+        return int(max(n)) if n else (os.cpu_count() or 1)
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference(args, rank):
+    """CPU arm: the float64 GEMM on the host cores over a bounded row sample."""
+    if rank != 0:
+        return
+    # size the sample so that steps+warmup fit in ~2 minutes
+    probe_rows = 256
+    rate, dt, threads = cpu_gemm_rate(probe_rows)
+    budget = 120.0 / max(args.steps + args.warmup, 1)
+    rows = int(min(M_TOTAL, max(probe_rows, probe_rows * budget / max(dt, 1e-6))))
+    rows = max(128, rows // 128 * 128)
+    rng = np.random.default_rng(4)
+    s = 1.0 / np.sqrt(K_DIM)
+    A = (rng.standard_normal((rows, K_DIM)) * s).astype(np.float32).astype(np.float16).astype(np.float64)
+    B = (rng.standard_normal((K_DIM, N_DIM)) * s).astype(np.float32).astype(np.float16).astype(np.float64)
+    for _ in range(args.warmup):
+        A @ B
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        A @ B
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    val = 2.0 * rows * K_DIM * N_DIM / dt / 1e12
+    sample = f"{rows} of {M_TOTAL} rows per step (float64 numpy/OpenBLAS; stand-in for gonum mat.Dense.Mul, gonum/Go not installed)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import gonngpu as g
+    import build as gonn_build
+    if rank == 0:
+        gonn_build.build()
+    dist = None
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.barrier()
+    L = g.lib()
+    assert L.gonngpu_set_device(local_rank) == 0, "no usable B200 for this rank"
+    stream = torch.cuda.ExternalStream(L.gonngpu_stream(), device=torch.device("cuda", local_rank))
+    lo, hi = shard_rows(M_TOTAL, world, rank)
+    rows = hi - lo
+    dev = torch.device("cuda", local_rank)
+    scale = 1.0 / np.sqrt(K_DIM)
+
+    with torch.cuda.stream(stream):
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(4 * 1000 + rank)
+        A32 = torch.randn((rows, K_DIM), generator=gen, device=dev, dtype=torch.float32) * scale
+        A16 = torch.empty((rows, K_DIM), device=dev, dtype=torch.float16)
+        B16 = torch.zeros((K_DIM, N_DIM), device=dev, dtype=torch.float16)
+        C = torch.empty((rows, N_DIM), device=dev, dtype=torch.float32)
+        gen.manual_seed(4)
+        B32 = torch.randn((K_DIM, N_DIM), generator=gen, device=dev, dtype=torch.float32) * scale
+        L.gonngpu_set_blocking(0)
+        g.convert_f16_device(A32.data_ptr(), rows, K_DIM, A16.data_ptr(), K_DIM)
+        if rank == 0:
+            g.convert_f16_device(B32.data_ptr(), K_DIM, N_DIM, B16.data_ptr(), N_DIM)
+        stream.synchronize()
+
+        def step():
+            if world > 1:
+                dist.broadcast(B16, src=0)
+            g.gemm_f16_device(A16.data_ptr(), (rows, K_DIM), K_DIM, False, B16.data_ptr(),
+                              (K_DIM, N_DIM), N_DIM, False, C.data_ptr(), N_DIM)
+
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        launches0 = g.stats()["kernel_launches"]
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in range(args.steps)]
+        ev0.record(stream)
+        for i in range(args.steps):
+            if world > 1:
+                dist.broadcast(B16, src=0)
+            kev[i][0].record(stream)
+            g.gemm_f16_device(A16.data_ptr(), (rows, K_DIM), K_DIM, False, B16.data_ptr(),
+                              (K_DIM, N_DIM), N_DIM, False, C.data_ptr(), N_DIM)
+            kev[i][1].record(stream)
+        ev1.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        clocks = sampler.result()
+        g.synchronize()  # surfaces any kernel status
+        launches = g.stats()["kernel_launches"] - launches0
+        total_ms = ev0.elapsed_time(ev1)
+        kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in kev]))
+        t = torch.tensor([total_ms, kernel_ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, kernel_ms_max = float(t[0]), float(t[1])
+        ms_per_step = total_ms / args.steps
+        value = 2.0 * M_TOTAL * K_DIM * N_DIM / (ms_per_step * 1e-3) / 1e12
+
+        # ---- spot check of the timed result against the CPU oracle (rank 0, a few rows)
+        check = None
+        if rank == 0:
+            from oracle import oracle
+            idx = torch.tensor([0, 1, rows // 2, rows - 1], device=dev)
+            ref = oracle.gemm_f64(A16[idx].float().cpu().numpy(), B16.float().cpu().numpy())
+            check = oracle.rel_frobenius(C[idx].cpu().numpy(), ref)
+
+        # ---- end to end through the handle-based C ABI from page-locked host memory
+        L.gonngpu_set_blocking(1)
+        e2e = None
+        if not args.no_e2e:
+            e2e = run_e2e(args, g, L, torch, dist, dev, rank, world, rows, A32, B32)
+        del A32
+
+    if rank == 0:
+        report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, clocks, launches, check, e2e)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, g, L, torch, dist, dev, rank, world, rows, A32, B32):
+    if True:
+        hA, pA = g.pinned_array((rows, K_DIM))
+        hC, pC = g.pinned_array((rows, N_DIM))
+        hB, pB = g.pinned_array((K_DIM, N_DIM))
+        A32h = torch.from_numpy(hA)
+        A32h.copy_(A32.cpu())
+        torch.from_numpy(hB).copy_(B32.cpu())
+        e2e_steps = max(1, min(args.steps, 4))
+
+        def e2e_step():
+            a = g.Buffer.from_host(hA)
+            c = g.Buffer.from_host(hC)
+            if world > 1:
+                # rank 0 uploads B; every other rank receives it over NVLink
+                Bdev = torch.empty((K_DIM, N_DIM), device=dev, dtype=torch.float32)
+                b = g.Buffer.wrap(Bdev.data_ptr(), Bdev.numel() * 4, Bdev)
+                if rank == 0:
+                    b.upload(hB)
+                dist.broadcast(Bdev, src=0)
+                L.gonngpu_mark_modified(b.handle)
+            else:
+                b = g.Buffer.from_host(hB)
+            g.matmul_ex(a, (rows, K_DIM), False, b, (K_DIM, N_DIM), False, c, (rows, N_DIM),
+                        precision=g.FP16_RN)
+            c.retrieve_into(hC)
+            for x in (a, b, c):
+                x.release()
+
+        e2e_step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        s0 = g.stats()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        s1 = g.stats()
+        te = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_s = float(te[0])
+        e2e_val = 2.0 * M_TOTAL * K_DIM * N_DIM / e2e_s / 1e12
+        h2d = (s1["h2d_bytes"] - s0["h2d_bytes"]) // e2e_steps
+        d2h = (s1["d2h_bytes"] - s0["d2h_bytes"]) // e2e_steps
+        for p in (pA, pB, pC):
+            L.gonngpu_host_free(p)
+        return {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_s * 1e3, "steps": e2e_steps}
+
+
+def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, clocks, launches, check, e2e):
+    if True:
+        peaks = load_peaks()
+        timed_s = total_ms * 1e-3
+        peak_kind = "sustained" if timed_s >= 1.0 else "burst"
+        achieved = 2.0 * rows * K_DIM * N_DIM / (kernel_ms_max * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "rows_per_gpu": rows, "parallelism": f"row-shard x{world}",
+                       "l2": "operands and result (>=384 MiB per GPU) exceed the 126 MB L2",
+                       "b_broadcast_in_step": world > 1},
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
+                         "frac": achieved / peaks[peak_kind], "traffic": None,
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 ({peak_kind})",
+                         "kernel_ms": kernel_ms_max},
+            "e2e": e2e,
+            "gpu_launches": int(launches),
+            "parity_spot_check_rel_frobenius": check,
+        }
+        if world == 1 and not args.no_cpu:
+            rate, dt, threads = cpu_gemm_rate(256)
+            rows_cpu = int(min(8192, max(256, 256 * 12.0 / max(dt, 1e-6)))) // 128 * 128
+            rate, dt, threads = cpu_gemm_rate(max(rows_cpu, 128))
+            line["cpu_baseline"] = {
+                "value": rate, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"{max(rows_cpu, 128)} of {M_TOTAL} rows, float64 numpy/OpenBLAS "
+                          f"(stand-in for gonum mat.Dense.Mul: Go and gonum are not installed), {dt:.1f} s"}
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    global M_TOTAL, WORKLOAD
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--m-total", type=int, default=M_TOTAL,
+                    help="rows of A (default: the benchmark's 131072; smaller only for profiler captures)")
+    args = ap.parse_args()
+    if args.m_total != M_TOTAL:
+        M_TOTAL = args.m_total
+        WORKLOAD = WORKLOAD.replace("M=131072", f"M={M_TOTAL} (reduced for profiling)")
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

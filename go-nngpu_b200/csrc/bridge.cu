@@ -684,6 +684,68 @@ void* createGPUBufferFromSharedMemory(void* /*device*/, void* memory, long size)
 // Part 2: additive entry points
 // =========================================================================
 
+int gonngpu_gemm_f16_device(const void* a, long aRows, long aCols, long aPitch, int transA,
+                            const void* b, long bRows, long bCols, long bPitch, int transB,
+                            float* c, long ldc, float alpha, float beta, const float* bias,
+                            int activation_type, float activation_param, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!a || !b || !c) {
+    set_error(err, "gemm_f16_device: NULL operand pointer.");
+    return -2;
+  }
+  if (ensure_device(g_current, err)) return -1;
+  Device& d = g_dev[g_current];
+  const long M = transA ? aCols : aRows, K = transA ? aRows : aCols;
+  const long Kb = transB ? bCols : bRows, N = transB ? bRows : bCols;
+  if (aRows <= 0 || aCols <= 0 || bRows <= 0 || bCols <= 0 || K != Kb || aPitch < aCols ||
+      bPitch < bCols || ldc < N || aPitch % 8 || bPitch % 8 || M >= (1l << 31) || N >= (1l << 31) ||
+      K >= (1l << 31)) {
+    set_error(err, "gemm_f16_device: incompatible dimensions or pitches (op(A) %ldx%ld, op(B) %ldx%ld).",
+              M, K, Kb, N);
+    return -3;
+  }
+  gonn::GemmOperand oa, ob;
+  oa.plane0 = a;
+  oa.pitch = uint64_t(aPitch);
+  oa.mn_major = transA != 0;
+  ob.plane0 = b;
+  ob.pitch = uint64_t(bPitch);
+  ob.mn_major = transB == 0;
+  gonn::GemmEpilogue epi;
+  epi.alpha = alpha;
+  epi.beta = beta;
+  epi.c_in = c;
+  epi.bias = bias;
+  epi.act = (activation_type >= 0 && activation_type <= 4) ? activation_type : GONNGPU_ACT_NONE;
+  epi.act_param = activation_param;
+  const char* msg = gonn::launch_gemm(gonn::Kind::F16, uint32_t(M), uint32_t(N), uint32_t(K), oa, ob, c,
+                                      uint64_t(ldc), epi, d.status_dev, d.sm_count, g_tune, d.stream);
+  if (msg) {
+    cudaGetLastError();
+    set_error(err, "gemm_f16_device: %s", msg);
+    return (std::strstr(msg, "pitch") || std::strstr(msg, "aligned")) ? -3 : -4;
+  }
+  ++g_stats[3];
+  ++g_stats[4];
+  return finish(d, err, -6, "gemm_f16_device");
+}
+
+int gonngpu_convert_f16_device(const float* src, long rows, long cols, void* dst, long dstPitch,
+                               int mode, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!src || !dst || rows < 0 || cols < 0 || dstPitch < cols ||
+      (mode != GONNGPU_FP16_RN && mode != GONNGPU_FP16_TRUNC)) {
+    set_error(err, "convert_f16_device: invalid arguments.");
+    return -3;
+  }
+  if (ensure_device(g_current, err)) return -1;
+  Device& d = g_dev[g_current];
+  gonn::launch_cvt_f16(src, uint64_t(rows), uint64_t(cols), dst, uint64_t(dstPitch),
+                       mode == GONNGPU_FP16_RN ? gonn::F16_RN : gonn::F16_TRUNC, d.stream);
+  ++g_stats[3];
+  return finish(d, err, -6, "convert_f16_device");
+}
+
 int gonngpu_column_sum(GPUPtr inPtr, long rows, long cols, GPUPtr outPtr, CError* err) {
   std::lock_guard<std::recursive_mutex> lk(g_mu);
   Buffer* in = as_buffer(inPtr);

@@ -377,6 +377,318 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
   }
 }
 
+// ---------------------------------------------------------------------------
+// fp32-accurate variant: three tf32 MMAs per k step on (hi, lo) planes, with
+// the TMEM accumulator PROMOTED to fp32 registers every CHUNK_KB k blocks.
+//
+// Why: the tensor core adds into its fp32 accumulator with truncation, so the
+// error of a long K loop grows linearly with the number of MMAs (measured:
+// 3.6e-6 relative at K=512, which would pass 1e-5 near K=1500).  Here an
+// accumulator only ever holds CHUNK_KB*32 values of K; the epilogue warps drain
+// it with tcgen05.ld and add it to running sums with round-to-nearest fp32
+// adds, so the error no longer depends on K.  The two TMEM accumulators
+// alternate per chunk, which also overlaps the drain with the next chunk's MMAs.
+//
+// 10 warps: 0 producer, 1 MMA issuer, 2-9 drain/epilogue (warp w reads TMEM
+// lanes 32*(w%4).., and columns half (w-2)/4 of the tile).
+constexpr uint32_t TF32_THREADS = 320;
+constexpr uint32_t CHUNK_KB = 4;  // k blocks (of 32) per TMEM accumulation chunk
+
+template <int NC>
+__device__ __forceinline__ void drain_add(uint32_t taddr, float (&sums)[NC]) {
+  static_assert(NC % 32 == 0 || NC == 16, "columns per thread");
+  if constexpr (NC == 16) {
+    uint32_t r[16];
+    ptx::tmem_ld_32x16(taddr, r);
+    ptx::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) sums[i] += __uint_as_float(r[i]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < NC / 32; ++j) {
+      uint32_t r[32];
+      ptx::tmem_ld_32x32(taddr + j * 32, r);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sums[j * 32 + i] += __uint_as_float(r[i]);
+    }
+  }
+}
+
+template <int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(TF32_THREADS, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
+                   const __grid_constant__ CUtensorMap tm_a1,
+                   const __grid_constant__ CUtensorMap tm_b0,
+                   const __grid_constant__ CUtensorMap tm_b1,
+                   const __grid_constant__ KernelParams p) {
+  constexpr uint32_t B_TILE_BYTES = BLOCK_N * SLAB_ROW_BYTES;
+  constexpr uint32_t STAGE_BYTES = 2 * (A_TILE_BYTES + B_TILE_BYTES);
+  constexpr uint32_t TMEM_COLS = (2 * BLOCK_N < 64) ? 64 : 2 * BLOCK_N;
+  constexpr int NC = BLOCK_N / 2;  // columns per drain thread
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 8);  // one arrival per drain warp
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&tm_a0);
+    ptx::prefetch_tmap(&tm_a1);
+    ptx::prefetch_tmap(&tm_b0);
+    ptx::prefetch_tmap(&tm_b1);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t chunks_per_tile = (p.num_kblocks + CHUNK_KB - 1) / CHUNK_KB;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    uint32_t stage = 0, phase = 0;
+    bool alive = true;
+    for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+      for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
+        bool ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 1, stage, t, kb);
+          }
+          alive = false;
+          break;
+        }
+        if (lane == 0) {
+          const uint32_t fb = full_bar(stage);
+          ptx::mbar_arrive_expect_tx(fb, STAGE_BYTES);
+          uint32_t dst = smem_base + stage * STAGE_BYTES;
+#pragma unroll
+          for (uint32_t pl = 0; pl < 2; ++pl) {
+            const CUtensorMap* ma = pl ? &tm_a1 : &tm_a0;
+            for (uint32_t s = 0; s < p.a.slabs; ++s) {
+              ptx::tma_load_2d(dst + s * p.a.slab_bytes, ma,
+                               int32_t(tm) * p.a.c0_tile + int32_t(s) * p.a.c0_slab +
+                                   int32_t(kb) * p.a.c0_k,
+                               int32_t(tm) * p.a.c1_tile + int32_t(kb) * p.a.c1_k, fb);
+            }
+            dst += A_TILE_BYTES;
+          }
+#pragma unroll
+          for (uint32_t pl = 0; pl < 2; ++pl) {
+            const CUtensorMap* mb = pl ? &tm_b1 : &tm_b0;
+            for (uint32_t s = 0; s < p.b.slabs; ++s) {
+              ptx::tma_load_2d(dst + s * p.b.slab_bytes, mb,
+                               int32_t(tn) * p.b.c0_tile + int32_t(s) * p.b.c0_slab +
+                                   int32_t(kb) * p.b.c0_k,
+                               int32_t(tn) * p.b.c1_tile + int32_t(kb) * p.b.c1_k, fb);
+            }
+            dst += B_TILE_BYTES;
+          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    uint32_t stage = 0, phase = 0;
+    uint32_t chunk = 0;  // running chunk count: selects accumulator and barrier parity
+    bool alive = true;
+    for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
+      for (uint32_t kb0 = 0; alive && kb0 < p.num_kblocks; kb0 += CHUNK_KB, ++chunk) {
+        const uint32_t acc = chunk & 1u;
+        const uint32_t acc_phase = (chunk >> 1) & 1u;
+        bool ok = ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 2, 0x100u | acc, t, kb0);
+          }
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        const uint32_t kb_end = min(kb0 + CHUNK_KB, p.num_kblocks);
+        for (uint32_t kb = kb0; kb < kb_end; ++kb) {
+          ok = ptx::mbar_wait(full_bar(stage), phase, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) {
+              *abort_flag = 1;
+              report(p.status, 2, stage, t, kb);
+            }
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+            const uint32_t b_addr = a_addr + 2 * A_TILE_BYTES;
+#pragma unroll
+            for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+              const uint32_t accum = ((kb - kb0) | ks) ? 1u : 0u;
+              const uint64_t a_hi = ptx::smem_desc_at(p.a.desc, a_addr + ks * p.a.kstep_bytes);
+              const uint64_t b_hi = ptx::smem_desc_at(p.b.desc, b_addr + ks * p.b.kstep_bytes);
+              const uint64_t a_lo =
+                  ptx::smem_desc_at(p.a.desc, a_addr + A_TILE_BYTES + ks * p.a.kstep_bytes);
+              const uint64_t b_lo =
+                  ptx::smem_desc_at(p.b.desc, b_addr + B_TILE_BYTES + ks * p.b.kstep_bytes);
+              ptx::mma_tf32(d_tmem, a_lo, b_hi, p.idesc, accum);
+              ptx::mma_tf32(d_tmem, a_hi, b_lo, p.idesc, 1u);
+              ptx::mma_tf32(d_tmem, a_hi, b_hi, p.idesc, 1u);
+            }
+            ptx::mma_commit(empty_bar(stage));
+            if (kb + 1 == kb_end) ptx::mma_commit(tfull_bar(acc));
+          }
+          __syncwarp();
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------- drain + epilogue warps
+    const uint32_t quarter = warp & 3u;
+    const uint32_t half = (warp - 2u) >> 2;  // which half of the tile's columns
+    uint32_t chunk = 0;
+    bool alive = true;
+    for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+      float sums[NC];
+#pragma unroll
+      for (int i = 0; i < NC; ++i) sums[i] = 0.f;
+      for (uint32_t c = 0; c < chunks_per_tile; ++c, ++chunk) {
+        const uint32_t acc = chunk & 1u;
+        const uint32_t acc_phase = (chunk >> 1) & 1u;
+        bool ok = ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 3, acc, t, c);
+          }
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        drain_add<NC>(tmem_base + ((quarter * 32u) << 16) + acc * BLOCK_N + half * NC, sums);
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      }
+      if (!alive) break;
+      const uint32_t row = tm * BLOCK_M + quarter * 32u + lane;
+      const uint32_t col0 = tn * BLOCK_N + half * NC;
+      if (row < p.M && col0 < p.N) {
+        float* c_row = p.C + uint64_t(row) * p.ldc;
+        const float* cin_row = p.c_in ? p.c_in + uint64_t(row) * p.ldc : nullptr;
+        if (col0 + NC <= p.N && p.vec_store) {
+#pragma unroll
+          for (int j = 0; j < NC; j += 4) {
+            float4 v;
+            v.x = sums[j + 0] * p.alpha;
+            v.y = sums[j + 1] * p.alpha;
+            v.z = sums[j + 2] * p.alpha;
+            v.w = sums[j + 3] * p.alpha;
+            if (cin_row) {
+              const float4 o = *reinterpret_cast<const float4*>(cin_row + col0 + j);
+              v.x += p.beta * o.x;
+              v.y += p.beta * o.y;
+              v.z += p.beta * o.z;
+              v.w += p.beta * o.w;
+            }
+            if (p.bias) {
+              const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+              v.x += b.x;
+              v.y += b.y;
+              v.z += b.z;
+              v.w += b.w;
+            }
+            if (p.act >= 0) {
+              v.x = apply_act(v.x, p.act, p.act_param);
+              v.y = apply_act(v.y, p.act, p.act_param);
+              v.z = apply_act(v.z, p.act, p.act_param);
+              v.w = apply_act(v.w, p.act, p.act_param);
+            }
+            *reinterpret_cast<float4*>(c_row + col0 + j) = v;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < NC; ++j) {
+            const uint32_t col = col0 + j;
+            if (col < p.N) {
+              float v = sums[j] * p.alpha;
+              if (cin_row) v += p.beta * cin_row[col];
+              if (p.bias) v += p.bias[col];
+              if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
+              c_row[col] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
+      if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
+      __nanosleep(1000);
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------- host side
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -471,7 +783,16 @@ const char* launch_variant(const CUtensorMap* maps, const KernelParams& kp, uint
   constexpr uint32_t smem = STAGES * planes * (A_TILE_BYTES + BLOCK_N * SLAB_ROW_BYTES) + 1024 + 256;
   static_assert(STAGES >= 2, "pipeline too shallow");
   static_assert(smem <= SMEM_LIMIT, "shared memory");
-  auto kern = gemm_tcgen05_kernel<KIND, BLOCK_N, STAGES>;
+  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+               const KernelParams);
+  uint32_t threads;
+  if constexpr (KIND == int(Kind::TF32x3)) {
+    kern = gemm_tf32x3_kernel<BLOCK_N, STAGES>;
+    threads = TF32_THREADS;
+  } else {
+    kern = gemm_tcgen05_kernel<KIND, BLOCK_N, STAGES>;
+    threads = NUM_THREADS;
+  }
   static bool attr_done_dev[64] = {};  // per variant and device
   int dev = 0;
   cudaGetDevice(&dev);
@@ -483,7 +804,7 @@ const char* launch_variant(const CUtensorMap* maps, const KernelParams& kp, uint
     }
     attr_done = true;
   }
-  kern<<<grid, NUM_THREADS, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], kp);
+  kern<<<grid, threads, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], kp);
   if (cudaGetLastError() != cudaSuccess) return "GEMM kernel launch failed";
   return nullptr;
 }

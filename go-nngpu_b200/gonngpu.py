@@ -54,6 +54,10 @@ SIGNATURES = {
     "gonngpu_matmul_ex": (
         _c_int, [_vp, _c_long, _c_long, _c_int, _vp, _c_long, _c_long, _c_int, _vp, _c_long, _c_long,
                  _c_int, _c_float, _c_float, _vp, _c_int, _c_float, _errp]),
+    "gonngpu_gemm_f16_device": (
+        _c_int, [_vp, _c_long, _c_long, _c_long, _c_int, _vp, _c_long, _c_long, _c_long, _c_int, _vp,
+                 _c_long, _c_float, _c_float, _vp, _c_int, _c_float, _errp]),
+    "gonngpu_convert_f16_device": (_c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_int, _errp]),
     "gonngpu_column_sum": (_c_int, [_vp, _c_long, _c_long, _vp, _errp]),
     "gonngpu_alloc_device_buffer": (_c_int, [_c_long, ctypes.POINTER(_vp), _errp]),
     "gonngpu_wrap_device_memory": (_c_int, [_vp, _c_long, ctypes.POINTER(_vp), _errp]),
@@ -214,6 +218,22 @@ def optimized_gemm(a, b, c, m, n, k, alpha, beta):
     err = CError()
     _check(lib().perform_optimized_gemm(a.handle, b.handle, c.handle, m, n, k, alpha, beta, None,
                                         ctypes.byref(err)), err)
+
+
+def gemm_f16_device(a_ptr, a_shape, a_pitch, trans_a, b_ptr, b_shape, b_pitch, trans_b, c_ptr, ldc,
+                    alpha=1.0, beta=0.0, bias_ptr=None, act=ACT_NONE, act_param=0.0):
+    """Raw device pointers (ints): fp16 operands as stored, float32 result."""
+    err = CError()
+    _check(lib().gonngpu_gemm_f16_device(
+        _vp(a_ptr), a_shape[0], a_shape[1], a_pitch, int(trans_a), _vp(b_ptr), b_shape[0], b_shape[1],
+        b_pitch, int(trans_b), _vp(c_ptr), ldc, alpha, beta, _vp(bias_ptr) if bias_ptr else None, act,
+        act_param, ctypes.byref(err)), err)
+
+
+def convert_f16_device(src_ptr, rows, cols, dst_ptr, dst_pitch, mode=FP16_RN):
+    err = CError()
+    _check(lib().gonngpu_convert_f16_device(_vp(src_ptr), rows, cols, _vp(dst_ptr), dst_pitch, mode,
+                                            ctypes.byref(err)), err)
 
 
 def column_sum(inp, rows, cols, out):

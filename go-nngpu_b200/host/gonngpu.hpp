@@ -1,0 +1,504 @@
+// Host-side mirror, in C++17, of the Go API that sits above the C ABI on the
+// reference's dense path.  The reference's host code is Go (not installed on
+// the build machine), so this header restates the same types, function names,
+// argument meaning and error behaviour; a Go `error` return becomes a thrown
+// gonngpu::Error with the reference's message text, a Go `panic` becomes a
+// thrown gonngpu::Panic.
+//
+//   namespace tensor  <- tensor/tensor.go
+//   namespace mat     <- the slice of gonum's mat package the reference touches
+//   namespace matrix  <- gpu/matrix/{matrix,gonum-compat,fused-operations,
+//                        optimized-kernels,mixed-precision,layers}.go
+//
+// Header only; link with -lgonngpu_cuda.  Nothing here computes on the CPU:
+// every operation is a call into the library (and fails if it does).
+#pragma once
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/gonngpu.h"
+
+namespace gonngpu {
+
+struct Error : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+struct Panic : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+namespace detail {
+// Reads and frees a CError message (the caller owns it, as in the Go callers:
+// gpu/matrix/matrix.go:95-102).
+inline std::string take_message(CError& e) {
+  std::string s;
+  if (e.message) {
+    s = e.message;
+    free_c_error_message(e.message);
+    e.message = nullptr;
+  }
+  return s;
+}
+}  // namespace detail
+}  // namespace gonngpu
+
+namespace tensor {
+
+// tensor/tensor.go:80-87.  Shape and Data are public as in Go.  Data is the
+// host copy; after an operation wrote the tensor on the device, call
+// RetrieveCPU() before reading Data (the protocol tensor.go states; on Apple
+// silicon the reference gets away without it because the buffer aliases Data).
+class Tensor {
+ public:
+  std::vector<int> Shape;
+  std::vector<float> Data;
+
+  Tensor(std::vector<int> shape, std::vector<float> data)
+      : Shape(std::move(shape)), Data(std::move(data)) {}
+  Tensor(const Tensor&) = delete;
+  Tensor& operator=(const Tensor&) = delete;
+  ~Tensor() {
+    if (gpuPtr_) release_gpu_buffer(gpuPtr_);
+  }
+
+  // tensor.go:113-150
+  void EnsureGPU() {
+    if (isOnGPU_) return;
+    // The reference leaves the old buffer behind after RetrieveCPU (tensor.go:154-184
+    // keeps gpuPtr); here it is released so that nothing leaks, and a new buffer
+    // registers the possibly modified Data.
+    if (gpuPtr_) {
+      release_gpu_buffer(gpuPtr_);
+      gpuPtr_ = nullptr;
+    }
+    CError err{nullptr};
+    GPUPtr p = nullptr;
+    DevicePtr d = nullptr;
+    static float dummy = 0.f;
+    float* data = Data.empty() ? &dummy : Data.data();
+    const int rc = create_gpu_buffer(data, long(Data.size() * sizeof(float)), &p, &d, &err);
+    if (rc != 0)
+      throw gonngpu::Error("failed to create GPU buffer (code " + std::to_string(rc) +
+                           "): " + gonngpu::detail::take_message(err));
+    gpuPtr_ = p;
+    devicePtr_ = d;
+    isOnGPU_ = true;
+  }
+
+  // tensor.go:154-184
+  void RetrieveCPU() {
+    if (!isOnGPU_) return;
+    if (!gpuPtr_) throw gonngpu::Error("tensor is marked as on GPU but has no GPU pointer");
+    CError err{nullptr};
+    const int rc =
+        retrieve_gpu_buffer_data(gpuPtr_, Data.data(), long(Data.size() * sizeof(float)), &err);
+    if (rc != 0)
+      throw gonngpu::Error("failed to retrieve GPU buffer data (code " + std::to_string(rc) +
+                           "): " + gonngpu::detail::take_message(err));
+    isOnGPU_ = false;
+  }
+
+  // tensor.go:189-202
+  void ReleaseGPU() {
+    if (gpuPtr_) {
+      release_gpu_buffer(gpuPtr_);
+      gpuPtr_ = nullptr;
+    }
+    isOnGPU_ = false;
+  }
+
+  GPUPtr GPUPointer() const { return gpuPtr_; }        // tensor.go:206 (GPUPtr)
+  DevicePtr DevicePointer() const { return devicePtr_; }  // tensor.go:212 (DevicePtr)
+  bool IsOnGPU() const { return isOnGPU_; }
+
+ private:
+  GPUPtr gpuPtr_ = nullptr;
+  DevicePtr devicePtr_ = nullptr;
+  bool isOnGPU_ = false;
+};
+
+using TensorPtr = std::shared_ptr<Tensor>;
+
+// tensor.go:90-109
+inline TensorPtr NewTensor(std::vector<int> shape, std::vector<float> data) {
+  size_t size = 1;
+  for (int d : shape) size *= size_t(d);
+  if (data.size() != size)
+    throw gonngpu::Error("data length (" + std::to_string(data.size()) +
+                         ") does not match shape dimensions (" + std::to_string(size) + ")");
+  return std::make_shared<Tensor>(std::move(shape), std::move(data));
+}
+
+}  // namespace tensor
+
+namespace mat {
+
+// The part of gonum's mat.Matrix the reference uses
+// (gpu/matrix/gonum-compat.go:30-42: Dims and At).
+struct Matrix {
+  virtual ~Matrix() = default;
+  virtual std::pair<int, int> Dims() const = 0;
+  virtual double At(int i, int j) const = 0;
+};
+
+// Row-major float64 matrix standing in for gonum's *mat.Dense (NewDense, At,
+// Dims, RawData are what the reference touches).
+class Dense : public Matrix {
+ public:
+  Dense(int r, int c, std::vector<double> data) : r_(r), c_(c), data_(std::move(data)) {
+    if (data_.empty()) data_.assign(size_t(r) * c, 0.0);
+    if (data_.size() != size_t(r) * c) throw gonngpu::Panic("mat: bad data length");
+  }
+  std::pair<int, int> Dims() const override { return {r_, c_}; }
+  double At(int i, int j) const override {
+    if (i < 0 || i >= r_ || j < 0 || j >= c_) throw gonngpu::Panic("mat: index out of range");
+    return data_[size_t(i) * c_ + j];
+  }
+  const std::vector<double>& RawData() const { return data_; }
+
+ private:
+  int r_, c_;
+  std::vector<double> data_;
+};
+
+inline std::shared_ptr<Dense> NewDense(int r, int c, std::vector<double> data) {
+  return std::make_shared<Dense>(r, c, std::move(data));
+}
+
+}  // namespace mat
+
+namespace matrix {
+
+using tensor::TensorPtr;
+
+// ---- gpu/matrix/activation.go:18-29 -----------------------------------------
+enum ActivationType { ReLU = 0, Sigmoid, Tanh, Softmax, LeakyReLU, ELU, Swish, GELU };
+
+// ---- gpu/matrix/matrix.go ------------------------------------------------------
+
+// matrix.go:53-105
+inline TensorPtr MatMul(const TensorPtr& A, const TensorPtr& B) {
+  if (A->Shape.size() != 2 || B->Shape.size() != 2)
+    throw gonngpu::Error("MatMul requires 2D tensors (matrices)");
+  if (A->Shape[1] != B->Shape[0])
+    throw gonngpu::Error("incompatible matrix dimensions for multiplication: A columns (" +
+                         std::to_string(A->Shape[1]) + ") != B rows (" +
+                         std::to_string(B->Shape[0]) + ")");
+  const int rows = A->Shape[0], cols = B->Shape[1];
+  TensorPtr result = tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols));
+  A->EnsureGPU();
+  B->EnsureGPU();
+  result->EnsureGPU();
+  CError err{nullptr};
+  const int rc = perform_mps_matrix_multiplication(
+      A->GPUPointer(), A->Shape[0], A->Shape[1], B->GPUPointer(), B->Shape[0], B->Shape[1],
+      result->GPUPointer(), rows, cols, result->DevicePointer(), &err);
+  if (rc != 0)
+    throw gonngpu::Error("GPU matrix multiplication failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
+// matrix.go:357-404
+inline TensorPtr Transpose(const TensorPtr& A) {
+  if (A->Shape.size() != 2) throw gonngpu::Error("Transpose requires 2D tensor (matrix)");
+  const int orows = A->Shape[1], ocols = A->Shape[0];
+  TensorPtr result = tensor::NewTensor({orows, ocols}, std::vector<float>(size_t(orows) * ocols));
+  A->EnsureGPU();
+  result->EnsureGPU();
+  CError err{nullptr};
+  const int rc = perform_mps_matrix_transpose(A->GPUPointer(), A->Shape[0], A->Shape[1],
+                                              result->GPUPointer(), orows, ocols,
+                                              A->DevicePointer(), &err);
+  if (rc != 0)
+    throw gonngpu::Error("GPU matrix transpose failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
+// matrix.go:407-548: element-wise Add with the 2-D broadcast patterns the
+// bias path uses ([M,N]+[1,N], [1,N]+[M,N], [M,N]+[M,1], [M,1]+[M,N]).
+inline TensorPtr AddBroadcast(const TensorPtr& A, const TensorPtr& B) {
+  if (A->Shape.size() != 2 || B->Shape.size() != 2)
+    throw gonngpu::Error("Add requires 2D tensors (matrices)");
+  const int rows = std::max(A->Shape[0], B->Shape[0]), cols = std::max(A->Shape[1], B->Shape[1]);
+  TensorPtr result = tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols));
+  A->EnsureGPU();
+  B->EnsureGPU();
+  result->EnsureGPU();
+  CError err{nullptr};
+  const int rc = perform_mps_matrix_add_broadcast(
+      A->GPUPointer(), A->Shape[0], A->Shape[1], B->GPUPointer(), B->Shape[0], B->Shape[1],
+      result->GPUPointer(), rows, cols, A->DevicePointer(), &err);
+  if (rc != 0)
+    throw gonngpu::Error("GPU matrix addition with broadcasting failed (code " +
+                         std::to_string(rc) + "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
+// ---- gpu/matrix/optimized-kernels.go:21-75 ----------------------------------------
+inline TensorPtr OptimizedGEMM(const TensorPtr& A, const TensorPtr& B, float alpha, float beta) {
+  if (A->Shape.size() != 2 || B->Shape.size() != 2)
+    throw gonngpu::Error("optimized GEMM requires 2D tensors");
+  const int M = A->Shape[0], K = A->Shape[1], K2 = B->Shape[0], N = B->Shape[1];
+  if (K != K2)
+    throw gonngpu::Error("matrix dimensions don't match: A(" + std::to_string(M) + "x" +
+                         std::to_string(K) + ") x B(" + std::to_string(K2) + "x" +
+                         std::to_string(N) + ")");
+  TensorPtr out = tensor::NewTensor({M, N}, std::vector<float>(size_t(M) * N));  // zeros, as in Go
+  A->EnsureGPU();
+  B->EnsureGPU();
+  out->EnsureGPU();
+  CError err{nullptr};
+  const int rc = perform_optimized_gemm(A->GPUPointer(), B->GPUPointer(), out->GPUPointer(), M, N,
+                                        K, alpha, beta, A->DevicePointer(), &err);
+  if (rc != 0)
+    throw gonngpu::Error("optimized GEMM failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return out;
+}
+
+// ---- gpu/matrix/fused-operations.go ------------------------------------------------
+struct FusedActivationConfig {  // fused-operations.go:24-28
+  ActivationType Type = ReLU;
+  float Alpha = 0.f;
+};
+struct FusedLinearConfig {  // fused-operations.go:49-54
+  bool Bias = false;
+  const FusedActivationConfig* Activation = nullptr;
+};
+
+// The Go caller hands its ActivationType enum straight to the native entry
+// (fused-operations.go:433-439), whose kernel decodes a different numbering
+// (default.metal:488-506); only ReLU agrees.  Callers of this mirror get the
+// activation they named: the enum is translated to the native code here.
+// Softmax, ELU and Swish have no fused native code.
+inline int native_activation_code(ActivationType t) {
+  switch (t) {
+    case ReLU: return 0;
+    case LeakyReLU: return 1;
+    case Sigmoid: return 2;
+    case Tanh: return 3;
+    case GELU: return 4;
+    default: throw gonngpu::Error("activation has no fused linear kernel");
+  }
+}
+
+// fused-operations.go:380-465 (FusedLinearActivation.Forward) and :1468-1520
+// (GradFusedLinearActivation, forward part).  inputs = {X[B,in], W[in,out], bias[out]?}.
+// A nil Activation means ReLU, as in the reference (:433).
+inline TensorPtr FusedLinearActivationForward(const std::vector<TensorPtr>& inputs,
+                                              const FusedLinearConfig& config) {
+  if (inputs.size() < 2)
+    throw gonngpu::Error("FusedLinearActivation requires at least input and weight tensors");
+  const TensorPtr& X = inputs[0];
+  const TensorPtr& W = inputs[1];
+  TensorPtr bias = (inputs.size() >= 3 && config.Bias) ? inputs[2] : nullptr;
+  if (X->Shape.size() != 2 || W->Shape.size() != 2 || X->Shape[1] != W->Shape[0])
+    throw gonngpu::Error("FusedLinearActivation: input and weight shapes do not match");
+  const int batch = X->Shape[0], in = X->Shape[1], out = W->Shape[1];
+  X->EnsureGPU();
+  W->EnsureGPU();
+  if (bias) bias->EnsureGPU();
+  TensorPtr Y = tensor::NewTensor({batch, out}, std::vector<float>(size_t(batch) * out));
+  Y->EnsureGPU();
+  int code = 0;
+  float alpha = 0.f;
+  if (config.Activation) {
+    code = native_activation_code(config.Activation->Type);
+    alpha = config.Activation->Alpha;
+  }
+  CError err{nullptr};
+  const int rc = perform_fused_linear_activation(
+      X->GPUPointer(), batch, in, W->GPUPointer(), out, bias ? bias->GPUPointer() : nullptr, code,
+      alpha, Y->GPUPointer(), X->DevicePointer(), &err);
+  if (rc != 0)
+    throw gonngpu::Error("fused linear+activation failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return Y;
+}
+
+// Backward GEMMs of a linear layer (layers.go:77-96, gradient.go:601-637):
+// dW = X^T . dY and dX = dY . W^T.  The reference materialises the transposes;
+// here the GEMM reads the operands transposed in place.
+inline TensorPtr MatMulTransposed(const TensorPtr& A, bool transA, const TensorPtr& B, bool transB) {
+  if (A->Shape.size() != 2 || B->Shape.size() != 2)
+    throw gonngpu::Error("MatMul requires 2D tensors (matrices)");
+  const int M = transA ? A->Shape[1] : A->Shape[0], K = transA ? A->Shape[0] : A->Shape[1];
+  const int Kb = transB ? B->Shape[1] : B->Shape[0], N = transB ? B->Shape[0] : B->Shape[1];
+  if (K != Kb)
+    throw gonngpu::Error("incompatible matrix dimensions for multiplication: A columns (" +
+                         std::to_string(K) + ") != B rows (" + std::to_string(Kb) + ")");
+  TensorPtr result = tensor::NewTensor({M, N}, std::vector<float>(size_t(M) * N));
+  A->EnsureGPU();
+  B->EnsureGPU();
+  result->EnsureGPU();
+  CError err{nullptr};
+  const int rc = gonngpu_matmul_ex(A->GPUPointer(), A->Shape[0], A->Shape[1], transA,
+                                   B->GPUPointer(), B->Shape[0], B->Shape[1], transB,
+                                   result->GPUPointer(), M, N, GONNGPU_FP32_3XTF32, 1.f, 0.f,
+                                   nullptr, GONNGPU_ACT_NONE, 0.f, &err);
+  if (rc != 0)
+    throw gonngpu::Error("GPU matrix multiplication failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
+// ---- gpu/matrix/mixed-precision.go ---------------------------------------------------
+using FloatMP16 = uint16_t;
+
+// mixed-precision.go:315-358 (ForwardFloat16): fp16-precision inputs, fp32
+// accumulate, fp32 result, optional bias.  The reference converts on the host
+// (ConvertTensorToFloat16, :192-210, truncating) and multiplies in fp32; here
+// the same truncation runs on the device and the product runs on fp16 tensor
+// cores, which is the same arithmetic: fp16-representable inputs, fp32 sums.
+inline TensorPtr ForwardFloat16(const TensorPtr& input, const TensorPtr& weights,
+                                const TensorPtr& bias = nullptr, bool round_to_nearest = false) {
+  if (input->Shape.size() != 2 || weights->Shape.size() != 2)
+    throw gonngpu::Error("MatMul requires 2D tensors (matrices)");
+  if (input->Shape[1] != weights->Shape[0])
+    throw gonngpu::Error("incompatible matrix dimensions for multiplication: A columns (" +
+                         std::to_string(input->Shape[1]) + ") != B rows (" +
+                         std::to_string(weights->Shape[0]) + ")");
+  const int M = input->Shape[0], N = weights->Shape[1];
+  TensorPtr result = tensor::NewTensor({M, N}, std::vector<float>(size_t(M) * N));
+  input->EnsureGPU();
+  weights->EnsureGPU();
+  if (bias) bias->EnsureGPU();
+  result->EnsureGPU();
+  CError err{nullptr};
+  const int rc = gonngpu_matmul_ex(
+      input->GPUPointer(), input->Shape[0], input->Shape[1], 0, weights->GPUPointer(),
+      weights->Shape[0], weights->Shape[1], 0, result->GPUPointer(), M, N,
+      round_to_nearest ? GONNGPU_FP16_RN : GONNGPU_FP16_TRUNC, 1.f, 0.f,
+      bias ? bias->GPUPointer() : nullptr, GONNGPU_ACT_NONE, 0.f, &err);
+  if (rc != 0)
+    throw gonngpu::Error("GPU matrix multiplication failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
+// ---- gpu/matrix/gonum-compat.go ---------------------------------------------------------
+class GPUDense : public mat::Matrix {
+ public:
+  explicit GPUDense(TensorPtr t) : tensor_(std::move(t)) {}  // NewGPUDenseFromTensor (:825-827)
+
+  std::pair<int, int> Dims() const override { return {tensor_->Shape[0], tensor_->Shape[1]}; }  // :45-47
+
+  double At(int i, int j) const override {  // :49-59
+    tensor_->RetrieveCPU();
+    const auto [rows, cols] = Dims();
+    if (i < 0 || i >= rows || j < 0 || j >= cols) throw gonngpu::Panic("matrix index out of range");
+    return double(tensor_->Data[size_t(i) * cols + j]);
+  }
+
+  std::shared_ptr<GPUDense> T() const {  // :61-68
+    try {
+      return std::make_shared<GPUDense>(Transpose(tensor_));
+    } catch (const gonngpu::Error& e) {
+      throw gonngpu::Panic(e.what());
+    }
+  }
+
+  void Set(int i, int j, double v) {  // :71-80
+    tensor_->RetrieveCPU();
+    const auto [rows, cols] = Dims();
+    if (i < 0 || i >= rows || j < 0 || j >= cols) throw gonngpu::Panic("matrix index out of range");
+    tensor_->Data[size_t(i) * cols + j] = float(v);
+  }
+
+  void Mul(const mat::Matrix& a, const mat::Matrix& b);  // :83-110
+
+  std::shared_ptr<mat::Dense> ToGonum() const {  // :322-334
+    tensor_->RetrieveCPU();
+    const auto [rows, cols] = Dims();
+    std::vector<double> d(tensor_->Data.begin(), tensor_->Data.end());
+    return mat::NewDense(rows, cols, std::move(d));
+  }
+
+  void ReleaseGPU() { tensor_->ReleaseGPU(); }       // :337-339
+  TensorPtr GetTensor() const { return tensor_; }    // :820-822
+
+ private:
+  mutable TensorPtr tensor_;
+};
+
+// gonum-compat.go:14-27
+inline std::shared_ptr<GPUDense> NewGPUDense(int rows, int cols, const std::vector<double>& data) {
+  std::vector<float> f(data.begin(), data.end());
+  try {
+    return std::make_shared<GPUDense>(tensor::NewTensor({rows, cols}, std::move(f)));
+  } catch (const gonngpu::Error& e) {
+    throw gonngpu::Panic(e.what());
+  }
+}
+
+// gonum-compat.go:30-42
+inline std::shared_ptr<GPUDense> FromGonum(const mat::Matrix& m) {
+  const auto [rows, cols] = m.Dims();
+  std::vector<double> data(size_t(rows) * cols);
+  for (int i = 0; i < rows; ++i)
+    for (int j = 0; j < cols; ++j) data[size_t(i) * cols + j] = m.At(i, j);
+  return NewGPUDense(rows, cols, data);
+}
+
+inline void GPUDense::Mul(const mat::Matrix& a, const mat::Matrix& b) {
+  std::shared_ptr<GPUDense> keepA, keepB;
+  TensorPtr ta, tb;
+  if (auto* ga = dynamic_cast<const GPUDense*>(&a)) {
+    ta = ga->tensor_;
+  } else {
+    keepA = FromGonum(a);
+    ta = keepA->tensor_;
+  }
+  if (auto* gb = dynamic_cast<const GPUDense*>(&b)) {
+    tb = gb->tensor_;
+  } else {
+    keepB = FromGonum(b);
+    tb = keepB->tensor_;
+  }
+  TensorPtr result;
+  try {
+    result = MatMul(ta, tb);
+  } catch (const gonngpu::Error& e) {
+    throw gonngpu::Panic(e.what());
+  }
+  tensor_->ReleaseGPU();
+  tensor_ = result;
+}
+
+// gonum-compat.go:342-367
+inline std::shared_ptr<mat::Dense> GPUMatMul(const mat::Matrix& a, const mat::Matrix& b) {
+  auto ga = FromGonum(a);
+  auto gb = FromGonum(b);
+  TensorPtr result;
+  try {
+    result = MatMul(ga->GetTensor(), gb->GetTensor());
+    result->RetrieveCPU();
+  } catch (const gonngpu::Error& e) {
+    throw gonngpu::Panic(e.what());
+  }
+  std::vector<double> d(result->Data.begin(), result->Data.end());
+  auto out = mat::NewDense(result->Shape[0], result->Shape[1], std::move(d));
+  result->ReleaseGPU();
+  ga->ReleaseGPU();
+  gb->ReleaseGPU();
+  return out;
+}
+
+// gonum-compat.go:744-752
+inline std::vector<std::shared_ptr<mat::Dense>> BatchGPUMatMul(
+    const std::vector<std::pair<const mat::Matrix*, const mat::Matrix*>>& operations) {
+  std::vector<std::shared_ptr<mat::Dense>> results;
+  results.reserve(operations.size());
+  for (const auto& op : operations) results.push_back(GPUMatMul(*op.first, *op.second));
+  return results;
+}
+
+}  // namespace matrix

@@ -147,6 +147,23 @@ GONNGPU_API int gonngpu_matmul_ex(GPUPtr a, long aRows, long aCols, int transA, 
                       float alpha, float beta, GPUPtr bias, int activation_type,
                       float activation_param, CError *err);
 
+/* The same GEMM on device-resident fp16 operands, for callers that keep their
+ * matrices in HBM as IEEE fp16 (what the reference's ForwardFloat16 simulates
+ * with fp16-valued float32).  `a` and `b` are device pointers to the matrices
+ * as stored ([rows, cols], pitch in elements); both pointers must be 16-byte
+ * aligned and both pitches multiples of 8.  `c` is float32 [M,N] with leading
+ * dimension ldc; `bias` (float32[N]) may be NULL.  All pointers belong to the
+ * current device.  Errors: -1 device, -2 NULL pointer, -3 dimensions or
+ * alignment, -4 kernel set-up, -6 execution. */
+GONNGPU_API int gonngpu_gemm_f16_device(const void *a, long aRows, long aCols, long aPitch, int transA,
+                            const void *b, long bRows, long bCols, long bPitch, int transB,
+                            float *c, long ldc, float alpha, float beta, const float *bias,
+                            int activation_type, float activation_param, CError *err);
+/* float32 [rows, cols] (dense) -> fp16 [rows, dstPitch] on the device; mode is
+ * GONNGPU_FP16_RN or GONNGPU_FP16_TRUNC. */
+GONNGPU_API int gonngpu_convert_f16_device(const float *src, long rows, long cols, void *dst, long dstPitch,
+                               int mode, CError *err);
+
 /* out[j] = sum_i in[i,j] (bias gradient, gpu/matrix/layers.go:281-294). */
 GONNGPU_API int gonngpu_column_sum(GPUPtr in, long rows, long cols, GPUPtr out, CError *err);
 
