@@ -32,14 +32,7 @@ WORKLOAD = "row-sharded GEMM fp16-in/fp32-acc M=131072 K=4096 N=4096 (A rows spl
 METRIC = "GEMM TFLOP/s"
 
 
-def shard_rows(m_total, world, rank, align=128):
-    """Contiguous row block of rank `rank`: blocks are multiples of `align`
-    (the GEMM's tile height) except possibly the last."""
-    per = -(-m_total // world)
-    per = -(-per // align) * align
-    lo = min(rank * per, m_total)
-    hi = min(lo + per, m_total)
-    return lo, hi
+from sharding import shard_rows  # go-nngpu_b200/sharding.py  # noqa: E402
 
 
 def load_peaks():
