@@ -58,6 +58,8 @@ SIGNATURES = {
         _c_int, [_vp, _c_long, _c_long, _c_long, _c_int, _vp, _c_long, _c_long, _c_long, _c_int, _vp,
                  _c_long, _c_float, _c_float, _vp, _c_int, _c_float, _errp]),
     "gonngpu_convert_f16_device": (_c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_int, _errp]),
+    "gonngpu_matmul_f16_static_scratch": (
+        _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _vp, _errp]),
     "gonngpu_column_sum": (_c_int, [_vp, _c_long, _c_long, _vp, _errp]),
     "gonngpu_alloc_device_buffer": (_c_int, [_c_long, ctypes.POINTER(_vp), _errp]),
     "gonngpu_wrap_device_memory": (_c_int, [_vp, _c_long, ctypes.POINTER(_vp), _errp]),
@@ -234,6 +236,14 @@ def convert_f16_device(src_ptr, rows, cols, dst_ptr, dst_pitch, mode=FP16_RN):
     err = CError()
     _check(lib().gonngpu_convert_f16_device(_vp(src_ptr), rows, cols, _vp(dst_ptr), dst_pitch, mode,
                                             ctypes.byref(err)), err)
+
+
+def matmul_f16_static_scratch(a_ptr, a_shape, b_ptr, b_shape, c_ptr, stream=None):
+    """float32 device pointers in, float32 device pointer out; allocates nothing."""
+    err = CError()
+    _check(lib().gonngpu_matmul_f16_static_scratch(
+        _vp(a_ptr), a_shape[0], a_shape[1], _vp(b_ptr), b_shape[0], b_shape[1], _vp(c_ptr),
+        _vp(stream) if stream else None, ctypes.byref(err)), err)
 
 
 def column_sum(inp, rows, cols, out):

@@ -164,6 +164,25 @@ GONNGPU_API int gonngpu_gemm_f16_device(const void *a, long aRows, long aCols, l
 GONNGPU_API int gonngpu_convert_f16_device(const float *src, long rows, long cols, void *dst, long dstPitch,
                                int mode, CError *err);
 
+/* No counterpart in the reference.  C[M,N] = A[M,K] . B[K,N] on the fp16 path
+ * (inputs rounded to fp16, fp32 accumulate, as GONNGPU_FP16_RN) for callers
+ * that must not allocate: programs that gave all of HBM to their own arena at
+ * start-up, or that call from a loop where a cudaMalloc / cudaFree would stall
+ * the whole device.  a, b, c are float32 DEVICE pointers of the current device
+ * (row-major, dense); nothing is allocated or freed: the fp16 operand planes
+ * live in a fixed array inside the library, GONNGPU_STATIC_SCRATCH_BYTES of HBM
+ * on every GPU that loads it.  Operands whose planes (rows x columns padded to
+ * 64, 2 bytes each, A and B together) exceed that are refused with -3.
+ * `stream` is the cudaStream_t to run on (NULL: the default stream); the call
+ * returns after the work finished.  The first call on a device looks up the
+ * array's address: make it before any stream capture.  All calls share the
+ * array, so calls that overlap on the GPU race; serialise them.
+ * Errors: -1 device, -2 NULL pointer, -3 dimensions or size, -4 kernel set-up,
+ * -6 execution. */
+#define GONNGPU_STATIC_SCRATCH_BYTES (32l << 20)
+GONNGPU_API int gonngpu_matmul_f16_static_scratch(const float *a, long aRows, long aCols, const float *b,
+                                      long bRows, long bCols, float *c, void *stream, CError *err);
+
 /* out[j] = sum_i in[i,j] (bias gradient, gpu/matrix/layers.go:281-294). */
 GONNGPU_API int gonngpu_column_sum(GPUPtr in, long rows, long cols, GPUPtr out, CError *err);
 
