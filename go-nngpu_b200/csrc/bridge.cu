@@ -929,6 +929,13 @@ int gonngpu_set_gemm_tuning(int block_n, int max_ctas) {
   return 0;
 }
 
+int gonngpu_set_gemm_pair_mode(int mode) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (mode < -1 || mode > 2) return -1;
+  g_tune.pair = mode;
+  return 0;
+}
+
 void gonngpu_get_stats(long out[8]) {
   std::lock_guard<std::recursive_mutex> lk(g_mu);
   for (int i = 0; i < 8; ++i) out[i] = g_stats[i];

@@ -19,6 +19,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -58,6 +59,7 @@ struct KernelParams {
   float alpha, beta, act_param;
   int act;
   uint32_t vec_store;  // C base and pitch allow 16-byte stores
+  uint32_t tma_store;  // epilogue may write C with TMA stores (no beta term, aligned C)
   GemmStatus* status;
 };
 
@@ -374,6 +376,631 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// fp16 kernel for large problems: CTA pairs (cta_group::2).
+//
+// A cluster of two CTAs computes a 256 x BLOCK_N tile.  CTA r of the pair
+// stages rows [128r, 128r+128) of the A tile and columns [r*BLOCK_N/2, ..) of
+// the B tile in its own shared memory; the leader (rank 0) issues one
+// tcgen05.mma.cta_group::2 with M=256 that reads both CTAs' shared memory and
+// writes 128 rows of D into each CTA's TMEM.  Per CTA this halves the B bytes
+// that cross L2 -> SM and that are written to and read from shared memory,
+// which is what limits the single-CTA kernel.  No multicast loads are used.
+//
+// Barriers (same offsets in both CTAs):
+//   full[s]   leader only: 1 arrival (leader's producer, expecting both CTAs'
+//             bytes) + the bytes of both CTAs' TMA loads
+//   empty[s]  per CTA: tcgen05.commit from the leader, multicast to both
+//   tfull[a]  per CTA: multicast commit when the tile's last MMA retired
+//   tempty[a] leader only: 8 arrivals = 4 epilogue warps of each CTA
+//
+// A stage holds SUB k blocks (each laid out as A tile then B half tile); one
+// barrier round (full wait, commit) therefore covers 4*SUB MMAs.
+template <int BLOCK_N, int STAGES, int SUB>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
+                     const __grid_constant__ CUtensorMap tm_b,
+                     const __grid_constant__ KernelParams p) {
+  constexpr uint32_t B_TILE_BYTES = (BLOCK_N / 2) * SLAB_ROW_BYTES;  // this CTA's half
+  constexpr uint32_t SUB_BYTES = A_TILE_BYTES + B_TILE_BYTES;        // one k block
+  constexpr uint32_t STAGE_BYTES = SUB * SUB_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512 && TMEM_COLS >= 32, "TMEM");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t cta_rank = ptx::cluster_ctarank();
+  const bool leader = (cta_rank == 0);
+  const uint32_t pair = blockIdx.x >> 1;
+  const uint32_t num_pairs = gridDim.x >> 1;
+  const uint32_t rounds = (p.num_kblocks + SUB - 1) / SUB;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 8);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&tm_a);
+    ptx::prefetch_tmap(&tm_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();  // the peer's barriers and TMEM exist before anyone signals them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    uint32_t stage = 0, phase = 0;
+    bool alive = true;
+    for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs) {
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+      const int32_t a_tile = int32_t(tm * 2 + cta_rank);  // in units of 128 rows
+      const int32_t b_tile = int32_t(tn * 2 + cta_rank);  // in units of BLOCK_N/2 columns
+      for (uint32_t rd = 0; rd < rounds; ++rd) {
+        bool ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 1, stage, t, rd);
+          }
+          alive = false;
+          break;
+        }
+        if (lane == 0) {
+          if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+          const uint32_t fb = ptx::mapa_shared(full_bar(stage), 0);  // the leader's barrier
+#pragma unroll
+          for (uint32_t j = 0; j < SUB; ++j) {
+            // k blocks past the end of K are fetched too: TMA fills them with zeros
+            const int32_t kb = int32_t(rd * SUB + j);
+            uint32_t dst = smem_base + stage * STAGE_BYTES + j * SUB_BYTES;
+            for (uint32_t sl = 0; sl < p.a.slabs; ++sl) {
+              ptx::tma_load_2d_pair(dst + sl * p.a.slab_bytes, &tm_a,
+                                    a_tile * p.a.c0_tile + int32_t(sl) * p.a.c0_slab + kb * p.a.c0_k,
+                                    a_tile * p.a.c1_tile + kb * p.a.c1_k, fb);
+            }
+            dst += A_TILE_BYTES;
+            for (uint32_t sl = 0; sl < p.b.slabs; ++sl) {
+              ptx::tma_load_2d_pair(dst + sl * p.b.slab_bytes, &tm_b,
+                                    b_tile * p.b.c0_tile + int32_t(sl) * p.b.c0_slab + kb * p.b.c0_k,
+                                    b_tile * p.b.c1_tile + kb * p.b.c1_k, fb);
+            }
+          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (leader CTA only)
+    // One thread runs the loop: the next stage's barrier is tested (without
+    // blocking) before this round's MMAs are issued and only waited on when
+    // that test failed; descriptors advance by 32-bit adds on their low words.
+    if (leader && lane == 0) {
+      const uint32_t a_hi = uint32_t(p.a.desc >> 32), b_hi = uint32_t(p.b.desc >> 32);
+      const uint32_t a_lo0 = uint32_t(p.a.desc), b_lo0 = uint32_t(p.b.desc);
+      const uint32_t a_step = p.a.kstep_bytes >> 4, b_step = p.b.kstep_bytes >> 4;
+      uint32_t stage = 0, phase = 0;
+      uint32_t local = 0;
+      uint32_t ready = 0;
+      bool alive = true;
+      for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs, ++local) {
+        const uint32_t acc = local & 1u;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          *abort_flag = 1;
+          report(p.status, 2, 0x100u | acc, t, 0);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        for (uint32_t rd = 0; rd < rounds; ++rd) {
+          if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
+            *abort_flag = 1;
+            report(p.status, 2, stage, t, rd);
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
+          const uint32_t next_phase = (stage + 1 == STAGES) ? phase ^ 1u : phase;
+          const uint32_t ready_next = ptx::mbar_test_wait(full_bar(next_stage), next_phase);
+#pragma unroll
+          for (uint32_t j = 0; j < SUB; ++j) {
+            const uint32_t a_addr = smem_base + stage * STAGE_BYTES + j * SUB_BYTES;
+            const uint32_t a_lo = a_lo0 + (a_addr >> 4);
+            const uint32_t b_lo = b_lo0 + ((a_addr + A_TILE_BYTES) >> 4);
+#pragma unroll
+            for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+              ptx::mma_f16_pair_lohi(d_tmem, a_lo + ks * a_step, a_hi, b_lo + ks * b_step, b_hi,
+                                     p.idesc, (rd | j | ks) ? 1u : 0u);
+            }
+          }
+          ptx::mma_commit_pair(empty_bar(stage), 3);
+          if (rd + 1 == rounds) ptx::mma_commit_pair(tfull_bar(acc), 3);
+          stage = next_stage;
+          phase = next_phase;
+          ready = ready_next;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const uint32_t quarter = warp & 3u;
+    uint32_t local = 0;
+    for (uint32_t t = pair; t < p.num_tiles; t += num_pairs, ++local) {
+      const uint32_t acc = local & 1u;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+      bool ok = ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          report(p.status, 3, acc, t, 0);
+        }
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t row = (tm * 2 + cta_rank) * BLOCK_M + quarter * 32u + lane;
+      const uint32_t col_tile = tn * BLOCK_N;
+      const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * BLOCK_N;
+      float* c_row = p.C + uint64_t(row) * p.ldc;
+      const float* cin_row = p.c_in ? p.c_in + uint64_t(row) * p.ldc : nullptr;
+#pragma unroll 1
+      for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
+        const uint32_t col0 = col_tile + ch * 32u;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + ch * 32u, r);
+        ptx::tmem_ld_wait();
+        if (row < p.M) {
+          if (col0 + 32u <= p.N && p.vec_store) {
+#pragma unroll
+            for (uint32_t j = 0; j < 32; j += 4) {
+              float4 v;
+              v.x = __uint_as_float(r[j + 0]) * p.alpha;
+              v.y = __uint_as_float(r[j + 1]) * p.alpha;
+              v.z = __uint_as_float(r[j + 2]) * p.alpha;
+              v.w = __uint_as_float(r[j + 3]) * p.alpha;
+              if (cin_row) {
+                const float4 o = *reinterpret_cast<const float4*>(cin_row + col0 + j);
+                v.x += p.beta * o.x;
+                v.y += p.beta * o.y;
+                v.z += p.beta * o.z;
+                v.w += p.beta * o.w;
+              }
+              if (p.bias) {
+                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+                v.x += b.x;
+                v.y += b.y;
+                v.z += b.z;
+                v.w += b.w;
+              }
+              if (p.act >= 0) {
+                v.x = apply_act(v.x, p.act, p.act_param);
+                v.y = apply_act(v.y, p.act, p.act_param);
+                v.z = apply_act(v.z, p.act, p.act_param);
+                v.w = apply_act(v.w, p.act, p.act_param);
+              }
+              *reinterpret_cast<float4*>(c_row + col0 + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (uint32_t j = 0; j < 32; ++j) {
+              const uint32_t col = col0 + j;
+              if (col < p.N) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (cin_row) v += p.beta * cin_row[col];
+                if (p.bias) v += p.bias[col];
+                if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
+                c_row[col] = v;
+              }
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(acc), 0));
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
+      if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
+      __nanosleep(1000);
+    }
+    __syncthreads();
+  }
+  // Neither CTA may leave while the other can still signal its barriers or the
+  // pair's MMAs can still touch its shared memory and TMEM.
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+// One thread's 32 consecutive accumulator columns of one output row:
+// alpha/beta/bias/activation, then 16-byte stores (scalar at ragged edges).
+__device__ __forceinline__ void epilogue_store32(const KernelParams& p, const uint32_t (&r)[32],
+                                                 uint32_t row, uint32_t col0) {
+  if (row >= p.M || col0 >= p.N) return;
+  float* c_row = p.C + uint64_t(row) * p.ldc;
+  const float* cin_row = p.c_in ? p.c_in + uint64_t(row) * p.ldc : nullptr;
+  if (col0 + 32u <= p.N && p.vec_store) {
+#pragma unroll
+    for (uint32_t j = 0; j < 32; j += 4) {
+      float4 v;
+      v.x = __uint_as_float(r[j + 0]) * p.alpha;
+      v.y = __uint_as_float(r[j + 1]) * p.alpha;
+      v.z = __uint_as_float(r[j + 2]) * p.alpha;
+      v.w = __uint_as_float(r[j + 3]) * p.alpha;
+      if (cin_row) {
+        const float4 o = *reinterpret_cast<const float4*>(cin_row + col0 + j);
+        v.x += p.beta * o.x;
+        v.y += p.beta * o.y;
+        v.z += p.beta * o.z;
+        v.w += p.beta * o.w;
+      }
+      if (p.bias) {
+        const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+        v.x += b.x;
+        v.y += b.y;
+        v.z += b.z;
+        v.w += b.w;
+      }
+      if (p.act >= 0) {
+        v.x = apply_act(v.x, p.act, p.act_param);
+        v.y = apply_act(v.y, p.act, p.act_param);
+        v.z = apply_act(v.z, p.act, p.act_param);
+        v.w = apply_act(v.w, p.act, p.act_param);
+      }
+      *reinterpret_cast<float4*>(c_row + col0 + j) = v;
+    }
+  } else {
+#pragma unroll
+    for (uint32_t j = 0; j < 32; ++j) {
+      const uint32_t col = col0 + j;
+      if (col < p.N) {
+        float v = __uint_as_float(r[j]) * p.alpha;
+        if (cin_row) v += p.beta * cin_row[col];
+        if (p.bias) v += p.bias[col];
+        if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
+        c_row[col] = v;
+      }
+    }
+  }
+}
+
+// Same values, but written to a 32-row x 128-byte staging tile in shared memory
+// (rows = this warp's 32 output rows) in the 128-byte-swizzle order a TMA store
+// expects, so that the store to C moves whole 128-byte lines.  No beta term.
+__device__ __forceinline__ void epilogue_stage32(const KernelParams& p, const uint32_t (&r)[32],
+                                                 uint32_t col0, uint32_t staging, uint32_t lane) {
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j) {
+    float v[4];
+#pragma unroll
+    for (uint32_t e = 0; e < 4; ++e) {
+      const uint32_t col = col0 + j * 4 + e;
+      float x = __uint_as_float(r[j * 4 + e]) * p.alpha;
+      if (p.bias && col < p.N) x += __ldg(p.bias + col);
+      if (p.act >= 0) x = apply_act(x, p.act, p.act_param);
+      v[e] = x;
+    }
+    const uint32_t addr = staging + lane * 128u + ((j ^ (lane & 7u)) << 4);
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[0]), "f"(v[1]),
+                 "f"(v[2]), "f"(v[3]) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// fp16 kernel for the largest problems: CTA pairs on 512 x 256 tiles.
+//
+// Measured on B200: TMA loads deliver at most ~46 bytes per clock per SM from
+// L2 however many stages are in flight, and the 256 x 256 pair tile needs 64
+// per clock at full tensor rate, so that kernel tops out near 70 % of the
+// pipe.  Here each CTA of the pair carries TWO 128-row A sub-tiles against the
+// same B half tile: 48 KB per k block feed 8 MMAs (1024 cycles), 48 bytes per
+// clock.  The two 256-column accumulators fill TMEM, so they cannot be double
+// buffered; instead sub-tile 0 is committed and drained first, and the next
+// tile's sub-tile-0 MMAs start while sub-tile 1 is still draining.
+//
+// Barriers: full[s] (leader), empty[s] (both), tfull[u] (both, u = sub-tile),
+// tempty[u] (leader, 8 arrivals = 4 epilogue warps of each CTA).
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
+                        const __grid_constant__ CUtensorMap tm_b,
+                        const __grid_constant__ CUtensorMap tm_c,
+                        const __grid_constant__ KernelParams p) {
+  constexpr uint32_t BN = 256;
+  constexpr uint32_t B_TILE_BYTES = (BN / 2) * SLAB_ROW_BYTES;
+  constexpr uint32_t STAGE_BYTES = 2 * A_TILE_BYTES + B_TILE_BYTES;  // A0, A1, B half
+  constexpr uint32_t TMEM_COLS = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 B), 1024-byte aligned
+  const uint32_t staging_base = bar_base + 1024u;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t cta_rank = ptx::cluster_ctarank();
+  const bool leader = (cta_rank == 0);
+  const uint32_t pair = blockIdx.x >> 1;
+  const uint32_t num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 8);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&tm_a);
+    ptx::prefetch_tmap(&tm_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    uint32_t stage = 0, phase = 0;
+    bool alive = true;
+    for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs) {
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+      const int32_t b_tile = int32_t(tn * 2 + cta_rank);  // units of 128 columns
+      for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
+        bool ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 1, stage, t, kb);
+          }
+          alive = false;
+          break;
+        }
+        if (lane == 0) {
+          if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+          const uint32_t fb = ptx::mapa_shared(full_bar(stage), 0);
+          uint32_t dst = smem_base + stage * STAGE_BYTES;
+#pragma unroll
+          for (uint32_t u = 0; u < 2; ++u) {
+            const int32_t a_tile = int32_t(tm * 4 + u * 2 + cta_rank);  // units of 128 rows
+            for (uint32_t sl = 0; sl < p.a.slabs; ++sl) {
+              ptx::tma_load_2d_pair(dst + sl * p.a.slab_bytes, &tm_a,
+                                    a_tile * p.a.c0_tile + int32_t(sl) * p.a.c0_slab +
+                                        int32_t(kb) * p.a.c0_k,
+                                    a_tile * p.a.c1_tile + int32_t(kb) * p.a.c1_k, fb);
+            }
+            dst += A_TILE_BYTES;
+          }
+          for (uint32_t sl = 0; sl < p.b.slabs; ++sl) {
+            ptx::tma_load_2d_pair(dst + sl * p.b.slab_bytes, &tm_b,
+                                  b_tile * p.b.c0_tile + int32_t(sl) * p.b.c0_slab +
+                                      int32_t(kb) * p.b.c0_k,
+                                  b_tile * p.b.c1_tile + int32_t(kb) * p.b.c1_k, fb);
+          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  }
+  else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (leader CTA only)
+    // One thread runs the whole loop.  Issuing a tcgen05.mma is not free (about
+    // 90 cycles each, measured), so everything else in a round has to fit in
+    // the ~300 cycles that 8 MMAs of 128 cycles leave: the next stage's barrier
+    // is peeked at with a non-blocking test BEFORE this round's MMAs are issued
+    // and only waited on if that test failed; descriptors are advanced with
+    // 32-bit adds on their low words.
+    if (leader && lane == 0) {
+      const uint32_t a_hi = uint32_t(p.a.desc >> 32), b_hi = uint32_t(p.b.desc >> 32);
+      const uint32_t a_lo0 = uint32_t(p.a.desc), b_lo0 = uint32_t(p.b.desc);
+      const uint32_t a_step = p.a.kstep_bytes >> 4, b_step = p.b.kstep_bytes >> 4;
+      uint32_t stage = 0, phase = 0;
+      uint32_t local = 0;
+      bool alive = true;
+      uint32_t ready = 0;
+      for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs, ++local) {
+        const uint32_t tparity = local & 1u;
+        for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
+          if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
+            *abort_flag = 1;
+            report(p.status, 2, stage, t, kb);
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
+          const uint32_t next_phase = (stage + 1 == STAGES) ? phase ^ 1u : phase;
+          const uint32_t ready_next = ptx::mbar_test_wait(full_bar(next_stage), next_phase);
+          const uint32_t stage_addr = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_lo = b_lo0 + ((stage_addr + 2 * A_TILE_BYTES) >> 4);
+#pragma unroll
+          for (uint32_t u = 0; u < 2; ++u) {
+            if (kb == 0) {
+              // accumulator u must have been drained of the previous tile
+              if (!ptx::mbar_wait(tempty_bar(u), tparity ^ 1u, abort_flag)) {
+                *abort_flag = 1;
+                report(p.status, 2, 0x100u | u, t, 0);
+                alive = false;
+                break;
+              }
+              ptx::tc_fence_after();
+            }
+            const uint32_t a_lo = a_lo0 + ((stage_addr + u * A_TILE_BYTES) >> 4);
+            const uint32_t d_tmem = tmem_base + u * BN;
+#pragma unroll
+            for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+              ptx::mma_f16_pair_lohi(d_tmem, a_lo + ks * a_step, a_hi, b_lo + ks * b_step, b_hi,
+                                     p.idesc, (kb | ks) ? 1u : 0u);
+            }
+            if (kb + 1 == p.num_kblocks) ptx::mma_commit_pair(tfull_bar(u), 3);
+          }
+          if (!alive) break;
+          ptx::mma_commit_pair(empty_bar(stage), 3);
+          stage = next_stage;
+          phase = next_phase;
+          ready = ready_next;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const uint32_t quarter = warp & 3u;
+    uint32_t local = 0;
+    bool alive = true;
+    for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs, ++local) {
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+#pragma unroll 1
+      for (uint32_t u = 0; u < 2; ++u) {
+        bool ok = ptx::mbar_wait(tfull_bar(u), local & 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 3, u, t, 0);
+          }
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t row0 = (tm * 4 + u * 2 + cta_rank) * BLOCK_M + quarter * 32u;
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + u * BN;
+        if (p.tma_store) {
+          // registers -> swizzled staging tile -> TMA store of whole 128-byte lines
+          // (TMA clips rows >= M and columns >= N)
+#pragma unroll 1
+          for (uint32_t ch = 0; ch < BN / 32; ++ch) {
+            const uint32_t col0 = tn * BN + ch * 32u;
+            if (col0 >= p.N) break;
+            const uint32_t staging = staging_base + ((warp - 2u) * 2u + (ch & 1u)) * 4096u;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(taddr + ch * 32u, r);
+            if (lane == 0) ptx::tma_store_wait_read<1>();  // the buffer used two chunks ago is free
+            __syncwarp();
+            ptx::tmem_ld_wait();
+            epilogue_stage32(p, r, col0, staging, lane);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+              ptx::tma_store_2d(&tm_c, int32_t(col0), int32_t(row0), staging);
+              ptx::tma_store_commit();
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (uint32_t ch = 0; ch < BN / 32; ++ch) {
+            const uint32_t col0 = tn * BN + ch * 32u;
+            if (col0 >= p.N) break;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(taddr + ch * 32u, r);
+            ptx::tmem_ld_wait();
+            epilogue_store32(p, r, row0 + lane, col0);
+          }
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(u), 0));
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();  // staging tiles fully read and written out
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
+      if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
+      __nanosleep(1000);
+    }
+    __syncthreads();
+  }
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -836,6 +1463,110 @@ int choose_block_n(Kind kind, uint32_t M, uint32_t N, uint32_t K, int sms) {
   return best;
 }
 
+template <int BLOCK_N, int SUB>
+const char* launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, const KernelParams& kp,
+                                uint32_t pairs, cudaStream_t stream) {
+  constexpr uint32_t stage = SUB * (A_TILE_BYTES + (BLOCK_N / 2) * SLAB_ROW_BYTES);
+  constexpr uint32_t avail = SMEM_LIMIT - 1024 - 256;
+  constexpr int STAGES = (avail / stage) > 8 ? 8 : int(avail / stage);
+  constexpr uint32_t smem = STAGES * stage + 1024 + 256;
+  static_assert(STAGES >= 1 && smem <= SMEM_LIMIT, "pair kernel shared memory");
+  auto kern = gemm_f16_pair_kernel<BLOCK_N, STAGES, SUB>;
+  static bool attr_done_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done_dev[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+        cudaSuccess)
+      return "cudaFuncSetAttribute(max dynamic shared memory) failed";
+    attr_done_dev[dev & 63] = true;
+  }
+  kern<<<2 * pairs, NUM_THREADS, smem, stream>>>(ma, mb, kp);  // cluster size 2 is compiled in
+  if (cudaGetLastError() != cudaSuccess) return "GEMM pair kernel launch failed";
+  return nullptr;
+}
+
+const char* launch_pair512(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                           const KernelParams& kp, uint32_t pairs, cudaStream_t stream) {
+  constexpr uint32_t stage = 2 * A_TILE_BYTES + 128 * SLAB_ROW_BYTES;
+  constexpr uint32_t extra = 1024 /*align*/ + 1024 /*barriers*/ + 4 * 2 * 4096 /*epilogue staging*/;
+  constexpr int STAGES = int((SMEM_LIMIT - extra) / stage);
+  constexpr uint32_t smem = STAGES * stage + extra;
+  static_assert(STAGES >= 3 && smem <= SMEM_LIMIT, "pair512 kernel shared memory");
+  auto kern = gemm_f16_pair512_kernel<STAGES>;
+  static bool attr_done_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done_dev[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+        cudaSuccess)
+      return "cudaFuncSetAttribute(max dynamic shared memory) failed";
+    attr_done_dev[dev & 63] = true;
+  }
+  kern<<<2 * pairs, NUM_THREADS, smem, stream>>>(ma, mb, mc, kp);
+  if (cudaGetLastError() != cudaSuccess) return "GEMM pair512 kernel launch failed";
+  return nullptr;
+}
+
+// fp16 GEMM on CTA pairs: (256 or 512) x bn tiles, one cluster of two CTAs per tile.
+const char* launch_gemm_pair(uint32_t M, uint32_t N, uint32_t K, int bn, bool tall,
+                             const GemmOperand& A, const GemmOperand& B, KernelParams kp,
+                             int sm_count, int max_ctas, cudaStream_t stream) {
+  const uint32_t block_k = 64;
+  const uint32_t tile_m = tall ? 4 * BLOCK_M : 2 * BLOCK_M;
+  kp.a = plan_operand(false, A.mn_major, BLOCK_M, block_k);
+  kp.b = plan_operand(false, B.mn_major, uint32_t(bn / 2), block_k);
+  kp.tiles_m = (M + tile_m - 1) / tile_m;
+  kp.tiles_n = (N + bn - 1) / bn;
+  kp.num_tiles = kp.tiles_m * kp.tiles_n;
+  kp.num_kblocks = (K + block_k - 1) / block_k;
+  kp.group_m = tall ? 4 : 8;
+  kp.idesc = ptx::make_idesc(0u, A.mn_major, B.mn_major, 2 * BLOCK_M, uint32_t(bn));
+  CUtensorMap ma, mb;
+  std::memset(&ma, 0, sizeof(ma));
+  std::memset(&mb, 0, sizeof(mb));
+  const uint32_t a_box_rows = A.mn_major ? block_k : BLOCK_M;
+  const uint32_t b_box_rows = B.mn_major ? block_k : uint32_t(bn / 2);
+  if (!make_map(&ma, false, A.plane0, A.mn_major ? M : K, A.mn_major ? K : M, A.pitch, a_box_rows,
+                A.mn_major) ||
+      !make_map(&mb, false, B.plane0, B.mn_major ? N : K, B.mn_major ? K : N, B.pitch, b_box_rows,
+                B.mn_major))
+    return "cuTensorMapEncodeTiled failed";
+  const uint32_t limit = uint32_t(max_ctas > 0 ? max_ctas : sm_count) / 2;
+  const uint32_t pairs = std::max<uint32_t>(1u, std::min<uint32_t>(kp.num_tiles, limit));
+  if (tall) {
+    // C as a TMA store target: boxes of 32 columns x 32 rows, 128-byte swizzle.
+    CUtensorMap mc;
+    std::memset(&mc, 0, sizeof(mc));
+    kp.tma_store = 0;
+    static const bool want_tma_store = [] {
+      const char* e = std::getenv("GONNGPU_TMA_STORE");  // experiment switch, off by default
+      return e && std::atoi(e) != 0;
+    }();
+    if (want_tma_store && kp.vec_store && !kp.c_in) {
+      EncodeTiledFn fn = encode_tiled();
+      cuuint64_t dims[2] = {N, M};
+      cuuint64_t strides[1] = {kp.ldc * 4};
+      cuuint32_t box[2] = {32, 32};
+      cuuint32_t estr[2] = {1, 1};
+      if (fn && fn(&mc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, kp.C, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+        kp.tma_store = 1;
+    }
+    return launch_pair512(ma, mb, mc, kp, pairs, stream);
+  }
+  static const int sub = [] {
+    const char* e = std::getenv("GONNGPU_PAIR_SUB");  // experiment switch: k blocks per stage
+    return e ? std::atoi(e) : 2;
+  }();
+  if (bn == 256)
+    return sub == 1 ? launch_pair_variant<256, 1>(ma, mb, kp, pairs, stream)
+                    : launch_pair_variant<256, 2>(ma, mb, kp, pairs, stream);
+  return sub == 1 ? launch_pair_variant<128, 1>(ma, mb, kp, pairs, stream)
+                  : launch_pair_variant<128, 2>(ma, mb, kp, pairs, stream);
+}
+
 }  // namespace
 
 const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const GemmOperand& A,
@@ -880,6 +1611,27 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
                  (!kp.c_in || reinterpret_cast<uintptr_t>(kp.c_in) % 16 == 0) &&
                  (!kp.bias || reinterpret_cast<uintptr_t>(kp.bias) % 16 == 0);
   kp.status = status;
+
+  // Large fp16 problems run on CTA pairs (256-row tiles); small ones, where the
+  // pair tiles would not fill the machine, stay on single-CTA tiles.
+  if (kind == Kind::F16 && tune.pair != 0) {
+    const uint64_t half_sms = uint64_t(sm_count) / 2;
+    // 512-row tiles need a quarter fewer operand bytes per flop than 256-row
+    // tiles but cannot overlap their epilogue with the next tile (TMEM is full),
+    // so they pay off only for deep K (measured: ahead at K=8192, behind at 4096).
+    const uint64_t tall_tiles = uint64_t((M + 511) / 512) * ((N + 255) / 256);
+    const bool tall_ok = (tune.block_n == 0 || tune.block_n == 256);
+    if (tall_ok && (tune.pair == 2 || (tune.pair < 0 && M >= 512 && N >= 128 && K >= 6144 && tall_tiles >= half_sms))) {
+      return launch_gemm_pair(M, N, K, 256, true, A, B, kp, sm_count, tune.max_ctas, stream);
+    }
+    const int pbn = (tune.block_n == 128) ? 128 : 256;
+    const uint64_t pair_tiles = uint64_t((M + 255) / 256) * ((N + pbn - 1) / pbn);
+    const bool fits = (tune.block_n == 0 || tune.block_n == 128 || tune.block_n == 256);
+    const bool worth = M >= 256 && N >= uint32_t(pbn) / 2 && pair_tiles >= half_sms;
+    if (fits && (tune.pair == 1 || (tune.pair < 0 && worth))) {
+      return launch_gemm_pair(M, N, K, pbn, false, A, B, kp, sm_count, tune.max_ctas, stream);
+    }
+  }
 
   // Tensor maps: inner extent is the contiguous index, outer the row index.
   CUtensorMap maps[4];

@@ -50,6 +50,7 @@ struct GemmStatus {
 struct GemmTuning {
   int block_n = 0;   // 0 = choose; else 32/64/128/256
   int max_ctas = 0;  // 0 = one per SM
+  int pair = -1;     // fp16 CTA-pair kernel: -1 = choose by size, 0 = never, 1 = always
 };
 
 // Enqueues the GEMM on `stream`.  Returns nullptr on success, else a static

@@ -10,7 +10,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libgonngpu_cuda.so")
+LIB_PATH = os.environ.get("GONNGPU_LIB", os.path.join(HERE, "libgonngpu_cuda.so"))
 
 FP32_3XTF32, FP16_RN, FP16_TRUNC = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_LEAKY, ACT_SIGMOID, ACT_TANH, ACT_GELU = -1, 0, 1, 2, 3, 4
@@ -76,6 +76,7 @@ SIGNATURES = {
     "gonngpu_synchronize": (_c_int, [_errp]),
     "gonngpu_set_plane_cache": (_c_int, [_c_int]),
     "gonngpu_set_gemm_tuning": (_c_int, [_c_int, _c_int]),
+    "gonngpu_set_gemm_pair_mode": (_c_int, [_c_int]),
     "gonngpu_get_stats": (None, [ctypes.POINTER(_c_long)]),
     "gonngpu_last_kernel_status": (None, [ctypes.POINTER(ctypes.c_uint)]),
     "gonngpu_version": (ctypes.c_char_p, []),

@@ -217,6 +217,10 @@ GONNGPU_API int gonngpu_set_plane_cache(int enabled);
 /* GEMM tile override for experiments: block_n in {0 = auto, 32, 64, 128, 256},
  * max_ctas 0 = one per SM. */
 GONNGPU_API int gonngpu_set_gemm_tuning(int block_n, int max_ctas);
+/* fp16 GEMM on CTA pairs (2-SM MMA): -1 (default) chosen by problem size,
+ * 0 never, 1 force 256-row tiles (block_n 0, 128 or 256), 2 force 512-row
+ * tiles (block_n 0 or 256). */
+GONNGPU_API int gonngpu_set_gemm_pair_mode(int mode);
 
 /* out[0] bytes of HBM held, [1] host->device bytes, [2] device->host bytes,
  * [3] kernels launched, [4] GEMM kernels launched, [5] buffers alive,

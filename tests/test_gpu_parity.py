@@ -340,3 +340,48 @@ def test_buffer_protocol(gpu):
     assert np.array_equal(out.retrieve((4, 4)), np.arange(16, dtype=np.float32).reshape(4, 4).T)
     hb.release()
     gpu.lib().gonngpu_host_free(p)
+
+
+# ------------------------------------------------------------------ CTA-pair (2-SM MMA) fp16 kernels
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 256, 256), (1024, 512, 512), (600, 400, 136),
+                                   (130, 300, 200), (257, 129, 65), (2048, 2048, 1024)])
+@pytest.mark.parametrize("layout", ["nn", "tn", "nt", "tt"])
+def test_fp16_cta_pair_kernels(gpu, mode, shape, layout):
+    """The 256-row (mode 1) and 512-row (mode 2) pair kernels, forced also for
+    shapes the size heuristic would give to the single-CTA kernel."""
+    m, n, k = shape
+    rng = np.random.default_rng(m * 31 + n * 17 + k)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    ta, tb = layout[0] == "t", layout[1] == "t"
+    As = np.ascontiguousarray(A.T) if ta else A
+    Bs = np.ascontiguousarray(B.T) if tb else B
+    try:
+        assert gpu.lib().gonngpu_set_gemm_pair_mode(mode) == 0
+        C = run_matmul(gpu, As, Bs, ta, tb, precision=gpu.FP16_RN)
+    finally:
+        gpu.lib().gonngpu_set_gemm_pair_mode(-1)
+    assert oracle.rel_frobenius(C, oracle.gemm_f64(oracle.f16_rn(As), oracle.f16_rn(Bs), ta, tb)) <= 2e-5
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_fp16_cta_pair_persistent_loop_and_epilogue(gpu, mode):
+    rng = np.random.default_rng(77 + mode)
+    A = rng.integers(-3, 4, (4096, 320)).astype(np.float32)
+    B = rng.integers(-3, 4, (320, 1024)).astype(np.float32)
+    bias = rng.integers(-5, 6, 1024).astype(np.float32)
+    C0 = rng.integers(-3, 4, (4096, 1024)).astype(np.float32)
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    try:
+        gpu.lib().gonngpu_set_gemm_pair_mode(mode)
+        gpu.lib().gonngpu_set_gemm_tuning(0, 6)       # 3 pairs walk 32 or 64 tiles: accumulator ring, stage ring
+        assert np.array_equal(run_matmul(gpu, A, B, precision=gpu.FP16_RN), ref.astype(np.float32))
+        gpu.lib().gonngpu_set_gemm_tuning(0, 0)
+        got = run_matmul(gpu, A, B, precision=gpu.FP16_RN, bias=bias, act=0)
+        assert np.array_equal(got, np.maximum(ref + bias, 0).astype(np.float32))
+        got = run_matmul(gpu, A, B, precision=gpu.FP16_RN, alpha=0.5, beta=2.0, C0=C0.copy())
+        assert np.array_equal(got, (0.5 * ref + 2.0 * C0).astype(np.float32))
+    finally:
+        gpu.lib().gonngpu_set_gemm_tuning(0, 0)
+        gpu.lib().gonngpu_set_gemm_pair_mode(-1)
