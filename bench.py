@@ -305,6 +305,18 @@ def run_e2e(args, g, L, torch, dist, dev, rank, world, rows, A32, B32):
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_s * 1e3, "steps": e2e_steps}
 
 
+# DRAM bytes of one GEMM launch measured with ncu (dram__bytes_read.sum +
+# dram__bytes_write.sum) on the M=8192 case of this kernel: see profiles/.
+NCU_TRAFFIC_M8192 = {"read": 180.0e6, "write": 99.5e6, "rows": 8192}
+
+
+def traffic_estimate(rows):
+    """Scales the captured traffic to `rows`: A and C grow with the rows, B (33.6 MB) does not."""
+    b_bytes = 2.0 * K_DIM * N_DIM
+    per_row = (NCU_TRAFFIC_M8192["read"] + NCU_TRAFFIC_M8192["write"] - b_bytes) / NCU_TRAFFIC_M8192["rows"]
+    return per_row * rows + b_bytes
+
+
 def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, clocks, launches, check, e2e):
     if True:
         peaks = load_peaks()
@@ -320,7 +332,7 @@ def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, cl
                        "b_broadcast_in_step": world > 1},
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
-                         "frac": achieved / peaks[peak_kind], "traffic": None,
+                         "frac": achieved / peaks[peak_kind], "traffic": traffic_estimate(rows),
                          "peak_source": f"{peaks['source']} cuBLAS bf16 ({peak_kind})",
                          "kernel_ms": kernel_ms_max},
             "e2e": e2e,
@@ -328,8 +340,9 @@ def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, cl
             "parity_spot_check_rel_frobenius": check,
         }
         if world == 1 and not args.no_cpu:
-            rate, dt, threads = cpu_gemm_rate(256)
-            rows_cpu = int(min(8192, max(256, 256 * 12.0 / max(dt, 1e-6)))) // 128 * 128
+            rate, dt, threads = cpu_gemm_rate(512)
+            # size the sample for roughly 15 s of CPU work (bounded by the whole workload)
+            rows_cpu = int(min(M_TOTAL, max(512, 512 * 15.0 / max(dt, 1e-6)))) // 128 * 128
             rate, dt, threads = cpu_gemm_rate(max(rows_cpu, 128))
             line["cpu_baseline"] = {
                 "value": rate, "unit": "TFLOP/s", "cores": threads, "kind": "port",
