@@ -7,8 +7,11 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
+#include <map>
 #include <mutex>
 #include <unordered_set>
+#include <vector>
 
 #include "../../include/gonngpu.h"
 #include "kernels.h"
@@ -41,6 +44,7 @@ struct Buffer {
   float* host = nullptr;      // caller memory registered by create_gpu_buffer
   bool host_pending = false;  // host bytes not yet copied to the device
   uint64_t version = 1;       // bumped whenever the device contents change
+  bool host_current = false;  // the registered host memory already holds the device contents
   Plane f16[2];               // [F16_RN], [F16_TRUNC]
   Plane tf32;
 };
@@ -49,7 +53,8 @@ struct Device {
   int ordinal = -1;
   bool ready = false;
   cudaStream_t stream = nullptr;
-  cudaStream_t copy_stream = nullptr;
+  cudaStream_t copy_stream = nullptr;  // host -> device side stream of the streamed MatMul
+  cudaStream_t d2h_stream = nullptr;   // device -> host side stream of the streamed MatMul
   int sm_count = 0;
   GemmStatus* status_host = nullptr;  // mapped pinned memory the kernels report into
   GemmStatus* status_dev = nullptr;
@@ -65,6 +70,45 @@ bool g_plane_cache = true;
 gonn::GemmTuning g_tune;
 std::unordered_set<Buffer*> g_buffers;
 long g_stats[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+
+// Device-memory cache.  cudaMalloc / cudaFree of multi-gigabyte blocks cost
+// milliseconds and synchronise the device, and the reference's callers create
+// and release a result buffer per MatMul, so freed blocks are kept (per device,
+// keyed by exact size, up to kPoolCapBytes) and handed out again.
+constexpr size_t kPoolCapBytes = size_t(24) << 30;
+std::multimap<size_t, void*> g_pool[kMaxDevices];
+size_t g_pool_bytes[kMaxDevices] = {};
+
+cudaError_t pool_alloc(int dev, void** out, size_t bytes) {
+  auto& pool = g_pool[dev];
+  auto it = pool.find(bytes);
+  if (it != pool.end()) {
+    *out = it->second;
+    g_pool_bytes[dev] -= bytes;
+    pool.erase(it);
+    return cudaSuccess;
+  }
+  cudaError_t e = cudaMalloc(out, bytes);
+  if (e != cudaSuccess && !pool.empty()) {  // give the cache back and retry once
+    cudaGetLastError();
+    for (auto& kv : pool) cudaFree(kv.second);
+    pool.clear();
+    g_pool_bytes[dev] = 0;
+    e = cudaMalloc(out, bytes);
+  }
+  return e;
+}
+
+// `dev` must be current.  The caller has made sure no work still uses `p`.
+void pool_free(int dev, void* p, size_t bytes) {
+  if (!p) return;
+  if (bytes >= (1u << 20) && g_pool_bytes[dev] + bytes <= kPoolCapBytes) {
+    g_pool[dev].emplace(bytes, p);
+    g_pool_bytes[dev] += bytes;
+  } else {
+    cudaFree(p);
+  }
+}
 
 void set_error(CError* err, const char* fmt, ...) {
   if (!err) return;
@@ -105,6 +149,7 @@ int ensure_device(int ordinal, CError* err) {
   d.sm_count = prop.multiProcessorCount;
   bool ok = cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking) == cudaSuccess &&
             cudaStreamCreateWithFlags(&d.copy_stream, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaStreamCreateWithFlags(&d.d2h_stream, cudaStreamNonBlocking) == cudaSuccess &&
             cudaHostAlloc(reinterpret_cast<void**>(&d.status_host), sizeof(GemmStatus),
                           cudaHostAllocMapped) == cudaSuccess &&
             cudaHostGetDevicePointer(reinterpret_cast<void**>(&d.status_dev), d.status_host, 0) ==
@@ -208,17 +253,20 @@ bool make_resident(Device& d, Buffer* b) {
 
 void wrote(Buffer* b) {
   b->host_pending = false;
+  b->host_current = false;
   ++b->version;
 }
 
 void free_plane(Plane& p) {
+  int dev = 0;
+  cudaGetDevice(&dev);
   if (p.p0) {
-    cudaFree(p.p0);
+    pool_free(dev, p.p0, p.bytes);
     g_stats[0] -= long(p.bytes);
     g_stats[6] -= long(p.bytes);
   }
   if (p.p1) {
-    cudaFree(p.p1);
+    pool_free(dev, p.p1, p.bytes);
     g_stats[0] -= long(p.bytes);
     g_stats[6] -= long(p.bytes);
   }
@@ -237,7 +285,7 @@ Plane* get_plane(Device& d, Buffer* b, uint64_t rows, uint64_t cols, int kind) {
   const size_t bytes = size_t(rows) * pitch * esz;
   if (!p.p0 || p.bytes < bytes) {
     free_plane(p);
-    if (cudaMalloc(&p.p0, bytes) != cudaSuccess) {
+    if (pool_alloc(d.ordinal, &p.p0, bytes) != cudaSuccess) {
       cudaGetLastError();
       p = Plane{};
       return nullptr;
@@ -245,9 +293,9 @@ Plane* get_plane(Device& d, Buffer* b, uint64_t rows, uint64_t cols, int kind) {
     g_stats[0] += long(bytes);
     g_stats[6] += long(bytes);
     if (kind == 2) {
-      if (cudaMalloc(&p.p1, bytes) != cudaSuccess) {
+      if (pool_alloc(d.ordinal, &p.p1, bytes) != cudaSuccess) {
         cudaGetLastError();
-        cudaFree(p.p0);
+        pool_free(d.ordinal, p.p0, bytes);
         g_stats[0] -= long(bytes);
         g_stats[6] -= long(bytes);
         p = Plane{};
@@ -303,6 +351,110 @@ struct MatmulArgs {
   float act_param;
 };
 
+// Streamed MatMul for a product whose A still lies in page-locked host memory
+// and whose C is registered over page-locked host memory: A is uploaded in row
+// blocks on one stream, each block is converted and multiplied on the compute
+// stream, and its rows of C go back to the host on a third stream, so that the
+// two PCIe directions and the tensor cores overlap.  The host copy of C is then
+// current, as it is with the reference's aliased buffers, and a later
+// retrieve_gpu_buffer_data into the same memory has nothing left to do.
+// Returns 1 when the product was done here, 0 when the caller should take the
+// ordinary path, -1 on a CUDA error.
+constexpr long kStreamRows = 8192;
+int matmul_streamed(Device& d, Buffer* A, Buffer* B, Buffer* C, Buffer* bias, long M, long N, long K,
+                    bool transB, int pkind, float alpha, int act, float act_param, const char** msg) {
+  if (pkind == 2 || !g_blocking || !A->host_pending || !C->host || M < 2 * kStreamRows) return 0;
+  if (!host_is_pinned(A->host) || !host_is_pinned(C->host)) return 0;
+  if (!make_resident(d, B) || (bias && !make_resident(d, bias))) return -1;
+  Plane* pb = get_plane(d, B, uint64_t(transB ? N : K), uint64_t(transB ? K : N), pkind);
+  // the A plane is filled block by block below; take it without converting
+  Plane& pa = A->f16[pkind];
+  const uint64_t pitch = round_up(uint64_t(K), 64);
+  const size_t pa_bytes = size_t(M) * pitch * 2;
+  if (!pb) return -1;
+  if (!pa.p0 || pa.bytes < pa_bytes) {
+    free_plane(pa);
+    if (pool_alloc(d.ordinal, &pa.p0, pa_bytes) != cudaSuccess) {
+      cudaGetLastError();
+      pa = Plane{};
+      return -1;
+    }
+    pa.bytes = pa_bytes;
+    g_stats[0] += long(pa_bytes);
+    g_stats[6] += long(pa_bytes);
+  }
+  const long blocks = (M + kStreamRows - 1) / kStreamRows;
+  std::vector<cudaEvent_t> up(blocks), done(blocks);
+  bool ok = true;
+  for (long i = 0; i < blocks && ok; ++i)
+    ok = cudaEventCreateWithFlags(&up[i], cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming) == cudaSuccess;
+  cudaEvent_t start;
+  ok = ok && cudaEventCreateWithFlags(&start, cudaEventDisableTiming) == cudaSuccess;
+  // the side streams start after everything already queued on the compute stream (B, bias)
+  ok = ok && cudaEventRecord(start, d.stream) == cudaSuccess &&
+       cudaStreamWaitEvent(d.copy_stream, start, 0) == cudaSuccess &&
+       cudaStreamWaitEvent(d.d2h_stream, start, 0) == cudaSuccess;
+  gonn::GemmOperand ob;
+  ob.plane0 = pb->p0;
+  ob.pitch = pb->pitch;
+  ob.mn_major = !transB;
+  for (long i = 0; i < blocks && ok; ++i) {
+    const long r0 = i * kStreamRows, rows = std::min(kStreamRows, M - r0);
+    float* a_dev = A->dptr + size_t(r0) * K;
+    float* c_dev = C->dptr + size_t(r0) * N;
+    ok = cudaMemcpyAsync(a_dev, A->host + size_t(r0) * K, size_t(rows) * K * 4, cudaMemcpyHostToDevice,
+                         d.copy_stream) == cudaSuccess &&
+         cudaEventRecord(up[i], d.copy_stream) == cudaSuccess &&
+         cudaStreamWaitEvent(d.stream, up[i], 0) == cudaSuccess;
+    if (!ok) break;
+    g_stats[1] += long(rows) * K * 4;
+    char* plane_rows = static_cast<char*>(pa.p0) + size_t(r0) * pitch * 2;
+    gonn::launch_cvt_f16(a_dev, uint64_t(rows), uint64_t(K), plane_rows, pitch, pkind, d.stream);
+    gonn::GemmOperand oa;
+    oa.plane0 = plane_rows;
+    oa.pitch = pitch;
+    oa.mn_major = false;
+    gonn::GemmEpilogue epi;
+    epi.alpha = alpha;
+    epi.bias = bias ? bias->dptr : nullptr;
+    epi.act = act;
+    epi.act_param = act_param;
+    *msg = gonn::launch_gemm(gonn::Kind::F16, uint32_t(rows), uint32_t(N), uint32_t(K), oa, ob, c_dev,
+                             uint64_t(N), epi, d.status_dev, d.sm_count, g_tune, d.stream);
+    if (*msg) {
+      ok = false;
+      break;
+    }
+    g_stats[3] += 2;
+    ++g_stats[4];
+    ok = cudaEventRecord(done[i], d.stream) == cudaSuccess &&
+         cudaStreamWaitEvent(d.d2h_stream, done[i], 0) == cudaSuccess &&
+         cudaMemcpyAsync(C->host + size_t(r0) * N, c_dev, size_t(rows) * N * 4, cudaMemcpyDeviceToHost,
+                         d.d2h_stream) == cudaSuccess;
+    g_stats[2] += long(rows) * N * 4;
+  }
+  // everything is complete on return (the ABI is blocking)
+  const bool synced = cudaStreamSynchronize(d.copy_stream) == cudaSuccess &&
+                      cudaStreamSynchronize(d.stream) == cudaSuccess &&
+                      cudaStreamSynchronize(d.d2h_stream) == cudaSuccess;
+  for (long i = 0; i < blocks; ++i) {
+    if (up[i]) cudaEventDestroy(up[i]);
+    if (done[i]) cudaEventDestroy(done[i]);
+  }
+  if (start) cudaEventDestroy(start);
+  if (!ok || !synced) return -1;
+  A->host_pending = false;
+  ++A->version;
+  pa.version = A->version;  // the plane matches the uploaded rows
+  pa.rows = uint64_t(M);
+  pa.cols = uint64_t(K);
+  pa.pitch = pitch;
+  wrote(C);
+  C->host_current = true;
+  return 1;
+}
+
 // Shared body of every GEMM entry point.  `codes` maps the failing step to the
 // caller's return value: {device, buffer, dims, setup, scratch, exec}.
 int matmul_core(const MatmulArgs& m, const int codes[6], const char* what, CError* err) {
@@ -349,6 +501,18 @@ int matmul_core(const MatmulArgs& m, const int codes[6], const char* what, CErro
   if (m.precision < 0 || m.precision > 2) {
     set_error(err, "%s: unknown precision %d.", what, m.precision);
     return codes[2];
+  }
+  if (!m.transA && m.beta == 0.f && m.precision != GONNGPU_FP32_3XTF32) {
+    const char* smsg = nullptr;
+    const int sr = matmul_streamed(d, A, B, C, bias, M, N, K, m.transB,
+                                   m.precision == GONNGPU_FP16_RN ? 0 : 1, m.alpha, m.act, m.act_param,
+                                   &smsg);
+    if (sr == 1) return finish(d, err, codes[5], what);
+    if (sr < 0) {
+      cudaGetLastError();
+      set_error(err, "%s: %s", what, smsg ? smsg : "streamed transfer failed.");
+      return smsg ? codes[3] : codes[5];
+    }
   }
   if (!make_resident(d, A) || !make_resident(d, B) || (bias && !make_resident(d, bias)) ||
       (m.beta != 0.f && !make_resident(d, C))) {
@@ -411,7 +575,7 @@ int new_buffer(int device, float* host, size_t bytes, void* wrap, Buffer** out, 
     b->dptr = static_cast<float*>(wrap);
     b->owns = false;
   } else {
-    if (cudaMalloc(reinterpret_cast<void**>(&b->dptr), bytes ? bytes : 4) != cudaSuccess) {
+    if (pool_alloc(device, reinterpret_cast<void**>(&b->dptr), bytes ? bytes : 4) != cudaSuccess) {
       cudaGetLastError();
       delete b;
       set_error(err, "Could not allocate %zu bytes of device memory.", bytes);
@@ -467,6 +631,7 @@ int retrieve_gpu_buffer_data(GPUPtr gpuPtr, float* data, long length_bytes, CErr
     if (data != b->host) std::memmove(data, b->host, size_t(length_bytes));
     return 0;
   }
+  if (b->host_current && data == b->host) return 0;  // the streamed MatMul already wrote it back
   if (ensure_device(b->device, err)) return -3;
   Device& d = g_dev[b->device];
   if (!copy_d2h(d, data, b->dptr, size_t(length_bytes))) {
@@ -489,7 +654,7 @@ int release_gpu_buffer(GPUPtr gpuPtr) {
   free_plane(b->f16[1]);
   free_plane(b->tf32);
   if (b->owns && b->dptr) {
-    cudaFree(b->dptr);
+    pool_free(b->device, b->dptr, b->bytes ? b->bytes : 4);
     g_stats[0] -= long(b->bytes);
   }
   cudaGetLastError();
@@ -936,9 +1101,33 @@ int gonngpu_set_gemm_pair_mode(int mode) {
   return 0;
 }
 
+long gonngpu_trim_cache(void) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  long freed = 0;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  for (int dev = 0; dev < kMaxDevices; ++dev) {
+    if (g_pool[dev].empty()) continue;
+    if (cudaSetDevice(dev) != cudaSuccess) continue;
+    if (g_dev[dev].ready) cudaStreamSynchronize(g_dev[dev].stream);
+    for (auto& kv : g_pool[dev]) {
+      cudaFree(kv.second);
+      freed += long(kv.first);
+    }
+    g_pool[dev].clear();
+    g_pool_bytes[dev] = 0;
+  }
+  cudaSetDevice(prev);
+  cudaGetLastError();
+  return freed;
+}
+
 void gonngpu_get_stats(long out[8]) {
   std::lock_guard<std::recursive_mutex> lk(g_mu);
   for (int i = 0; i < 8; ++i) out[i] = g_stats[i];
+  long cached = 0;
+  for (int dev = 0; dev < kMaxDevices; ++dev) cached += long(g_pool_bytes[dev]);
+  out[7] = cached;
 }
 
 void gonngpu_last_kernel_status(unsigned out[4]) {

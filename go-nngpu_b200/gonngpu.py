@@ -77,6 +77,7 @@ SIGNATURES = {
     "gonngpu_set_plane_cache": (_c_int, [_c_int]),
     "gonngpu_set_gemm_tuning": (_c_int, [_c_int, _c_int]),
     "gonngpu_set_gemm_pair_mode": (_c_int, [_c_int]),
+    "gonngpu_trim_cache": (_c_long, []),
     "gonngpu_get_stats": (None, [ctypes.POINTER(_c_long)]),
     "gonngpu_last_kernel_status": (None, [ctypes.POINTER(ctypes.c_uint)]),
     "gonngpu_version": (ctypes.c_char_p, []),
@@ -261,7 +262,7 @@ def stats():
     out = (_c_long * 8)()
     lib().gonngpu_get_stats(out)
     keys = ["hbm_bytes", "h2d_bytes", "d2h_bytes", "kernel_launches", "gemm_launches", "buffers",
-            "plane_bytes", "reserved"]
+            "plane_bytes", "cached_bytes"]
     return dict(zip(keys, list(out)))
 
 

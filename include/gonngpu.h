@@ -222,9 +222,16 @@ GONNGPU_API int gonngpu_set_gemm_tuning(int block_n, int max_ctas);
  * tiles (block_n 0 or 256). */
 GONNGPU_API int gonngpu_set_gemm_pair_mode(int mode);
 
-/* out[0] bytes of HBM held, [1] host->device bytes, [2] device->host bytes,
- * [3] kernels launched, [4] GEMM kernels launched, [5] buffers alive,
- * [6] scratch (operand plane) bytes held, [7] reserved. */
+/* Released buffers and operand planes are kept in a per-device cache (the
+ * reference's callers create and release a result buffer per MatMul, and
+ * cudaMalloc/cudaFree of gigabytes cost milliseconds).  This returns the cache
+ * to the driver and reports the bytes freed. */
+GONNGPU_API long gonngpu_trim_cache(void);
+
+/* out[0] bytes of HBM held by live buffers and planes, [1] host->device bytes,
+ * [2] device->host bytes, [3] kernels launched, [4] GEMM kernels launched,
+ * [5] buffers alive, [6] scratch (operand plane) bytes held, [7] bytes in the
+ * released-block cache. */
 GONNGPU_API void gonngpu_get_stats(long out[8]);
 /* Status words of the last GEMM kernel on the current device: code (0 fine,
  * 1 producer / 2 MMA issuer / 3 epilogue wait ran out), where, tile, k block. */

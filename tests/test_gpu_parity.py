@@ -385,3 +385,40 @@ def test_fp16_cta_pair_persistent_loop_and_epilogue(gpu, mode):
     finally:
         gpu.lib().gonngpu_set_gemm_tuning(0, 0)
         gpu.lib().gonngpu_set_gemm_pair_mode(-1)
+
+
+def test_streamed_matmul_from_pinned_host_memory(gpu):
+    """A large product whose A and C live in page-locked host memory takes the
+    streamed path (upload, multiply and write-back overlapped in row blocks);
+    the host copy of C is current on return and the device copies stay valid."""
+    m, k, n = 20000, 256, 512                     # ragged last block (20000 = 2*8192 + 3616)
+    rng = np.random.default_rng(5)
+    hA, pA = gpu.pinned_array((m, k))
+    hC, pC = gpu.pinned_array((m, n))
+    hA[:] = (rng.standard_normal((m, k)) / 16).astype(np.float32)
+    B = (rng.standard_normal((k, n)) / 16).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    hC[:] = -5.0
+    a, b, c, bb = gpu.Buffer.from_host(hA), gpu.Buffer.from_host(B), gpu.Buffer.from_host(hC), gpu.Buffer.from_host(bias)
+    before = gpu.stats()
+    gpu.matmul_ex(a, (m, k), False, b, (k, n), False, c, (m, n), precision=gpu.FP16_RN, bias=bb, act=0)
+    after = gpu.stats()
+    ref = np.maximum(oracle.gemm_f64(oracle.f16_rn(hA), oracle.f16_rn(B)) + bias, 0)
+    assert oracle.rel_frobenius(hC, ref) <= 2e-5            # written back without a retrieve call
+    assert after["gemm_launches"] - before["gemm_launches"] == 3   # three row blocks
+    assert after["d2h_bytes"] - before["d2h_bytes"] == m * n * 4
+    c.retrieve_into(hC)                                      # nothing left to copy
+    assert gpu.stats()["d2h_bytes"] == after["d2h_bytes"]
+    other = c.retrieve((m, n))                               # a different destination still copies
+    assert np.array_equal(other, hC)
+    # the device copies are valid: reuse A (cached plane) and C (as an input) in ordinary calls
+    c2 = gpu.Buffer.empty(m * n * 4)
+    gpu.matmul_ex(a, (m, k), False, b, (k, n), False, c2, (m, n), precision=gpu.FP16_RN, bias=bb, act=0)
+    assert np.array_equal(c2.retrieve((m, n)), hC)
+    t = gpu.Buffer.empty(m * n * 4)
+    gpu.transpose(c, (m, n), t)
+    assert np.array_equal(t.retrieve((n, m)), hC.T)
+    for x in (a, b, c, bb, c2, t):
+        x.release()
+    gpu.lib().gonngpu_host_free(pA)
+    gpu.lib().gonngpu_host_free(pC)
