@@ -1316,6 +1316,250 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
   }
 }
 
+// ---------------------------------------------------------------------------
+// fp32-accurate variant on CTA pairs: the same three-MMA tf32 scheme and chunked
+// promotion as gemm_tf32x3_kernel, with the 2-SM MMA (M=256) of the fp16 pair
+// kernel: each CTA stages its 128 rows of A (hi, lo) and its half of the B tile
+// (hi, lo), 64 KB per k block of 32 for 12 MMAs.  8 drain warps per CTA.
+//   full[s] leader; empty[s] both; tfull[a] both; tempty[a] leader, 16 arrivals.
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TF32_THREADS, 1)
+gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
+                        const __grid_constant__ CUtensorMap tm_a1,
+                        const __grid_constant__ CUtensorMap tm_b0,
+                        const __grid_constant__ CUtensorMap tm_b1,
+                        const __grid_constant__ KernelParams p) {
+  constexpr uint32_t BN = 256;
+  constexpr uint32_t B_TILE_BYTES = (BN / 2) * SLAB_ROW_BYTES;  // this CTA's half, one plane
+  constexpr uint32_t STAGE_BYTES = 2 * (A_TILE_BYTES + B_TILE_BYTES);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr int NC = BN / 2;  // columns per drain thread
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](uint32_t s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t cta_rank = ptx::cluster_ctarank();
+  const bool leader = (cta_rank == 0);
+  const uint32_t pair = blockIdx.x >> 1;
+  const uint32_t num_pairs = gridDim.x >> 1;
+  const uint32_t chunks_per_tile = (p.num_kblocks + CHUNK_KB - 1) / CHUNK_KB;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 16);  // 8 drain warps of each CTA
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&tm_a0);
+    ptx::prefetch_tmap(&tm_a1);
+    ptx::prefetch_tmap(&tm_b0);
+    ptx::prefetch_tmap(&tm_b1);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    uint32_t stage = 0, phase = 0;
+    bool alive = true;
+    for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs) {
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+      const int32_t a_tile = int32_t(tm * 2 + cta_rank);
+      const int32_t b_tile = int32_t(tn * 2 + cta_rank);
+      for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
+        bool ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 1, stage, t, kb);
+          }
+          alive = false;
+          break;
+        }
+        if (lane == 0) {
+          if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+          const uint32_t fb = ptx::mapa_shared(full_bar(stage), 0);
+          uint32_t dst = smem_base + stage * STAGE_BYTES;
+#pragma unroll
+          for (uint32_t pl = 0; pl < 2; ++pl) {
+            const CUtensorMap* ma = pl ? &tm_a1 : &tm_a0;
+            for (uint32_t sl = 0; sl < p.a.slabs; ++sl) {
+              ptx::tma_load_2d_pair(dst + sl * p.a.slab_bytes, ma,
+                                    a_tile * p.a.c0_tile + int32_t(sl) * p.a.c0_slab +
+                                        int32_t(kb) * p.a.c0_k,
+                                    a_tile * p.a.c1_tile + int32_t(kb) * p.a.c1_k, fb);
+            }
+            dst += A_TILE_BYTES;
+          }
+#pragma unroll
+          for (uint32_t pl = 0; pl < 2; ++pl) {
+            const CUtensorMap* mb = pl ? &tm_b1 : &tm_b0;
+            for (uint32_t sl = 0; sl < p.b.slabs; ++sl) {
+              ptx::tma_load_2d_pair(dst + sl * p.b.slab_bytes, mb,
+                                    b_tile * p.b.c0_tile + int32_t(sl) * p.b.c0_slab +
+                                        int32_t(kb) * p.b.c0_k,
+                                    b_tile * p.b.c1_tile + int32_t(kb) * p.b.c1_k, fb);
+            }
+            dst += B_TILE_BYTES;
+          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------- MMA issuer: one thread of the leader
+    if (leader && lane == 0) {
+      const uint32_t a_hi32 = uint32_t(p.a.desc >> 32), b_hi32 = uint32_t(p.b.desc >> 32);
+      const uint32_t a_lo0 = uint32_t(p.a.desc), b_lo0 = uint32_t(p.b.desc);
+      const uint32_t a_step = p.a.kstep_bytes >> 4, b_step = p.b.kstep_bytes >> 4;
+      uint32_t stage = 0, phase = 0;
+      uint32_t chunk = 0;
+      uint32_t ready = 0;
+      bool alive = true;
+      for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs) {
+        for (uint32_t kb0 = 0; alive && kb0 < p.num_kblocks; kb0 += CHUNK_KB, ++chunk) {
+          const uint32_t acc = chunk & 1u;
+          const uint32_t acc_phase = (chunk >> 1) & 1u;
+          if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+            *abort_flag = 1;
+            report(p.status, 2, 0x100u | acc, t, kb0);
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          const uint32_t kb_end = min(kb0 + CHUNK_KB, p.num_kblocks);
+          for (uint32_t kb = kb0; kb < kb_end; ++kb) {
+            if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
+              *abort_flag = 1;
+              report(p.status, 2, stage, t, kb);
+              alive = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
+            const uint32_t next_phase = (stage + 1 == STAGES) ? phase ^ 1u : phase;
+            const uint32_t ready_next = ptx::mbar_test_wait(full_bar(next_stage), next_phase);
+            const uint32_t st = smem_base + stage * STAGE_BYTES;
+            const uint32_t ah = a_lo0 + (st >> 4), al = a_lo0 + ((st + A_TILE_BYTES) >> 4);
+            const uint32_t bh = b_lo0 + ((st + 2 * A_TILE_BYTES) >> 4);
+            const uint32_t bl = b_lo0 + ((st + 2 * A_TILE_BYTES + B_TILE_BYTES) >> 4);
+#pragma unroll
+            for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+              const uint32_t accum = ((kb - kb0) | ks) ? 1u : 0u;
+              ptx::mma_tf32_pair_lohi(d_tmem, al + ks * a_step, a_hi32, bh + ks * b_step, b_hi32,
+                                      p.idesc, accum);
+              ptx::mma_tf32_pair_lohi(d_tmem, ah + ks * a_step, a_hi32, bl + ks * b_step, b_hi32,
+                                      p.idesc, 1u);
+              ptx::mma_tf32_pair_lohi(d_tmem, ah + ks * a_step, a_hi32, bh + ks * b_step, b_hi32,
+                                      p.idesc, 1u);
+            }
+            ptx::mma_commit_pair(empty_bar(stage), 3);
+            if (kb + 1 == kb_end) ptx::mma_commit_pair(tfull_bar(acc), 3);
+            stage = next_stage;
+            phase = next_phase;
+            ready = ready_next;
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------- drain + epilogue warps
+    const uint32_t quarter = warp & 3u;
+    const uint32_t half = (warp - 2u) >> 2;
+    uint32_t chunk = 0;
+    bool alive = true;
+    for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs) {
+      uint32_t tm, tn;
+      tile_coords(p, t, tm, tn);
+      float sums[NC];
+#pragma unroll
+      for (int i = 0; i < NC; ++i) sums[i] = 0.f;
+      for (uint32_t c = 0; c < chunks_per_tile; ++c, ++chunk) {
+        const uint32_t acc = chunk & 1u;
+        const uint32_t acc_phase = (chunk >> 1) & 1u;
+        bool ok = ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report(p.status, 3, acc, t, c);
+          }
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        drain_add<NC>(tmem_base + ((quarter * 32u) << 16) + acc * BN + half * NC, sums);
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(acc), 0));
+      }
+      if (!alive) break;
+      const uint32_t row = (tm * 2 + cta_rank) * BLOCK_M + quarter * 32u + lane;
+      const uint32_t colb = tn * BN + half * NC;
+#pragma unroll
+      for (int j = 0; j < NC / 32; ++j) {
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(sums[j * 32 + i]);
+        epilogue_store32(p, r, row, colb + j * 32);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
+      if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
+      __nanosleep(1000);
+    }
+    __syncthreads();
+  }
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------- host side
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1567,6 +1811,50 @@ const char* launch_gemm_pair(uint32_t M, uint32_t N, uint32_t K, int bn, bool ta
                   : launch_pair_variant<128, 2>(ma, mb, kp, pairs, stream);
 }
 
+// fp32-accurate GEMM on CTA pairs (256 x 256 tiles).
+const char* launch_tf32_pair(uint32_t M, uint32_t N, uint32_t K, const GemmOperand& A,
+                             const GemmOperand& B, KernelParams kp, int sm_count, int max_ctas,
+                             cudaStream_t stream) {
+  constexpr uint32_t block_k = 32;
+  constexpr uint32_t stage = 2 * (A_TILE_BYTES + 128 * SLAB_ROW_BYTES);
+  constexpr int STAGES = int((SMEM_LIMIT - 1024 - 256) / stage);
+  constexpr uint32_t smem = STAGES * stage + 1024 + 256;
+  static_assert(STAGES >= 3 && smem <= SMEM_LIMIT, "tf32 pair kernel shared memory");
+  kp.a = plan_operand(true, A.mn_major, BLOCK_M, block_k);
+  kp.b = plan_operand(true, B.mn_major, 128, block_k);
+  kp.tiles_m = (M + 255) / 256;
+  kp.tiles_n = (N + 255) / 256;
+  kp.num_tiles = kp.tiles_m * kp.tiles_n;
+  kp.num_kblocks = (K + block_k - 1) / block_k;
+  kp.group_m = 8;
+  kp.idesc = ptx::make_idesc(2u, A.mn_major, B.mn_major, 2 * BLOCK_M, 256);
+  CUtensorMap maps[4];
+  std::memset(maps, 0, sizeof(maps));
+  const uint32_t a_box = A.mn_major ? block_k : BLOCK_M, b_box = B.mn_major ? block_k : 128;
+  const uint64_t a_in = A.mn_major ? M : K, a_out = A.mn_major ? K : M;
+  const uint64_t b_in = B.mn_major ? N : K, b_out = B.mn_major ? K : N;
+  if (!make_map(&maps[0], true, A.plane0, a_in, a_out, A.pitch, a_box, A.mn_major) ||
+      !make_map(&maps[1], true, A.plane1, a_in, a_out, A.pitch, a_box, A.mn_major) ||
+      !make_map(&maps[2], true, B.plane0, b_in, b_out, B.pitch, b_box, B.mn_major) ||
+      !make_map(&maps[3], true, B.plane1, b_in, b_out, B.pitch, b_box, B.mn_major))
+    return "cuTensorMapEncodeTiled failed";
+  auto kern = gemm_tf32x3_pair_kernel<STAGES>;
+  static bool attr_done_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done_dev[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+        cudaSuccess)
+      return "cudaFuncSetAttribute(max dynamic shared memory) failed";
+    attr_done_dev[dev & 63] = true;
+  }
+  const uint32_t limit = uint32_t(max_ctas > 0 ? max_ctas : sm_count) / 2;
+  const uint32_t pairs = std::max<uint32_t>(1u, std::min<uint32_t>(kp.num_tiles, limit));
+  kern<<<2 * pairs, TF32_THREADS, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], kp);
+  if (cudaGetLastError() != cudaSuccess) return "GEMM tf32 pair kernel launch failed";
+  return nullptr;
+}
+
 }  // namespace
 
 const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const GemmOperand& A,
@@ -1631,6 +1919,12 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
     if (fits && (tune.pair == 1 || (tune.pair < 0 && worth))) {
       return launch_gemm_pair(M, N, K, pbn, false, A, B, kp, sm_count, tune.max_ctas, stream);
     }
+  }
+
+  if (kind == Kind::TF32x3 && tune.pair != 0 && (tune.block_n == 0 || tune.block_n == 256)) {
+    const uint64_t pair_tiles = uint64_t((M + 255) / 256) * ((N + 255) / 256);
+    if (tune.pair >= 1 || (M >= 256 && N >= 128 && pair_tiles >= uint64_t(sm_count) / 2))
+      return launch_tf32_pair(M, N, K, A, B, kp, sm_count, tune.max_ctas, stream);
   }
 
   // Tensor maps: inner extent is the contiguous index, outer the row index.

@@ -276,6 +276,21 @@ __device__ __forceinline__ void mma_f16_pair_lohi(uint32_t d_tmem, uint32_t a_lo
       ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void mma_tf32_pair_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                                   uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                   uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      ".reg .b64 DA, DB;\n\t"
+      "mov.b64 DA, {%1, %2};\n\t"
+      "mov.b64 DB, {%3, %4};\n\t"
+      "setp.ne.b32 P, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], DA, DB, %5, P;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on the barrier at this shared-memory offset in every CTA of `cta_mask`
 // once the pair's MMAs issued so far retired.
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t cta_mask) {

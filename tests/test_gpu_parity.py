@@ -422,3 +422,41 @@ def test_streamed_matmul_from_pinned_host_memory(gpu):
         x.release()
     gpu.lib().gonngpu_host_free(pA)
     gpu.lib().gonngpu_host_free(pC)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 32), (512, 256, 200), (600, 400, 136), (130, 300, 2000),
+                                   (257, 129, 65), (2048, 1024, 4096)])
+@pytest.mark.parametrize("layout", ["nn", "tn", "nt", "tt"])
+def test_fp32_cta_pair_kernel(gpu, shape, layout):
+    """The fp32-accurate (3xTF32, chunk-promoted) kernel on CTA pairs, forced for
+    every shape; K up to 4096 to show that the error does not grow with K."""
+    m, n, k = shape
+    rng = np.random.default_rng(m * 13 + n * 7 + k)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    ta, tb = layout[0] == "t", layout[1] == "t"
+    As = np.ascontiguousarray(A.T) if ta else A
+    Bs = np.ascontiguousarray(B.T) if tb else B
+    try:
+        assert gpu.lib().gonngpu_set_gemm_pair_mode(1) == 0
+        C = run_matmul(gpu, As, Bs, ta, tb, precision=gpu.FP32_3XTF32)
+    finally:
+        gpu.lib().gonngpu_set_gemm_pair_mode(-1)
+    assert oracle.rel_frobenius(C, oracle.gemm_f64(As, Bs, ta, tb)) <= 2e-6
+
+
+def test_fp32_cta_pair_kernel_persistent_loop_and_epilogue(gpu):
+    rng = np.random.default_rng(91)
+    A = rng.integers(-3, 4, (2048, 160)).astype(np.float32)
+    B = rng.integers(-3, 4, (160, 768)).astype(np.float32)
+    bias = rng.integers(-5, 6, 768).astype(np.float32)
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    try:
+        gpu.lib().gonngpu_set_gemm_pair_mode(1)
+        gpu.lib().gonngpu_set_gemm_tuning(0, 4)      # 2 pairs walk 24 tiles
+        assert np.array_equal(run_matmul(gpu, A, B), ref.astype(np.float32))
+        gpu.lib().gonngpu_set_gemm_tuning(0, 0)
+        assert np.array_equal(run_matmul(gpu, A, B, bias=bias, act=0), np.maximum(ref + bias, 0).astype(np.float32))
+    finally:
+        gpu.lib().gonngpu_set_gemm_tuning(0, 0)
+        gpu.lib().gonngpu_set_gemm_pair_mode(-1)
