@@ -911,6 +911,235 @@ int gonngpu_convert_f16_device(const float* src, long rows, long cols, void* dst
   return finish(d, err, -6, "convert_f16_device");
 }
 
+int perform_batch_matmul_optimized(GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long batchSize, long M,
+                                   long N, long K, DevicePtr /*device*/, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* A = as_buffer(aPtr);
+  Buffer* B = as_buffer(bPtr);
+  Buffer* C = as_buffer(cPtr);
+  if (!A || !B || !C) {
+    set_error(err, "Invalid buffer pointers");
+    return -2;
+  }
+  if (batchSize <= 0 || M <= 0 || N <= 0 || K <= 0 || M >= (1l << 31) || N >= (1l << 31) ||
+      K >= (1l << 31) || batchSize * M >= (1l << 31) || batchSize * (K + 32) >= (1l << 31) ||
+      size_t(batchSize) * M * K * 4 > A->bytes || size_t(batchSize) * K * N * 4 > B->bytes ||
+      size_t(batchSize) * M * N * 4 > C->bytes || A->device != C->device || B->device != C->device ||
+      C == A || C == B) {
+    set_error(err, "batch matmul: invalid dimensions (batch %ld, M %ld, N %ld, K %ld).", batchSize, M, N,
+              K);
+    return -3;
+  }
+  if (ensure_device(C->device, err)) return -1;
+  Device& d = g_dev[C->device];
+  if (!make_resident(d, A) || !make_resident(d, B)) {
+    cudaGetLastError();
+    set_error(err, "batch matmul: host to device copy failed.");
+    return -6;
+  }
+  Plane* pa = get_plane(d, A, uint64_t(batchSize) * M, uint64_t(K), 2);
+  if (!pa) {
+    set_error(err, "batch matmul: could not allocate operand planes.");
+    return -3;
+  }
+  gonn::GemmOperand oa, ob;
+  oa.plane0 = pa->p0;
+  oa.plane1 = pa->p1;
+  oa.pitch = pa->pitch;
+  oa.mn_major = false;
+  ob.mn_major = true;
+  gonn::GemmBatch gb;
+  gb.count = uint32_t(batchSize);
+  void *thi = nullptr, *tlo = nullptr;
+  size_t tbytes = 0;
+  if (K % 32 == 0) {
+    // the stacked B is its own padded layout
+    Plane* pb = get_plane(d, B, uint64_t(batchSize) * K, uint64_t(N), 2);
+    if (!pb) {
+      set_error(err, "batch matmul: could not allocate operand planes.");
+      return -3;
+    }
+    ob.plane0 = pb->p0;
+    ob.plane1 = pb->p1;
+    ob.pitch = pb->pitch;
+    gb.b_rows = uint32_t(K);
+  } else {
+    // K is not a multiple of the k block: each batch of B gets zero rows up to the next
+    // multiple, so that a k block never reads into the following batch
+    const uint64_t kp = round_up(uint64_t(K), 32), pitch = round_up(uint64_t(N), 64);
+    tbytes = size_t(batchSize) * kp * pitch * 4;
+    if (pool_alloc(C->device, &thi, tbytes) != cudaSuccess ||
+        pool_alloc(C->device, &tlo, tbytes) != cudaSuccess) {
+      cudaGetLastError();
+      if (thi) pool_free(C->device, thi, tbytes);
+      set_error(err, "batch matmul: could not allocate operand planes.");
+      return -3;
+    }
+    cudaMemsetAsync(thi, 0, tbytes, d.stream);
+    cudaMemsetAsync(tlo, 0, tbytes, d.stream);
+    for (long b = 0; b < batchSize; ++b) {
+      gonn::launch_split_tf32(B->dptr + size_t(b) * K * N, uint64_t(K), uint64_t(N),
+                              static_cast<float*>(thi) + size_t(b) * kp * pitch,
+                              static_cast<float*>(tlo) + size_t(b) * kp * pitch, pitch, d.stream);
+      ++g_stats[3];
+    }
+    ob.plane0 = thi;
+    ob.plane1 = tlo;
+    ob.pitch = pitch;
+    gb.b_rows = uint32_t(kp);
+  }
+  gonn::GemmEpilogue epi;
+  const char* msg = gonn::launch_gemm(gonn::Kind::TF32x3, uint32_t(M), uint32_t(N), uint32_t(K), oa, ob,
+                                      C->dptr, uint64_t(N), epi, d.status_dev, d.sm_count, g_tune,
+                                      d.stream, &gb);
+  if (thi) {
+    pool_free(C->device, thi, tbytes);
+    pool_free(C->device, tlo, tbytes);
+  }
+  if (msg) {
+    cudaGetLastError();
+    set_error(err, "batch matmul: %s", msg);
+    return -3;
+  }
+  ++g_stats[3];
+  ++g_stats[4];
+  wrote(C);
+  return finish(d, err, -6, "batch matmul");
+}
+
+int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOutPtr, long batch,
+                            long in_size, long out_size, GPUPtr dxPtr, GPUPtr dwPtr, GPUPtr dbPtr,
+                            CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* X = as_buffer(xPtr);
+  Buffer* W = as_buffer(wPtr);
+  Buffer* dY = as_buffer(dyPtr);
+  Buffer* act = actOutPtr ? as_buffer(actOutPtr) : nullptr;
+  Buffer* dX = dxPtr ? as_buffer(dxPtr) : nullptr;
+  Buffer* dW = dwPtr ? as_buffer(dwPtr) : nullptr;
+  Buffer* db = dbPtr ? as_buffer(dbPtr) : nullptr;
+  if (!dY || (actOutPtr && !act) || (dxPtr && !dX) || (dwPtr && !dW) || (dbPtr && !db) ||
+      (dW && !X) || (dX && !W)) {
+    set_error(err, "Invalid input or output buffer pointers.");
+    return -2;
+  }
+  if (batch <= 0 || in_size <= 0 || out_size <= 0 || batch >= (1l << 31) || in_size >= (1l << 31) ||
+      out_size >= (1l << 31)) {
+    set_error(err, "linear backward: dimensions must be positive.");
+    return -3;
+  }
+  const size_t by = size_t(batch) * out_size * 4;
+  if (dY->bytes < by || (act && act->bytes < by) || (X && X->bytes < size_t(batch) * in_size * 4) ||
+      (W && W->bytes < size_t(in_size) * out_size * 4) ||
+      (dX && dX->bytes < size_t(batch) * in_size * 4) ||
+      (dW && dW->bytes < size_t(in_size) * out_size * 4) || (db && db->bytes < size_t(out_size) * 4)) {
+    set_error(err, "linear backward: a buffer is smaller than its stated matrix.");
+    return -3;
+  }
+  const int dev = dY->device;
+  for (Buffer* b : {X, W, act, dX, dW, db}) {
+    if (b && b->device != dev) {
+      set_error(err, "linear backward: buffers live on different devices.");
+      return -2;
+    }
+  }
+  if (ensure_device(dev, err)) return -1;
+  Device& d = g_dev[dev];
+  if (!make_resident(d, dY) || (act && !make_resident(d, act)) || (X && dW && !make_resident(d, X)) ||
+      (W && dX && !make_resident(d, W))) {
+    cudaGetLastError();
+    set_error(err, "linear backward: host to device copy failed.");
+    return -6;
+  }
+  // bias gradient: column sums of the masked gradient
+  if (db) {
+    gonn::launch_colsum(dY->dptr, uint64_t(batch), uint64_t(out_size), db->dptr, d.stream,
+                        act ? act->dptr : nullptr);
+    ++g_stats[3];
+    wrote(db);
+  }
+  int rc = 0;
+  if (dX || dW) {
+    // operand planes of dAct = dY (.) [actOut > 0]: the mask is applied while the
+    // planes are written, the masked gradient itself is never stored
+    const uint64_t pitch = round_up(uint64_t(out_size), 64);
+    const size_t pbytes = size_t(batch) * pitch * 4;
+    void *hi = nullptr, *lo = nullptr;
+    if (pool_alloc(dev, &hi, pbytes) != cudaSuccess || pool_alloc(dev, &lo, pbytes) != cudaSuccess) {
+      cudaGetLastError();
+      if (hi) pool_free(dev, hi, pbytes);
+      set_error(err, "linear backward: could not allocate operand planes.");
+      return -5;
+    }
+    gonn::launch_split_tf32(dY->dptr, uint64_t(batch), uint64_t(out_size), static_cast<float*>(hi),
+                            static_cast<float*>(lo), pitch, d.stream, act ? act->dptr : nullptr);
+    ++g_stats[3];
+    gonn::GemmOperand g;  // dAct stored [batch, out]
+    g.plane0 = hi;
+    g.plane1 = lo;
+    g.pitch = pitch;
+    gonn::GemmEpilogue epi;
+    const char* msg = nullptr;
+    if (dW) {
+      // dW[in, out] = X^T . dAct : A = X stored [batch(K), in(M)], B = dAct stored [batch(K), out(N)]
+      Plane* px = get_plane(d, X, uint64_t(batch), uint64_t(in_size), 2);
+      if (!px) {
+        msg = "could not allocate operand planes";
+      } else {
+        gonn::GemmOperand a;
+        a.plane0 = px->p0;
+        a.plane1 = px->p1;
+        a.pitch = px->pitch;
+        a.mn_major = true;
+        gonn::GemmOperand b = g;
+        b.mn_major = true;
+        msg = gonn::launch_gemm(gonn::Kind::TF32x3, uint32_t(in_size), uint32_t(out_size),
+                                uint32_t(batch), a, b, dW->dptr, uint64_t(out_size), epi, d.status_dev,
+                                d.sm_count, g_tune, d.stream);
+        if (!msg) {
+          ++g_stats[3];
+          ++g_stats[4];
+          wrote(dW);
+        }
+      }
+    }
+    if (!msg && dX) {
+      // dX[batch, in] = dAct . W^T : A = dAct stored [batch(M), out(K)], B = W stored [in(N), out(K)]
+      Plane* pw = get_plane(d, W, uint64_t(in_size), uint64_t(out_size), 2);
+      if (!pw) {
+        msg = "could not allocate operand planes";
+      } else {
+        gonn::GemmOperand a = g;
+        a.mn_major = false;
+        gonn::GemmOperand b;
+        b.plane0 = pw->p0;
+        b.plane1 = pw->p1;
+        b.pitch = pw->pitch;
+        b.mn_major = false;
+        msg = gonn::launch_gemm(gonn::Kind::TF32x3, uint32_t(batch), uint32_t(in_size),
+                                uint32_t(out_size), a, b, dX->dptr, uint64_t(in_size), epi,
+                                d.status_dev, d.sm_count, g_tune, d.stream);
+        if (!msg) {
+          ++g_stats[3];
+          ++g_stats[4];
+          wrote(dX);
+        }
+      }
+    }
+    // The planes go back to the cache; later work on the same stream may reuse them
+    // only after the GEMMs above (stream order).
+    pool_free(dev, hi, pbytes);
+    pool_free(dev, lo, pbytes);
+    if (msg) {
+      cudaGetLastError();
+      set_error(err, "linear backward: %s", msg);
+      rc = -4;
+    }
+  }
+  const int frc = finish(d, err && rc == 0 ? err : nullptr, -6, "linear backward");
+  return rc ? rc : frc;
+}
+
 int gonngpu_column_sum(GPUPtr inPtr, long rows, long cols, GPUPtr outPtr, CError* err) {
   std::lock_guard<std::recursive_mutex> lk(g_mu);
   Buffer* in = as_buffer(inPtr);

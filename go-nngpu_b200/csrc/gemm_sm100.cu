@@ -60,6 +60,10 @@ struct KernelParams {
   int act;
   uint32_t vec_store;  // C base and pitch allow 16-byte stores
   uint32_t tma_store;  // epilogue may write C with TMA stores (no beta term, aligned C)
+  // batched products (stacked matrices): tiles per batch (0 = one product), and the
+  // row-coordinate step per batch of the A and B tensor maps; M is then per batch
+  uint32_t batch_tiles;
+  int32_t a_batch_c1, b_batch_c1;
   GemmStatus* status;
 };
 
@@ -74,6 +78,13 @@ __device__ __forceinline__ void tile_coords(const KernelParams& p, uint32_t t, u
   const uint32_t r = t - g * per_group;
   tm = first_m + r % gm;
   tn = r / gm;
+}
+
+// Batched products: tiles are numbered batch by batch.
+__device__ __forceinline__ void tile_coords(const KernelParams& p, uint32_t t, uint32_t& tm,
+                                            uint32_t& tn, uint32_t& batch) {
+  batch = p.batch_tiles ? t / p.batch_tiles : 0u;
+  tile_coords(p, t - batch * p.batch_tiles, tm, tn);
 }
 
 __device__ __forceinline__ float apply_act(float v, int act, float param) {
@@ -1108,7 +1119,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
     bool alive = true;
     for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
       uint32_t tm, tn;
-      tile_coords(p, t, tm, tn);
+      uint32_t bt;
+      tile_coords(p, t, tm, tn, bt);
       for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
         bool ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -1131,7 +1143,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
               ptx::tma_load_2d(dst + s * p.a.slab_bytes, ma,
                                int32_t(tm) * p.a.c0_tile + int32_t(s) * p.a.c0_slab +
                                    int32_t(kb) * p.a.c0_k,
-                               int32_t(tm) * p.a.c1_tile + int32_t(kb) * p.a.c1_k, fb);
+                               int32_t(tm) * p.a.c1_tile + int32_t(kb) * p.a.c1_k +
+                                   int32_t(bt) * p.a_batch_c1,
+                               fb);
             }
             dst += A_TILE_BYTES;
           }
@@ -1142,7 +1156,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
               ptx::tma_load_2d(dst + s * p.b.slab_bytes, mb,
                                int32_t(tn) * p.b.c0_tile + int32_t(s) * p.b.c0_slab +
                                    int32_t(kb) * p.b.c0_k,
-                               int32_t(tn) * p.b.c1_tile + int32_t(kb) * p.b.c1_k, fb);
+                               int32_t(tn) * p.b.c1_tile + int32_t(kb) * p.b.c1_k +
+                                   int32_t(bt) * p.b_batch_c1,
+                               fb);
             }
             dst += B_TILE_BYTES;
           }
@@ -1223,7 +1239,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
     bool alive = true;
     for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
       uint32_t tm, tn;
-      tile_coords(p, t, tm, tn);
+      uint32_t bt;
+      tile_coords(p, t, tm, tn, bt);
       float sums[NC];
 #pragma unroll
       for (int i = 0; i < NC; ++i) sums[i] = 0.f;
@@ -1247,11 +1264,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
         if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
       }
       if (!alive) break;
-      const uint32_t row = tm * BLOCK_M + quarter * 32u + lane;
+      const uint32_t row = tm * BLOCK_M + quarter * 32u + lane;  // within its batch
+      const uint64_t grow = uint64_t(bt) * p.M + row;            // in the stacked C
       const uint32_t col0 = tn * BLOCK_N + half * NC;
       if (row < p.M && col0 < p.N) {
-        float* c_row = p.C + uint64_t(row) * p.ldc;
-        const float* cin_row = p.c_in ? p.c_in + uint64_t(row) * p.ldc : nullptr;
+        float* c_row = p.C + grow * p.ldc;
+        const float* cin_row = p.c_in ? p.c_in + grow * p.ldc : nullptr;
         if (col0 + NC <= p.N && p.vec_store) {
 #pragma unroll
           for (int j = 0; j < NC; j += 4) {
@@ -1860,8 +1878,10 @@ const char* launch_tf32_pair(uint32_t M, uint32_t N, uint32_t K, const GemmOpera
 const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const GemmOperand& A,
                         const GemmOperand& B, float* C, uint64_t ldc, const GemmEpilogue& epi,
                         GemmStatus* status, int sm_count, const GemmTuning& tune,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const GemmBatch* batch) {
   if (M == 0 || N == 0 || K == 0) return "GEMM dimensions must be positive";
+  if (batch && (kind != Kind::TF32x3 || A.mn_major || !B.mn_major || batch->count == 0))
+    return "batched GEMM supports fp32 A[b,M,K].B[b,K,N] only";
   const bool f32 = (kind == Kind::TF32x3);
   const uint32_t esz = f32 ? 4 : 2;
   const uint32_t block_k = SLAB_ROW_BYTES / esz;
@@ -1870,7 +1890,9 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
     return "operand planes must be 16-byte aligned";
   if (f32 && (!A.plane1 || !B.plane1)) return "TF32x3 needs the low planes";
 
-  int bn = tune.block_n ? tune.block_n : choose_block_n(kind, M, N, K, sm_count);
+  // (for a batched product the tiles of all batches fill the machine together)
+  int bn = tune.block_n ? tune.block_n
+                        : choose_block_n(kind, batch ? M * batch->count : M, N, K, sm_count);
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return "unsupported BLOCK_N";
   // An N-major fp16 tile narrower than one 128-byte swizzle row (64 columns)
   // would need the 64-byte swizzle; use the 64-wide tile instead.
@@ -1921,7 +1943,7 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
     }
   }
 
-  if (kind == Kind::TF32x3 && tune.pair != 0 && (tune.block_n == 0 || tune.block_n == 256)) {
+  if (kind == Kind::TF32x3 && !batch && tune.pair != 0 && (tune.block_n == 0 || tune.block_n == 256)) {
     const uint64_t pair_tiles = uint64_t((M + 255) / 256) * ((N + 255) / 256);
     if (tune.pair >= 1 || (M >= 256 && N >= 128 && pair_tiles >= uint64_t(sm_count) / 2))
       return launch_tf32_pair(M, N, K, A, B, kp, sm_count, tune.max_ctas, stream);
@@ -1932,8 +1954,18 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
   std::memset(maps, 0, sizeof(maps));
   const uint32_t a_box_rows = A.mn_major ? block_k : BLOCK_M;
   const uint32_t b_box_rows = B.mn_major ? block_k : uint32_t(bn);
-  const uint64_t a_inner = A.mn_major ? M : K, a_outer = A.mn_major ? K : M;
-  const uint64_t b_inner = B.mn_major ? N : K, b_outer = B.mn_major ? K : N;
+  uint64_t a_inner = A.mn_major ? M : K, a_outer = A.mn_major ? K : M;
+  uint64_t b_inner = B.mn_major ? N : K, b_outer = B.mn_major ? K : N;
+  if (batch) {
+    // stacked matrices: A is [count*M, K]; B is [count*b_rows, N] with b_rows >= K rows per
+    // batch, the rows past K zero; tiles are numbered batch by batch
+    a_outer = uint64_t(batch->count) * M;
+    b_outer = uint64_t(batch->count) * batch->b_rows;
+    kp.batch_tiles = kp.num_tiles;
+    kp.num_tiles *= batch->count;
+    kp.a_batch_c1 = int32_t(M);
+    kp.b_batch_c1 = int32_t(batch->b_rows);
+  }
   if (!make_map(&maps[0], f32, A.plane0, a_inner, a_outer, A.pitch, a_box_rows, A.mn_major) ||
       !make_map(&maps[2], f32, B.plane0, b_inner, b_outer, B.pitch, b_box_rows, B.mn_major))
     return "cuTensorMapEncodeTiled failed";

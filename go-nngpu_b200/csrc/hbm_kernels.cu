@@ -132,7 +132,12 @@ __device__ __forceinline__ float rna_tf32(float x) {
   return __uint_as_float(r);
 }
 
+// `mask` (optional, same shape as src): elements whose mask value is not > 0 are
+// taken as zero - the ReLU derivative of
+// internal/cgo/metal_bridge_activation.m:74-77 applied while the operand planes
+// of the backward GEMMs are written, so the masked gradient never exists in HBM.
 __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ src,
+                                                         const float* __restrict__ mask,
                                                          uint64_t rows, uint64_t cols,
                                                          float* __restrict__ hi,
                                                          float* __restrict__ lo, uint64_t pitch,
@@ -142,7 +147,14 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
     for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
          i += uint64_t(gridDim.x) * blockDim.x) {
       const uint64_t r = i / q, c = (i - r * q) << 2;
-      const float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * cols + c));
+      float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * cols + c));
+      if (mask) {
+        const float4 m = __ldcs(reinterpret_cast<const float4*>(mask + r * cols + c));
+        v.x = m.x > 0.0f ? v.x : 0.0f;
+        v.y = m.y > 0.0f ? v.y : 0.0f;
+        v.z = m.z > 0.0f ? v.z : 0.0f;
+        v.w = m.w > 0.0f ? v.w : 0.0f;
+      }
       float4 h, l;
       h.x = rna_tf32(v.x); l.x = rna_tf32(v.x - h.x);
       h.y = rna_tf32(v.y); l.y = rna_tf32(v.y - h.y);
@@ -156,7 +168,8 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
     for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
          i += uint64_t(gridDim.x) * blockDim.x) {
       const uint64_t r = i / cols, c = i - r * cols;
-      const float x = src[i];
+      float x = src[i];
+      if (mask && !(mask[i] > 0.0f)) x = 0.0f;
       const float h = rna_tf32(x);
       hi[r * pitch + c] = h;
       lo[r * pitch + c] = rna_tf32(x - h);
@@ -203,14 +216,18 @@ __global__ void __launch_bounds__(256) relu_bwd_kernel(const float* __restrict__
 
 // Column sum (bias gradient, gpu/matrix/layers.go:281-294): rows are added in
 // index order per partial, partials in order, so the result is deterministic.
-__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ in, uint64_t rows,
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ in,
+                                                     const float* __restrict__ mask, uint64_t rows,
                                                      uint64_t cols, float* __restrict__ out) {
   __shared__ float part[8][33];
   const uint32_t cx = threadIdx.x & 31u, ry = threadIdx.x >> 5;
   const uint64_t col = blockIdx.x * 32ull + cx;
   float s = 0.f;
   if (col < cols)
-    for (uint64_t r = ry; r < rows; r += 8) s += in[r * cols + col];
+    for (uint64_t r = ry; r < rows; r += 8) {
+      const float v = in[r * cols + col];
+      s += (!mask || mask[r * cols + col] > 0.0f) ? v : 0.0f;
+    }
   part[ry][cx] = s;
   __syncthreads();
   if (ry == 0 && col < cols) {
@@ -258,12 +275,13 @@ void launch_cvt_f16(const float* src, uint64_t rows, uint64_t cols, void* dst, u
 }
 
 void launch_split_tf32(const float* src, uint64_t rows, uint64_t cols, float* hi, float* lo,
-                       uint64_t pitch, cudaStream_t stream) {
+                       uint64_t pitch, cudaStream_t stream, const float* mask) {
   if (rows == 0 || cols == 0) return;
-  const int vec = (cols % 4 == 0) && aligned16(src) && aligned16(hi) && aligned16(lo) && (pitch % 4 == 0);
+  const int vec = (cols % 4 == 0) && aligned16(src) && aligned16(hi) && aligned16(lo) &&
+                  (pitch % 4 == 0) && (!mask || aligned16(mask));
   const uint64_t items = vec ? rows * (cols / 4) : rows * cols;
-  split_tf32_kernel<<<stream_grid(items, 256, 148 * 16), 256, 0, stream>>>(src, rows, cols, hi, lo,
-                                                                           pitch, vec);
+  split_tf32_kernel<<<stream_grid(items, 256, 148 * 16), 256, 0, stream>>>(src, mask, rows, cols, hi,
+                                                                           lo, pitch, vec);
 }
 
 void launch_add_broadcast(const float* a, const float* b, float* c, uint64_t rows, uint64_t cols,
@@ -284,9 +302,10 @@ void launch_relu_backward(const float* grad_out, const float* act_out, float* gr
   relu_bwd_kernel<<<stream_grid(n, 256, 148 * 16), 256, 0, stream>>>(grad_out, act_out, grad_in, n);
 }
 
-void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream) {
+void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream,
+                   const float* mask) {
   if (cols == 0) return;
-  colsum_kernel<<<uint32_t((cols + 31) / 32), 256, 0, stream>>>(in, rows, cols, out);
+  colsum_kernel<<<uint32_t((cols + 31) / 32), 256, 0, stream>>>(in, mask, rows, cols, out);
 }
 
 }  // namespace gonn

@@ -53,13 +53,21 @@ struct GemmTuning {
   int pair = -1;     // fp16 CTA-pair kernel: -1 = choose by size, 0 = never, 1 = always
 };
 
+// Batched product C[b] = A[b].B[b] over stacked matrices (fp32 path, A[b,M,K] and
+// B[b,K,N] layouts only).  The B planes hold `b_rows` >= K rows per batch, a
+// multiple of the 32-row k block, the rows past K zero.
+struct GemmBatch {
+  uint32_t count = 1;
+  uint32_t b_rows = 0;
+};
+
 // Enqueues the GEMM on `stream`.  Returns nullptr on success, else a static
 // message.  `status` is device memory holding one GemmStatus, zeroed by the
 // caller before the launch.
 const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const GemmOperand& A,
                         const GemmOperand& B, float* C, uint64_t ldc, const GemmEpilogue& epi,
                         GemmStatus* status, int sm_count, const GemmTuning& tune,
-                        cudaStream_t stream);
+                        cudaStream_t stream, const GemmBatch* batch = nullptr);
 
 // ---- pre-pass: operand planes ---------------------------------------------
 enum F16Mode : int { F16_RN = 0, F16_TRUNC = 1 };
@@ -67,8 +75,9 @@ enum F16Mode : int { F16_RN = 0, F16_TRUNC = 1 };
 void launch_cvt_f16(const float* src, uint64_t rows, uint64_t cols, void* dst, uint64_t pitch,
                     int mode, cudaStream_t stream);
 // fp32 -> (hi, lo) tf32 planes: hi = rna_tf32(x), lo = rna_tf32(x - hi).
+// With `mask` (same shape as src): x is taken as 0 where mask <= 0 (ReLU derivative).
 void launch_split_tf32(const float* src, uint64_t rows, uint64_t cols, float* hi, float* lo,
-                       uint64_t pitch, cudaStream_t stream);
+                       uint64_t pitch, cudaStream_t stream, const float* mask = nullptr);
 
 // ---- HBM-bound kernels -----------------------------------------------------
 void launch_transpose(const float* in, uint64_t rows, uint64_t cols, float* out, int sm_count,
@@ -80,6 +89,7 @@ void launch_relu_forward(const float* in, float* out, uint64_t n, cudaStream_t s
 void launch_relu_backward(const float* grad_out, const float* act_out, float* grad_in, uint64_t n,
                           cudaStream_t stream);
 // out[j] = sum_i in[i, j]   (bias gradient)
-void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream);
+void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream,
+                   const float* mask = nullptr);
 
 }  // namespace gonn

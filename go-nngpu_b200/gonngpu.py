@@ -49,6 +49,8 @@ SIGNATURES = {
         _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _vp, _c_int, _c_float, _vp, _vp, _errp]),
     "perform_optimized_gemm": (
         _c_int, [_vp, _vp, _vp, _c_long, _c_long, _c_long, _c_float, _c_float, _vp, _errp]),
+    "perform_batch_matmul_optimized": (
+        _c_int, [_vp, _vp, _vp, _c_long, _c_long, _c_long, _c_long, _vp, _errp]),
     "allocateSharedMemory": (_vp, [_c_long]),
     "createGPUBufferFromSharedMemory": (_vp, [_vp, _vp, _c_long]),
     "gonngpu_matmul_ex": (
@@ -60,6 +62,8 @@ SIGNATURES = {
     "gonngpu_convert_f16_device": (_c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_int, _errp]),
     "gonngpu_matmul_f16_static_scratch": (
         _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _vp, _errp]),
+    "gonngpu_linear_backward": (
+        _c_int, [_vp, _vp, _vp, _vp, _c_long, _c_long, _c_long, _vp, _vp, _vp, _errp]),
     "gonngpu_column_sum": (_c_int, [_vp, _c_long, _c_long, _vp, _errp]),
     "gonngpu_alloc_device_buffer": (_c_int, [_c_long, ctypes.POINTER(_vp), _errp]),
     "gonngpu_wrap_device_memory": (_c_int, [_vp, _c_long, ctypes.POINTER(_vp), _errp]),
@@ -246,6 +250,19 @@ def matmul_f16_static_scratch(a_ptr, a_shape, b_ptr, b_shape, c_ptr, stream=None
     _check(lib().gonngpu_matmul_f16_static_scratch(
         _vp(a_ptr), a_shape[0], a_shape[1], _vp(b_ptr), b_shape[0], b_shape[1], _vp(c_ptr),
         _vp(stream) if stream else None, ctypes.byref(err)), err)
+
+
+def linear_backward(x, w, dy, act_out, batch, in_size, out_size, dx=None, dw=None, db=None):
+    err = CError()
+    h = lambda b: b.handle if b is not None else None  # noqa: E731
+    _check(lib().gonngpu_linear_backward(h(x), h(w), h(dy), h(act_out), batch, in_size, out_size,
+                                         h(dx), h(dw), h(db), ctypes.byref(err)), err)
+
+
+def batch_matmul(a, b, c, batch, m, n, k):
+    err = CError()
+    _check(lib().perform_batch_matmul_optimized(a.handle, b.handle, c.handle, batch, m, n, k, None,
+                                                ctypes.byref(err)), err)
 
 
 def column_sum(inp, rows, cols, out):

@@ -350,6 +350,67 @@ inline TensorPtr MatMulTransposed(const TensorPtr& A, bool transA, const TensorP
   return result;
 }
 
+// gpu/matrix/optimized-kernels.go:78-135.  A[batch,M,K] . B[batch,K,N] -> [batch,M,N].
+inline TensorPtr OptimizedBatchMatMul(const TensorPtr& A, const TensorPtr& B) {
+  if (A->Shape.size() != 3 || B->Shape.size() != 3)
+    throw gonngpu::Error("batch matrix multiplication requires 3D tensors");
+  const int batch = A->Shape[0], M = A->Shape[1], K = A->Shape[2], K2 = B->Shape[1], N = B->Shape[2];
+  if (A->Shape[0] != B->Shape[0])
+    throw gonngpu::Error("batch sizes don't match: " + std::to_string(A->Shape[0]) + " vs " +
+                         std::to_string(B->Shape[0]));
+  if (K != K2)
+    throw gonngpu::Error("matrix dimensions don't match: K=" + std::to_string(K) +
+                         " vs K2=" + std::to_string(K2));
+  TensorPtr out = tensor::NewTensor({batch, M, N}, std::vector<float>(size_t(batch) * M * N));
+  A->EnsureGPU();
+  B->EnsureGPU();
+  out->EnsureGPU();
+  CError err{nullptr};
+  const int rc = perform_batch_matmul_optimized(A->GPUPointer(), B->GPUPointer(), out->GPUPointer(),
+                                                batch, M, N, K, A->DevicePointer(), &err);
+  if (rc != 0)
+    throw gonngpu::Error("optimized batch matrix multiplication failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return out;
+}
+
+// The three gradients of a linear layer in one call: what LinearLayer.Backward
+// (layers.go:77-96) computes with two Transposes, two MatMuls and sumAlongAxis,
+// preceded, when `activationOutput` is given, by ReLULayer.Backward
+// (layers.go:133-142).  Returns {gradInput, gradWeight, gradBias}.
+struct LinearGradients {
+  TensorPtr Input, Weight, Bias;
+};
+inline LinearGradients LinearBackward(const TensorPtr& input, const TensorPtr& weight,
+                                      const TensorPtr& gradOutput,
+                                      const TensorPtr& activationOutput = nullptr) {
+  if (input->Shape.size() != 2 || weight->Shape.size() != 2 || gradOutput->Shape.size() != 2 ||
+      input->Shape[1] != weight->Shape[0] || gradOutput->Shape[0] != input->Shape[0] ||
+      gradOutput->Shape[1] != weight->Shape[1])
+    throw gonngpu::Error("LinearBackward: shapes of input, weight and gradOutput do not match");
+  const int batch = input->Shape[0], in = input->Shape[1], out = weight->Shape[1];
+  LinearGradients g;
+  g.Input = tensor::NewTensor({batch, in}, std::vector<float>(size_t(batch) * in));
+  g.Weight = tensor::NewTensor({in, out}, std::vector<float>(size_t(in) * out));
+  g.Bias = tensor::NewTensor({out}, std::vector<float>(size_t(out)));
+  input->EnsureGPU();
+  weight->EnsureGPU();
+  gradOutput->EnsureGPU();
+  if (activationOutput) activationOutput->EnsureGPU();
+  g.Input->EnsureGPU();
+  g.Weight->EnsureGPU();
+  g.Bias->EnsureGPU();
+  CError err{nullptr};
+  const int rc = gonngpu_linear_backward(
+      input->GPUPointer(), weight->GPUPointer(), gradOutput->GPUPointer(),
+      activationOutput ? activationOutput->GPUPointer() : nullptr, batch, in, out,
+      g.Input->GPUPointer(), g.Weight->GPUPointer(), g.Bias->GPUPointer(), &err);
+  if (rc != 0)
+    throw gonngpu::Error("GPU matrix multiplication failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return g;
+}
+
 // ---- gpu/matrix/mixed-precision.go ---------------------------------------------------
 using FloatMP16 = uint16_t;
 

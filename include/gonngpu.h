@@ -118,6 +118,13 @@ GONNGPU_API int perform_fused_linear_activation(GPUPtr input, long batch_size, l
 GONNGPU_API int perform_optimized_gemm(GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long M, long N, long K,
                            float alpha, float beta, DevicePtr mtlDevicePtr, CError *err);
 
+/* metal_bridge.h:1432-1437.  C[b] = A[b] . B[b] for b < batchSize over the
+ * contiguous stacks A[batch,M,K], B[batch,K,N], C[batch,M,N] (fp32, computed like
+ * the single product); one launch walks the tiles of every batch.
+ * Errors: -1 device, -2 bad buffer, -3 dimensions or kernel set-up, -6 execution. */
+GONNGPU_API int perform_batch_matmul_optimized(GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long batchSize, long M,
+                                   long N, long K, DevicePtr mtlDevicePtr, CError *err);
+
 /* metal_bridge.h:1803.  Host memory for the reference's unified-memory
  * adapter: page-locked, zero-filled, 16 KiB aligned; NULL on failure.  Freed by
  * gonngpu_host_free(). */
@@ -182,6 +189,21 @@ GONNGPU_API int gonngpu_convert_f16_device(const float *src, long rows, long col
 #define GONNGPU_STATIC_SCRATCH_BYTES (32l << 20)
 GONNGPU_API int gonngpu_matmul_f16_static_scratch(const float *a, long aRows, long aCols, const float *b,
                                       long bRows, long bCols, float *c, void *stream, CError *err);
+
+/* Backward pass of a linear layer Y = act(X.W + b), all three gradients in one
+ * call (replaces, in gpu/matrix/layers.go:77-96,139-141 and
+ * fused-operations.go:467-578, ReLUBackward + Transpose + MatMul + Transpose +
+ * MatMul + sumAlongAxis):
+ *   dAct = dY (.) [actOut > 0]   when actOut is non-NULL (ReLU derivative,
+ *                                metal_bridge_activation.m:74-77), else dY
+ *   dW[in,out] = X^T . dAct,  dX[batch,in] = dAct . W^T,  db[out] = column sums of dAct
+ * x is [batch,in], w is [in,out], dy and actOut are [batch,out].  Any of dx, dw,
+ * db may be NULL (x may be NULL when dw is, w when dx is).  The mask is applied
+ * while the tensor-core operand planes of dY are written, so the masked
+ * gradient is never materialised; both GEMMs read their operands transposed in
+ * place (fp32 accuracy, 3xTF32).  Errors as perform_mps_matrix_multiplication. */
+GONNGPU_API int gonngpu_linear_backward(GPUPtr x, GPUPtr w, GPUPtr dy, GPUPtr actOut, long batch, long in_size,
+                            long out_size, GPUPtr dx, GPUPtr dw, GPUPtr db, CError *err);
 
 /* out[j] = sum_i in[i,j] (bias gradient, gpu/matrix/layers.go:281-294). */
 GONNGPU_API int gonngpu_column_sum(GPUPtr in, long rows, long cols, GPUPtr out, CError *err);

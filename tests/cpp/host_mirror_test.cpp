@@ -148,6 +148,55 @@ static void with_gpu() {
   auto back = recv->T()->ToGonum();
   CHECK(back->Dims().first == N && std::fabs(back->At(4, 3) - ref[size_t(3) * N + 4]) <= 1e-4);
 
+  // batched product over 3-D tensors
+  {
+    const int nb = 3, bm = 40, bk = 50, bn = 24;
+    std::vector<float> bA(size_t(nb) * bm * bk), bB(size_t(nb) * bk * bn);
+    for (auto& x : bA) x = u(rng);
+    for (auto& x : bB) x = u(rng);
+    auto tbA = tensor::NewTensor({nb, bm, bk}, bA), tbB = tensor::NewTensor({nb, bk, bn}, bB);
+    auto tbC = matrix::OptimizedBatchMatMul(tbA, tbB);
+    tbC->RetrieveCPU();
+    for (int b = 0; b < nb; ++b) {
+      std::vector<float> a1(bA.begin() + size_t(b) * bm * bk, bA.begin() + size_t(b + 1) * bm * bk);
+      std::vector<float> b1(bB.begin() + size_t(b) * bk * bn, bB.begin() + size_t(b + 1) * bk * bn);
+      std::vector<float> c1(tbC->Data.begin() + size_t(b) * bm * bn, tbC->Data.begin() + size_t(b + 1) * bm * bn);
+      CHECK(rel_frob(c1, ref_gemm(a1, b1, bm, bk, bn)) <= 1e-5);
+    }
+    try {
+      matrix::OptimizedBatchMatMul(tA, tB);
+      CHECK(false);
+    } catch (const gonngpu::Error& e) {
+      CHECK(std::string(e.what()) == "batch matrix multiplication requires 3D tensors");
+    }
+  }
+
+  // linear layer backward in one call, with the ReLU mask of the layer's output
+  {
+    std::vector<float> dY(size_t(M) * N), act(size_t(M) * N);
+    for (auto& x : dY) x = u(rng);
+    for (auto& x : act) x = std::max(0.f, u(rng));
+    auto tdY = tensor::NewTensor({M, N}, dY), tact = tensor::NewTensor({M, N}, act);
+    auto g = matrix::LinearBackward(tA, tB, tdY, tact);
+    g.Input->RetrieveCPU();
+    g.Weight->RetrieveCPU();
+    g.Bias->RetrieveCPU();
+    std::vector<double> dAct(size_t(M) * N), dW(size_t(K) * N, 0.0), dX(size_t(M) * K, 0.0), dbias(N, 0.0);
+    for (size_t i = 0; i < dAct.size(); ++i) dAct[i] = act[i] > 0.f ? dY[i] : 0.0;
+    for (int i = 0; i < M; ++i)
+      for (int j = 0; j < N; ++j) {
+        const double gv = dAct[size_t(i) * N + j];
+        dbias[j] += gv;
+        for (int k = 0; k < K; ++k) {
+          dW[size_t(k) * N + j] += double(A[size_t(i) * K + k]) * gv;
+          dX[size_t(i) * K + k] += gv * double(B[size_t(k) * N + j]);
+        }
+      }
+    CHECK(rel_frob(g.Weight->Data, dW) <= 1e-5);
+    CHECK(rel_frob(g.Input->Data, dX) <= 1e-5);
+    CHECK(rel_frob(g.Bias->Data, dbias) <= 1e-5);
+  }
+
   // modifying Data after RetrieveCPU is seen by the next device op (aliasing
   // semantics the eager layers rely on, layers.go:271-279)
   tC->Data[0] = 1234.0f;

@@ -460,3 +460,79 @@ def test_fp32_cta_pair_kernel_persistent_loop_and_epilogue(gpu):
     finally:
         gpu.lib().gonngpu_set_gemm_tuning(0, 0)
         gpu.lib().gonngpu_set_gemm_pair_mode(-1)
+
+
+# ------------------------------------------------------------------ fused linear backward
+@pytest.mark.parametrize("shape", [(1, 1, 1), (33, 70, 10), (130, 257, 99), (512, 784, 1024)])
+@pytest.mark.parametrize("masked", [False, True])
+def test_linear_backward_matches_unfused_oracle(gpu, shape, masked):
+    """dW, dX, db of a linear layer in one call against the reference's unfused
+    chain (ReLU backward, Transpose + MatMul twice, column sums) done by the oracle."""
+    batch, fin, fout = shape
+    rng = np.random.default_rng(batch * 3 + fin * 5 + fout * 7 + masked)
+    X = rng.uniform(0, 1, (batch, fin)).astype(np.float32)
+    W = (rng.standard_normal((fin, fout)) * np.sqrt(2.0 / fin)).astype(np.float32)
+    dY = (rng.standard_normal((batch, fout)) * 1e-2).astype(np.float32)
+    act = np.maximum(rng.standard_normal((batch, fout)), 0).astype(np.float32) if masked else None
+    dAct = oracle.relu_backward(dY, act) if masked else dY
+    x, w, dy = gpu.Buffer.from_host(X), gpu.Buffer.from_host(W), gpu.Buffer.from_host(dY)
+    a = gpu.Buffer.from_host(act) if masked else None
+    dx, dw, db = gpu.Buffer.empty(X.nbytes), gpu.Buffer.empty(W.nbytes), gpu.Buffer.empty(fout * 4)
+    gpu.linear_backward(x, w, dy, a, batch, fin, fout, dx=dx, dw=dw, db=db)
+    assert oracle.rel_frobenius(dw.retrieve(W.shape), oracle.gemm_f64(X, dAct, True, False)) <= FP32_TOL
+    assert oracle.rel_frobenius(dx.retrieve(X.shape), oracle.gemm_f64(dAct, W, False, True)) <= FP32_TOL
+    ref_db = dAct.astype(np.float64).sum(axis=0)
+    assert np.allclose(db.retrieve((fout,)), ref_db, rtol=1e-5, atol=1e-6 * max(1.0, np.abs(ref_db).max()))
+    # partial requests
+    dw2 = gpu.Buffer.empty(W.nbytes)
+    gpu.linear_backward(x, None, dy, a, batch, fin, fout, dw=dw2)
+    assert np.array_equal(dw2.retrieve(W.shape), dw.retrieve(W.shape))
+    with pytest.raises(gpu.GonnError) as e:
+        gpu.linear_backward(None, w, dy, a, batch, fin, fout, dw=dw2)   # dW needs X
+    assert e.value.code == -2
+
+
+def test_config3_training_step_with_fused_calls(gpu):
+    """The MLP step of configuration 3 as 3 fused forward calls and 3 fused
+    backward calls (the ReLU mask of the hidden layers applied inside)."""
+    X, Ws, bs, dYs = oracle.config3()
+    acts = [X]
+    for layer in range(3):
+        acts.append(run_matmul(gpu, acts[-1], Ws[layer], bias=bs[layer], act=0 if layer < 2 else -1))
+    grad = dYs[2]                                   # gradient arriving at the output layer
+    for layer in (2, 1, 0):
+        h_in, W = acts[layer], Ws[layer]
+        mask = acts[layer + 1] if layer < 2 else None
+        x, w, dy = gpu.Buffer.from_host(h_in), gpu.Buffer.from_host(W), gpu.Buffer.from_host(grad)
+        m = gpu.Buffer.from_host(mask) if mask is not None else None
+        dx, dw, db = gpu.Buffer.empty(h_in.nbytes), gpu.Buffer.empty(W.nbytes), gpu.Buffer.empty(W.shape[1] * 4)
+        gpu.linear_backward(x, w, dy, m, h_in.shape[0], W.shape[0], W.shape[1], dx=dx, dw=dw, db=db)
+        dAct = oracle.relu_backward(grad, mask) if mask is not None else grad
+        assert oracle.rel_frobenius(dw.retrieve(W.shape), oracle.gemm_f64(h_in, dAct, True, False)) <= FP32_TOL
+        got_dx = dx.retrieve(h_in.shape)
+        assert oracle.rel_frobenius(got_dx, oracle.gemm_f64(dAct, W, False, True)) <= FP32_TOL
+        grad = got_dx
+
+
+# ------------------------------------------------------------------ batched product
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1), (3, 5, 7, 9), (4, 128, 64, 32), (5, 130, 70, 33),
+                                   (16, 200, 96, 100), (64, 64, 64, 64), (2, 512, 1024, 784)])
+def test_batch_matmul_matches_per_batch_oracle(gpu, shape):
+    batch, m, n, k = shape
+    rng = np.random.default_rng(batch * 11 + m * 7 + n * 3 + k)
+    A = rng.standard_normal((batch, m, k)).astype(np.float32)
+    B = rng.standard_normal((batch, k, n)).astype(np.float32)
+    # a poisoned batch must not leak into its neighbours (k blocks never straddle batches)
+    if batch > 2:
+        B[1] = np.float32("inf")
+    a, b = gpu.Buffer.from_host(A), gpu.Buffer.from_host(B)
+    c = gpu.Buffer.from_host(np.full((batch, m, n), np.float32(-9.0)))
+    gpu.batch_matmul(a, b, c, batch, m, n, k)
+    C = c.retrieve((batch, m, n))
+    for i in range(batch):
+        if batch > 2 and i == 1:
+            continue
+        assert oracle.rel_frobenius(C[i], oracle.gemm_f64(A[i], B[i])) <= FP32_TOL, i
+    with pytest.raises(gpu.GonnError) as e:
+        gpu.batch_matmul(a, b, c, batch + 1, m, n, k)
+    assert e.value.code == -3
