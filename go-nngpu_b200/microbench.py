@@ -1,0 +1,159 @@
+"""Per-configuration timings of the dense path on one GPU (device-resident inputs).
+
+    python go-nngpu_b200/microbench.py [--config c1|c2|c2t|transpose|c3|c4|all] [--iters N]
+
+Prints one JSON line per measured operation: time, TFLOP/s or GB/s, and the
+fraction of the measured peaks when MEASURED_PEAKS.json lies beside the
+repository root.  Inputs are the seeded synthetic matrices of the benchmark
+configurations (numpy PCG64).  Timing: `iters` asynchronous calls on the
+library's stream between two synchronisations; operands rotate over several
+buffer sets where one set would fit in the 126 MB L2.
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import gonngpu as g  # noqa: E402
+
+
+def peaks():
+    path = os.path.join(os.path.dirname(HERE), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"tensor": p["bf16_tflops"], "hbm": p["hbm_gbs"], "source": "measured"}
+    return {"tensor": 1590.0, "hbm": 6650.0, "source": "fallback"}
+
+
+def timed(fn, iters, sets=1):
+    L = g.lib()
+    L.gonngpu_set_blocking(1)
+    for s in range(sets):
+        fn(s)
+    L.gonngpu_set_blocking(0)
+    g.synchronize()
+    t0 = time.perf_counter()
+    for i in range(iters):
+        fn(i % sets)
+    g.synchronize()
+    dt = (time.perf_counter() - t0) / iters
+    L.gonngpu_set_blocking(1)
+    return dt
+
+
+def emit(name, dt, flops=None, bytes_=None, extra=None):
+    pk = peaks()
+    line = {"op": name, "us": round(dt * 1e6, 2)}
+    if flops:
+        line["tflops"] = round(flops / dt / 1e12, 2)
+        line["frac_of_cublas_bf16_peak"] = round(flops / dt / 1e12 / pk["tensor"], 4)
+    if bytes_:
+        line["gb_per_s"] = round(bytes_ / dt / 1e9, 1)
+        line["frac_of_hbm_copy_peak"] = round(bytes_ / dt / 1e9 / pk["hbm"], 4)
+    line["peaks"] = pk["source"]
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def gemm_case(name, A, B, ta, tb, precision, iters):
+    M = A.shape[1] if ta else A.shape[0]
+    K = A.shape[0] if ta else A.shape[1]
+    N = B.shape[0] if tb else B.shape[1]
+    a, b = g.Buffer.from_host(A), g.Buffer.from_host(B)
+    c = g.Buffer.empty(M * N * 4)
+    dt = timed(lambda s: g.matmul_ex(a, A.shape, ta, b, B.shape, tb, c, (M, N), precision=precision), iters)
+    emit(name, dt, flops=2.0 * M * N * K)
+    for x in (a, b, c):
+        x.release()
+
+
+def config1(iters):
+    rng = np.random.default_rng(0)
+    A = rng.uniform(-1, 1, (1024, 1024)).astype(np.float32)
+    B = rng.uniform(-1, 1, (1024, 1024)).astype(np.float32)
+    gemm_case("c1 fp32 1024^3 A.B", A, B, False, False, g.FP32_3XTF32, iters)
+
+
+def config2(iters, transposes=True):
+    rng = np.random.default_rng(1)
+    A = (rng.standard_normal((4096, 4096)) / 64).astype(np.float32)
+    B = (rng.standard_normal((4096, 4096)) / 64).astype(np.float32)
+    gemm_case("c2 fp32 4096^3 A.B", A, B, False, False, g.FP32_3XTF32, iters)
+    if transposes:
+        gemm_case("c2 fp32 4096^3 At.B", A, B, True, False, g.FP32_3XTF32, iters)
+        gemm_case("c2 fp32 4096^3 A.Bt", A, B, False, True, g.FP32_3XTF32, iters)
+
+
+def transpose_case(iters, n=4096):
+    rng = np.random.default_rng(1)
+    X = (rng.standard_normal((n, n)) / 64).astype(np.float32)
+    sets = 4  # 4 x (64 + 64) MiB: no set is still in L2 when its turn comes again
+    ins = [g.Buffer.from_host(X) for _ in range(sets)]
+    outs = [g.Buffer.empty(X.nbytes) for _ in range(sets)]
+    dt = timed(lambda s: g.transpose(ins[s], X.shape, outs[s]), iters, sets)
+    emit(f"transpose {n}x{n} fp32", dt, bytes_=2.0 * X.nbytes)
+    for x in ins + outs:
+        x.release()
+
+
+def config3(iters):
+    rng = np.random.default_rng(2)
+    dims = (784, 1024, 1024, 10)
+    batch = 512
+    X = rng.uniform(0, 1, (batch, dims[0])).astype(np.float32)
+    Ws = [(rng.standard_normal((dims[i], dims[i + 1])) * np.sqrt(2.0 / dims[i])).astype(np.float32) for i in range(3)]
+    bs = [np.zeros(dims[i + 1], np.float32) for i in range(3)]
+    dY3 = (rng.standard_normal((batch, dims[3])) * 1e-2).astype(np.float32)
+    w = [g.Buffer.from_host(W) for W in Ws]
+    b = [g.Buffer.from_host(x) for x in bs]
+    h = [g.Buffer.from_host(X)] + [g.Buffer.empty(batch * dims[i + 1] * 4) for i in range(3)]
+    dh = [g.Buffer.empty(batch * dims[i] * 4) for i in range(3)] + [g.Buffer.from_host(dY3)]
+    dw = [g.Buffer.empty(W.nbytes) for W in Ws]
+    db = [g.Buffer.empty(dims[i + 1] * 4) for i in range(3)]
+
+    def step(_):
+        for i in range(3):
+            g.fused_linear_activation(h[i], batch, dims[i], w[i], dims[i + 1], b[i], 0 if i < 2 else -1, 0.0, h[i + 1])
+        for i in (2, 1, 0):
+            g.linear_backward(h[i], w[i], dh[i + 1], h[i + 1] if i < 2 else None, batch, dims[i], dims[i + 1],
+                              dx=dh[i], dw=dw[i], db=db[i])
+
+    dt = timed(step, iters)
+    flops = sum(3 * 2.0 * batch * dims[i] * dims[i + 1] for i in range(3))
+    emit("c3 MLP step 512x(784-1024-1024-10) fwd+bwd, 6 fused calls", dt, flops=flops)
+    for x in w + b + h + dh + dw + db:
+        x.release()
+
+
+def config4(iters):
+    rng = np.random.default_rng(3)
+    s = 1.0 / np.sqrt(8192)
+    A = (rng.standard_normal((8192, 8192)) * s).astype(np.float32)
+    B = (rng.standard_normal((8192, 8192)) * s).astype(np.float32)
+    gemm_case("c4 fp16-in/fp32-acc 8192^3 A.B", A, B, False, False, g.FP16_RN, iters)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="all")
+    ap.add_argument("--iters", type=int, default=50)
+    args = ap.parse_args()
+    assert g.lib().gonngpu_set_device(0) == 0, "no usable B200"
+    run = {"c1": lambda: config1(args.iters), "c2": lambda: config2(args.iters),
+           "c2nn": lambda: config2(args.iters, transposes=False),
+           "transpose": lambda: transpose_case(args.iters), "c3": lambda: config3(args.iters),
+           "c4": lambda: config4(args.iters)}
+    names = ["c1", "c2", "transpose", "c3", "c4"] if args.config == "all" else [args.config]
+    for n in names:
+        run[n]()
+
+
+if __name__ == "__main__":
+    main()
