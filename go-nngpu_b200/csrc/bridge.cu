@@ -59,6 +59,7 @@ struct Device {
   GemmStatus* status_host = nullptr;  // mapped pinned memory the kernels report into
   GemmStatus* status_dev = nullptr;
   GemmStatus last_status{};
+  unsigned long long* first_zero_dev = nullptr;  // scratch word of the element-wise divide
   void* stage[2] = {nullptr, nullptr};
   cudaEvent_t stage_ev[2] = {nullptr, nullptr};
 };
@@ -153,7 +154,8 @@ int ensure_device(int ordinal, CError* err) {
             cudaHostAlloc(reinterpret_cast<void**>(&d.status_host), sizeof(GemmStatus),
                           cudaHostAllocMapped) == cudaSuccess &&
             cudaHostGetDevicePointer(reinterpret_cast<void**>(&d.status_dev), d.status_host, 0) ==
-                cudaSuccess;
+                cudaSuccess &&
+            cudaMalloc(reinterpret_cast<void**>(&d.first_zero_dev), 8) == cudaSuccess;
   for (int i = 0; ok && i < 2; ++i) {
     ok = cudaHostAlloc(&d.stage[i], kStageBytes, cudaHostAllocDefault) == cudaSuccess &&
          cudaEventCreateWithFlags(&d.stage_ev[i], cudaEventDisableTiming) == cudaSuccess;
@@ -909,6 +911,153 @@ int gonngpu_convert_f16_device(const float* src, long rows, long cols, void* dst
                        mode == GONNGPU_FP16_RN ? gonn::F16_RN : gonn::F16_TRUNC, d.stream);
   ++g_stats[3];
   return finish(d, err, -6, "convert_f16_device");
+}
+
+// ---- element-wise family (internal/cgo/metal_bridge_matrix.m:172-543) -------------
+namespace {
+// Equal-shaped binary op.  Order of checks and codes as in the reference:
+// dimensions (-2), device (-1), buffers (-3).
+int ew_binary(int op, const char* noun, GPUPtr aPtr, long aRows, long aCols, GPUPtr bPtr, long bRows,
+              long bCols, GPUPtr cPtr, long cRows, long cCols, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (aRows != bRows || aCols != bCols || aRows != cRows || aCols != cCols || aRows < 0 || aCols < 0) {
+    set_error(err, "Matrices must have the same dimensions for element-wise %s.", noun);
+    return -2;
+  }
+  Buffer* A = as_buffer(aPtr);
+  Buffer* B = as_buffer(bPtr);
+  Buffer* C = as_buffer(cPtr);
+  const size_t n = size_t(aRows) * size_t(aCols);
+  if (!A || !B || !C || n * 4 > A->bytes || n * 4 > B->bytes || n * 4 > C->bytes ||
+      A->device != C->device || B->device != C->device) {
+    set_error(err, "Invalid input or output buffer pointers.");
+    return -3;
+  }
+  if (ensure_device(C->device, err)) return -1;
+  Device& d = g_dev[C->device];
+  if (!make_resident(d, A) || !make_resident(d, B)) {
+    cudaGetLastError();
+    set_error(err, "element-wise %s: host to device copy failed.", noun);
+    return -6;
+  }
+  size_t count = n;
+  long zero_at = -1;
+  if (op == gonn::EW_DIV && n > 0) {
+    // The reference stops at the first zero divisor: the elements before it are
+    // written, the rest are not, and the call fails with -4.
+    unsigned long long idx = ~0ull;
+    bool ok = cudaMemsetAsync(d.first_zero_dev, 0xFF, 8, d.stream) == cudaSuccess;
+    if (ok) gonn::launch_first_zero(B->dptr, n, d.first_zero_dev, d.stream);
+    ok = ok && cudaMemcpyAsync(&idx, d.first_zero_dev, 8, cudaMemcpyDeviceToHost, d.stream) == cudaSuccess &&
+         cudaStreamSynchronize(d.stream) == cudaSuccess;
+    ++g_stats[3];
+    if (!ok) {
+      cudaGetLastError();
+      set_error(err, "element-wise division: CUDA error.");
+      return -6;
+    }
+    if (idx < n) {
+      zero_at = long(idx);
+      count = size_t(idx);
+    }
+  }
+  if (count > 0) {
+    if (C->host_pending && count < n && !make_resident(d, C)) {  // keep the untouched tail
+      cudaGetLastError();
+      set_error(err, "element-wise %s: host to device copy failed.", noun);
+      return -6;
+    }
+    gonn::launch_elementwise(op, A->dptr, B->dptr, C->dptr, count, 0.f, d.stream);
+    ++g_stats[3];
+    wrote(C);
+  }
+  const int rc = finish(d, err, -6, "element-wise operation");
+  if (rc == 0 && zero_at >= 0) {
+    set_error(err, "Division by zero encountered at element %ld.", zero_at);
+    return -4;
+  }
+  return rc;
+}
+
+// One-operand op with a scalar, or activation forward (b == nullptr), or
+// activation backward (a = gradient, b = activation output).  Bad buffers: -1.
+int ew_unary(int op, const char* what, GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long n, float scalar,
+             CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* A = as_buffer(aPtr);
+  Buffer* B = bPtr ? as_buffer(bPtr) : nullptr;
+  Buffer* C = as_buffer(cPtr);
+  if (!A || !C || (bPtr && !B) || n < 0 || size_t(n) * 4 > A->bytes || size_t(n) * 4 > C->bytes ||
+      (B && size_t(n) * 4 > B->bytes) || A->device != C->device || (B && B->device != C->device)) {
+    set_error(err, "Invalid %s.", what);
+    return -1;
+  }
+  if (ensure_device(C->device, err)) return -1;
+  Device& d = g_dev[C->device];
+  if (!make_resident(d, A) || (B && !make_resident(d, B))) {
+    cudaGetLastError();
+    set_error(err, "%s: host to device copy failed.", what);
+    return -6;
+  }
+  gonn::launch_elementwise(op, A->dptr, B ? B->dptr : nullptr, C->dptr, uint64_t(n), scalar, d.stream);
+  ++g_stats[3];
+  wrote(C);
+  return finish(d, err, -6, what);
+}
+}  // namespace
+
+int perform_mps_matrix_add(GPUPtr a, long aRows, long aCols, GPUPtr b, long bRows, long bCols, GPUPtr c,
+                           long cRows, long cCols, DevicePtr, CError* err) {
+  return ew_binary(gonn::EW_ADD, "addition", a, aRows, aCols, b, bRows, bCols, c, cRows, cCols, err);
+}
+int perform_mps_matrix_subtract(GPUPtr a, long aRows, long aCols, GPUPtr b, long bRows, long bCols,
+                                GPUPtr c, long cRows, long cCols, DevicePtr, CError* err) {
+  return ew_binary(gonn::EW_SUB, "subtraction", a, aRows, aCols, b, bRows, bCols, c, cRows, cCols, err);
+}
+int perform_mps_matrix_element_multiply(GPUPtr a, long aRows, long aCols, GPUPtr b, long bRows,
+                                        long bCols, GPUPtr c, long cRows, long cCols, DevicePtr,
+                                        CError* err) {
+  return ew_binary(gonn::EW_MUL, "multiplication", a, aRows, aCols, b, bRows, bCols, c, cRows, cCols, err);
+}
+int perform_mps_matrix_element_divide(GPUPtr a, long aRows, long aCols, GPUPtr b, long bRows, long bCols,
+                                      GPUPtr c, long cRows, long cCols, DevicePtr, CError* err) {
+  return ew_binary(gonn::EW_DIV, "division", a, aRows, aCols, b, bRows, bCols, c, cRows, cCols, err);
+}
+int perform_mps_matrix_scalar_add(GPUPtr in, long rows, long cols, float scalar, GPUPtr out, DevicePtr,
+                                  CError* err) {
+  return ew_unary(gonn::EW_SCALAR_ADD, "input or output buffer pointers", in, nullptr, out,
+                  rows < 0 || cols < 0 ? -1 : rows * cols, scalar, err);
+}
+int perform_mps_matrix_scalar_multiply(GPUPtr in, long rows, long cols, float scalar, GPUPtr out,
+                                       DevicePtr, CError* err) {
+  return ew_unary(gonn::EW_SCALAR_MUL, "input or output buffer pointers", in, nullptr, out,
+                  rows < 0 || cols < 0 ? -1 : rows * cols, scalar, err);
+}
+int perform_activation_sigmoid_forward(GPUPtr in, long size, GPUPtr out, DevicePtr, CError* err) {
+  return ew_unary(gonn::EW_SIGMOID, "buffer pointers for Sigmoid forward", in, nullptr, out, size, 0.f, err);
+}
+int perform_activation_sigmoid_backward(GPUPtr gradOut, GPUPtr actOut, long size, GPUPtr gradIn,
+                                        DevicePtr, CError* err) {
+  return ew_unary(gonn::EW_SIGMOID_BWD, "buffer pointers for Sigmoid backward", gradOut, actOut, gradIn,
+                  size, 0.f, err);
+}
+int perform_activation_tanh_forward(GPUPtr in, long size, GPUPtr out, DevicePtr, CError* err) {
+  return ew_unary(gonn::EW_TANH, "buffer pointers for Tanh forward", in, nullptr, out, size, 0.f, err);
+}
+int perform_activation_tanh_backward(GPUPtr gradOut, GPUPtr actOut, long size, GPUPtr gradIn, DevicePtr,
+                                     CError* err) {
+  return ew_unary(gonn::EW_TANH_BWD, "buffer pointers for Tanh backward", gradOut, actOut, gradIn, size,
+                  0.f, err);
+}
+int perform_activation_leaky_relu_forward(GPUPtr in, long size, float alpha, GPUPtr out, DevicePtr,
+                                          CError* err) {
+  return ew_unary(gonn::EW_LEAKY, "buffer pointers for Leaky ReLU forward", in, nullptr, out, size, alpha,
+                  err);
+}
+int perform_activation_leaky_relu_backward(GPUPtr gradOut, GPUPtr actOut, long size, float alpha,
+                                           GPUPtr gradIn, DevicePtr, CError* err) {
+  return ew_unary(gonn::EW_LEAKY_BWD, "buffer pointers for Leaky ReLU backward", gradOut, actOut, gradIn,
+                  size, alpha, err);
 }
 
 int perform_batch_matmul_optimized(GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long batchSize, long M,

@@ -92,4 +92,15 @@ void launch_relu_backward(const float* grad_out, const float* act_out, float* gr
 void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream,
                    const float* mask = nullptr);
 
+// ---- element-wise family ----------------------------------------------------------
+enum EwOp : int {
+  EW_ADD = 0, EW_SUB, EW_MUL, EW_DIV, EW_SCALAR_ADD, EW_SCALAR_MUL,
+  EW_SIGMOID, EW_SIGMOID_BWD, EW_TANH, EW_TANH_BWD, EW_LEAKY, EW_LEAKY_BWD,
+};
+// c[i] = op(a[i], b[i], scalar); b may be null for the one-operand ops.
+void launch_elementwise(int op, const float* a, const float* b, float* c, uint64_t n, float scalar,
+                        cudaStream_t stream);
+// *out = min(*out, smallest i with b[i] == 0); the caller presets *out to ~0.
+void launch_first_zero(const float* b, uint64_t n, unsigned long long* out, cudaStream_t stream);
+
 }  // namespace gonn

@@ -45,6 +45,22 @@ SIGNATURES = {
         _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _errp]),
     "perform_activation_relu_forward": (_c_int, [_vp, _c_long, _vp, _vp, _errp]),
     "perform_activation_relu_backward": (_c_int, [_vp, _vp, _c_long, _vp, _vp, _errp]),
+    "perform_mps_matrix_add": (
+        _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _errp]),
+    "perform_mps_matrix_subtract": (
+        _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _errp]),
+    "perform_mps_matrix_element_multiply": (
+        _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _errp]),
+    "perform_mps_matrix_element_divide": (
+        _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _errp]),
+    "perform_mps_matrix_scalar_add": (_c_int, [_vp, _c_long, _c_long, _c_float, _vp, _vp, _errp]),
+    "perform_mps_matrix_scalar_multiply": (_c_int, [_vp, _c_long, _c_long, _c_float, _vp, _vp, _errp]),
+    "perform_activation_sigmoid_forward": (_c_int, [_vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_sigmoid_backward": (_c_int, [_vp, _vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_tanh_forward": (_c_int, [_vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_tanh_backward": (_c_int, [_vp, _vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_leaky_relu_forward": (_c_int, [_vp, _c_long, _c_float, _vp, _vp, _errp]),
+    "perform_activation_leaky_relu_backward": (_c_int, [_vp, _vp, _c_long, _c_float, _vp, _vp, _errp]),
     "perform_fused_linear_activation": (
         _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _vp, _c_int, _c_float, _vp, _vp, _errp]),
     "perform_optimized_gemm": (
@@ -257,6 +273,40 @@ def linear_backward(x, w, dy, act_out, batch, in_size, out_size, dx=None, dw=Non
     h = lambda b: b.handle if b is not None else None  # noqa: E731
     _check(lib().gonngpu_linear_backward(h(x), h(w), h(dy), h(act_out), batch, in_size, out_size,
                                          h(dx), h(dw), h(db), ctypes.byref(err)), err)
+
+
+def elementwise(name, a, b, c, shape):
+    """name in {add, subtract, element_multiply, element_divide}; equal shapes."""
+    err = CError()
+    fn = getattr(lib(), "perform_mps_matrix_" + name)
+    _check(fn(a.handle, shape[0], shape[1], b.handle, shape[0], shape[1], c.handle, shape[0], shape[1],
+              None, ctypes.byref(err)), err)
+
+
+def scalar_op(name, a, shape, scalar, c):
+    """name in {scalar_add, scalar_multiply}."""
+    err = CError()
+    fn = getattr(lib(), "perform_mps_matrix_" + name)
+    _check(fn(a.handle, shape[0], shape[1], scalar, c.handle, None, ctypes.byref(err)), err)
+
+
+def activation_forward(name, inp, size, out, alpha=None):
+    """name in {sigmoid, tanh, leaky_relu}."""
+    err = CError()
+    fn = getattr(lib(), f"perform_activation_{name}_forward")
+    if alpha is None:
+        _check(fn(inp.handle, size, out.handle, None, ctypes.byref(err)), err)
+    else:
+        _check(fn(inp.handle, size, alpha, out.handle, None, ctypes.byref(err)), err)
+
+
+def activation_backward(name, grad_out, act_out, size, grad_in, alpha=None):
+    err = CError()
+    fn = getattr(lib(), f"perform_activation_{name}_backward")
+    if alpha is None:
+        _check(fn(grad_out.handle, act_out.handle, size, grad_in.handle, None, ctypes.byref(err)), err)
+    else:
+        _check(fn(grad_out.handle, act_out.handle, size, alpha, grad_in.handle, None, ctypes.byref(err)), err)
 
 
 def batch_matmul(a, b, c, batch, m, n, k):

@@ -103,6 +103,48 @@ GONNGPU_API int perform_activation_relu_forward(GPUPtr inputPtr, long size, GPUP
 GONNGPU_API int perform_activation_relu_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr, long size,
                                      GPUPtr gradInputPtr, DevicePtr mtlDevicePtr, CError *err);
 
+/* ---- element-wise family used between the GEMMs of eager layer chains -------
+ * (CPU loops in the reference; streaming kernels here, so the data stays in HBM) */
+
+/* metal_bridge.h:44-50, 60-82.  c = a (op) b for equal shapes.  Errors: -2
+ * shapes differ, -1 device, -3 bad buffer, -6 execution; the divide also -4
+ * "Division by zero encountered at element i" for the first zero divisor, with
+ * the elements before i written and the rest left as they were, as the
+ * reference's loop does (metal_bridge_matrix.m:470-479). */
+GONNGPU_API int perform_mps_matrix_add(GPUPtr aMatrixPtr, long aRows, long aCols, GPUPtr bMatrixPtr, long bRows,
+                           long bCols, GPUPtr resultMatrixPtr, long resultRows, long resultCols,
+                           DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_mps_matrix_subtract(GPUPtr aMatrixPtr, long aRows, long aCols, GPUPtr bMatrixPtr, long bRows,
+                                long bCols, GPUPtr resultMatrixPtr, long resultRows, long resultCols,
+                                DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_mps_matrix_element_multiply(GPUPtr aMatrixPtr, long aRows, long aCols, GPUPtr bMatrixPtr,
+                                        long bRows, long bCols, GPUPtr resultMatrixPtr, long resultRows,
+                                        long resultCols, DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_mps_matrix_element_divide(GPUPtr aMatrixPtr, long aRows, long aCols, GPUPtr bMatrixPtr,
+                                      long bRows, long bCols, GPUPtr resultMatrixPtr, long resultRows,
+                                      long resultCols, DevicePtr mtlDevicePtr, CError *err);
+/* metal_bridge.h:85-99.  result = input + scalar / input * scalar.  Errors: -1 bad buffer. */
+GONNGPU_API int perform_mps_matrix_scalar_add(GPUPtr inputMatrixPtr, long rows, long cols, float scalar,
+                                  GPUPtr resultMatrixPtr, DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_mps_matrix_scalar_multiply(GPUPtr inputMatrixPtr, long rows, long cols, float scalar,
+                                       GPUPtr resultMatrixPtr, DevicePtr mtlDevicePtr, CError *err);
+/* metal_bridge.h:274-301, 334-348.  Sigmoid and tanh clamp their input to
+ * [-88, 88] (metal_bridge_activation.m:105, 166); the backward forms take the
+ * activation OUTPUT.  Errors: -1 bad buffer. */
+GONNGPU_API int perform_activation_sigmoid_forward(GPUPtr inputPtr, long size, GPUPtr outputPtr,
+                                       DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_sigmoid_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr, long size,
+                                        GPUPtr gradInputPtr, DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_tanh_forward(GPUPtr inputPtr, long size, GPUPtr outputPtr,
+                                    DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_tanh_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr, long size,
+                                     GPUPtr gradInputPtr, DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_leaky_relu_forward(GPUPtr inputPtr, long size, float alpha, GPUPtr outputPtr,
+                                          DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_leaky_relu_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr,
+                                           long size, float alpha, GPUPtr gradInputPtr,
+                                           DevicePtr mtlDevicePtr, CError *err);
+
 /* metal_bridge.h:1348-1353.  output[b,o] = act(sum_i input[b,i]*weight[i,o] +
  * bias[o]); `bias` may be NULL.  activation_type is decoded as the reference's
  * kernel decodes it (default.metal:488-506): 0 ReLU, 1 LeakyReLU(alpha),

@@ -217,3 +217,64 @@ float oracle_f16_to_f32(uint16_t h) {
 void oracle_convert_tensor_f16(const float *src, float *dst, long n) {
   for (long i = 0; i < n; i++) dst[i] = oracle_f16_to_f32(oracle_f32_to_f16_trunc(src[i]));
 }
+
+/* ---- element-wise family --------------------------------------------------------
+ * internal/cgo/metal_bridge_matrix.m:172-249 (add), :322-392 (subtract),
+ * :394-439 (multiply), :441-484 (divide), :486-543 (scalar add / multiply).
+ * op: 0 add, 1 subtract, 2 multiply, 3 divide.  The divide stops at the first
+ * zero divisor: earlier elements are written, the rest are not, and it returns
+ * -4 with that index in *zero_index (metal_bridge_matrix.m:470-479). */
+int oracle_elementwise(int op, const float *a, const float *b, float *r, long n, long *zero_index) {
+  for (long i = 0; i < n; i++) {
+    switch (op) {
+      case 0: r[i] = a[i] + b[i]; break;
+      case 1: r[i] = a[i] - b[i]; break;
+      case 2: r[i] = a[i] * b[i]; break;
+      default:
+        if (b[i] == 0.0f) {
+          if (zero_index) *zero_index = i;
+          return -4;
+        }
+        r[i] = a[i] / b[i];
+    }
+  }
+  return 0;
+}
+
+void oracle_scalar_op(int multiply, const float *in, float scalar, float *out, long n) {
+  for (long i = 0; i < n; i++) out[i] = multiply ? in[i] * scalar : in[i] + scalar;
+}
+
+/* internal/cgo/metal_bridge_activation.m:83-170 (sigmoid, tanh: input clamped
+ * to [-88, 88]; derivatives from the activation output), :372-430 (leaky ReLU).
+ * kind: 0 sigmoid, 1 tanh, 2 leaky ReLU. */
+void oracle_activation_forward(int kind, const float *in, float *out, long n, float alpha) {
+  for (long i = 0; i < n; i++) {
+    if (kind == 0) {
+      float x = fmaxf(-88.0f, fminf(88.0f, in[i]));
+      out[i] = 1.0f / (1.0f + expf(-x));
+    } else if (kind == 1) {
+      float x = fmaxf(-88.0f, fminf(88.0f, in[i]));
+      out[i] = tanhf(x);
+    } else {
+      float x = in[i];
+      out[i] = (x > 0.0f) ? x : alpha * x;
+    }
+  }
+}
+
+void oracle_activation_backward(int kind, const float *grad_out, const float *act_out, float *grad_in,
+                                long n, float alpha) {
+  for (long i = 0; i < n; i++) {
+    if (kind == 0) {
+      float s = act_out[i];
+      grad_in[i] = grad_out[i] * s * (1.0f - s);
+    } else if (kind == 1) {
+      float t = act_out[i];
+      grad_in[i] = grad_out[i] * (1.0f - t * t);
+    } else {
+      float d = (act_out[i] > 0.0f) ? 1.0f : alpha;
+      grad_in[i] = grad_out[i] * d;
+    }
+  }
+}

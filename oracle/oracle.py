@@ -253,3 +253,48 @@ def config5(m=131072, k=4096, n=4096):
         A[r:r + step] = rng.standard_normal((min(step, m - r), k)) * s
     B = (rng.standard_normal((k, n)) * s).astype(np.float32)
     return A, B
+
+
+# ---------------------------------------------------------------- element-wise family
+def elementwise(op, a, b, out=None):
+    """op: 0 add, 1 subtract, 2 multiply, 3 divide.  Returns (code, result, zero_index);
+    `out` gives the previous contents of the result (the divide may leave a tail untouched)."""
+    h = lib()
+    h.oracle_elementwise.argtypes = [_i, _f32p, _f32p, _f32p, _l, ctypes.POINTER(_l)]
+    h.oracle_elementwise.restype = _i
+    a, b = _c32(a), _c32(b)
+    r = _c32(out).copy() if out is not None else np.zeros_like(a)
+    z = _l(-1)
+    rc = h.oracle_elementwise(op, _p32(a), _p32(b), _p32(r), a.size, ctypes.byref(z))
+    return rc, r, z.value
+
+
+def scalar_op(multiply, x, scalar):
+    h = lib()
+    h.oracle_scalar_op.argtypes = [_i, _f32p, _f, _f32p, _l]
+    h.oracle_scalar_op.restype = None
+    x = _c32(x)
+    out = np.empty_like(x)
+    h.oracle_scalar_op(int(multiply), _p32(x), scalar, _p32(out), x.size)
+    return out
+
+
+def activation_forward(kind, x, alpha=0.0):
+    """kind: 0 sigmoid, 1 tanh, 2 leaky ReLU."""
+    h = lib()
+    h.oracle_activation_forward.argtypes = [_i, _f32p, _f32p, _l, _f]
+    h.oracle_activation_forward.restype = None
+    x = _c32(x)
+    out = np.empty_like(x)
+    h.oracle_activation_forward(kind, _p32(x), _p32(out), x.size, alpha)
+    return out
+
+
+def activation_backward(kind, grad_out, act_out, alpha=0.0):
+    h = lib()
+    h.oracle_activation_backward.argtypes = [_i, _f32p, _f32p, _f32p, _l, _f]
+    h.oracle_activation_backward.restype = None
+    g, a = _c32(grad_out), _c32(act_out)
+    out = np.empty_like(g)
+    h.oracle_activation_backward(kind, _p32(g), _p32(a), _p32(out), g.size, alpha)
+    return out

@@ -536,3 +536,72 @@ def test_batch_matmul_matches_per_batch_oracle(gpu, shape):
     with pytest.raises(gpu.GonnError) as e:
         gpu.batch_matmul(a, b, c, batch + 1, m, n, k)
     assert e.value.code == -3
+
+
+# ------------------------------------------------------------------ element-wise family
+@pytest.mark.parametrize("shape", [(1, 1), (3, 5), (37, 101), (512, 1024), (1000, 1001)])
+def test_elementwise_ops_are_bit_exact(gpu, shape):
+    rng = np.random.default_rng(shape[0] * 7 + shape[1])
+    A = rng.standard_normal(shape).astype(np.float32)
+    B = (rng.standard_normal(shape) + np.float32(3.0)).astype(np.float32)
+    B[B == 0] = 1.0
+    a, b, c = gpu.Buffer.from_host(A), gpu.Buffer.from_host(B), gpu.Buffer.empty(A.nbytes)
+    for op, name in enumerate(["add", "subtract", "element_multiply", "element_divide"]):
+        gpu.elementwise(name, a, b, c, shape)
+        rc, ref, _ = oracle.elementwise(op, A, B)
+        assert rc == 0
+        assert np.array_equal(c.retrieve(shape).view(np.uint32), ref.reshape(shape).view(np.uint32)), name
+    for mult, name in ((False, "scalar_add"), (True, "scalar_multiply")):
+        gpu.scalar_op(name, a, shape, 1.375, c)
+        assert np.array_equal(c.retrieve(shape), oracle.scalar_op(mult, A, 1.375).reshape(shape))
+    with pytest.raises(gpu.GonnError) as e:
+        lib = gpu.lib()
+        err = gpu.CError()
+        rc = lib.perform_mps_matrix_add(a.handle, shape[0], shape[1], b.handle, shape[0], shape[1] + 1, c.handle,
+                                        shape[0], shape[1], None, ctypes.byref(err))
+        gpu._check(rc, err)
+    assert e.value.code == -2 and "same dimensions" in e.value.message
+
+
+def test_divide_stops_at_first_zero_like_the_reference(gpu):
+    rng = np.random.default_rng(8)
+    n = 5000
+    A = rng.standard_normal((1, n)).astype(np.float32)
+    B = (rng.standard_normal((1, n)) + np.float32(4.0)).astype(np.float32)
+    B[0, 1234] = 0.0
+    B[0, 4000] = -0.0
+    prev = np.full((1, n), 7.0, np.float32)
+    a, b, c = gpu.Buffer.from_host(A), gpu.Buffer.from_host(B), gpu.Buffer.from_host(prev)
+    with pytest.raises(gpu.GonnError) as e:
+        gpu.elementwise("element_divide", a, b, c, (1, n))
+    assert e.value.code == -4 and "Division by zero encountered at element 1234" in e.value.message
+    rc, ref, z = oracle.elementwise(3, A, B, out=prev)
+    assert rc == -4 and z == 1234
+    assert np.array_equal(c.retrieve((1, n)).view(np.uint32), ref.reshape(1, n).view(np.uint32))
+
+
+def test_activation_family_matches_oracle(gpu, golden):
+    ref, _ = golden
+    rng = np.random.default_rng(9)
+    x = np.concatenate([rng.standard_normal(4093) * 3, [-1e30, -100.0, 0.0, -0.0, 100.0, 1e30]]).astype(np.float32)
+    go = rng.standard_normal(x.size).astype(np.float32)
+    xi, gi = gpu.Buffer.from_host(x), gpu.Buffer.from_host(go)
+    out, gin = gpu.Buffer.empty(x.nbytes), gpu.Buffer.empty(x.nbytes)
+    for kind, name, alpha in ((0, "sigmoid", None), (1, "tanh", None), (2, "leaky_relu", 0.1)):
+        gpu.activation_forward(name, xi, x.size, out, alpha)
+        y = out.retrieve(x.shape)
+        y_ref = oracle.activation_forward(kind, x, alpha or 0.0)
+        assert np.allclose(y, y_ref, rtol=2e-6, atol=1e-7), name     # expf / tanhf differ by an ulp or two
+        gpu.activation_backward(name, gi, out, x.size, gin, alpha)
+        assert np.allclose(gin.retrieve(x.shape), oracle.activation_backward(kind, go, y, alpha or 0.0),
+                           rtol=2e-6, atol=1e-7), name
+    # the reference's own vectors
+    k = ref["leaky_relu_forward"]
+    v = np.array(k["input"], np.float32)
+    vi, vo = gpu.Buffer.from_host(v), gpu.Buffer.empty(v.nbytes)
+    gpu.activation_forward("leaky_relu", vi, v.size, vo, k["alpha"])
+    assert np.allclose(vo.retrieve(v.shape), k["expected"], atol=1e-6)
+    gpu.activation_forward("sigmoid", vi, v.size, vo)
+    assert abs(vo.retrieve(v.shape)[2] - 0.5) <= 1e-6
+    gpu.activation_forward("tanh", vi, v.size, vo)
+    assert abs(vo.retrieve(v.shape)[2]) <= 1e-6

@@ -101,3 +101,29 @@ def test_config_generators_are_seeded_and_shaped():
     A, B = oracle.config5(256, 64, 32)
     assert A.shape == (256, 64) and B.shape == (64, 32)
     assert abs(A.std() - 1 / 8) < 0.01
+
+
+def test_elementwise_family_against_reference_kats_and_numpy(golden):
+    ref, _ = golden
+    k = ref["leaky_relu_forward"]
+    assert np.allclose(oracle.activation_forward(2, np.array(k["input"], np.float32), k["alpha"]), k["expected"], atol=1e-6)
+    k = ref["sigmoid_forward"]
+    s = oracle.activation_forward(0, np.array(k["input"], np.float32))
+    assert abs(s[k["index_of_zero"]] - 0.5) <= 1e-6 and (s >= 0).all() and (s <= 1).all()
+    k = ref["tanh_forward"]
+    t = oracle.activation_forward(1, np.array(k["input"], np.float32))
+    assert abs(t[k["index_of_zero"]]) <= 1e-6 and (np.abs(t) <= 1).all()
+    rng = np.random.default_rng(3)
+    a, b = rng.standard_normal(1000).astype(np.float32), rng.standard_normal(1000).astype(np.float32)
+    for op, fn in ((0, np.add), (1, np.subtract), (2, np.multiply), (3, np.divide)):
+        rc, r, _ = oracle.elementwise(op, a, b)
+        assert rc == 0 and np.array_equal(r, fn(a, b))
+    b[17] = 0.0
+    b[500] = -0.0
+    rc, r, z = oracle.elementwise(3, a, b, out=np.full(1000, 7.0, np.float32))
+    assert rc == -4 and z == 17 and np.array_equal(r[:17], a[:17] / b[:17]) and (r[17:] == 7.0).all()
+    assert np.array_equal(oracle.scalar_op(False, a, 1.5), a + np.float32(1.5))
+    assert np.array_equal(oracle.scalar_op(True, a, 1.5), a * np.float32(1.5))
+    # clamping: huge inputs neither overflow nor produce NaN
+    big = np.array([-1e30, -100, 100, 1e30], np.float32)
+    assert np.isfinite(oracle.activation_forward(0, big)).all() and np.isfinite(oracle.activation_forward(1, big)).all()
