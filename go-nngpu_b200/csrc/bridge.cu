@@ -981,8 +981,10 @@ int ew_binary(int op, const char* noun, GPUPtr aPtr, long aRows, long aCols, GPU
 
 // One-operand op with a scalar, or activation forward (b == nullptr), or
 // activation backward (a = gradient, b = activation output).  Bad buffers: -1.
+// `softmax_rows` >= 0 selects the row softmax over [softmax_rows, n / softmax_rows]
+// instead of `op` (forward when b == nullptr, else backward).
 int ew_unary(int op, const char* what, GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long n, float scalar,
-             CError* err) {
+             CError* err, long softmax_rows = -1) {
   std::lock_guard<std::recursive_mutex> lk(g_mu);
   Buffer* A = as_buffer(aPtr);
   Buffer* B = bPtr ? as_buffer(bPtr) : nullptr;
@@ -999,7 +1001,11 @@ int ew_unary(int op, const char* what, GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, lo
     set_error(err, "%s: host to device copy failed.", what);
     return -6;
   }
-  gonn::launch_elementwise(op, A->dptr, B ? B->dptr : nullptr, C->dptr, uint64_t(n), scalar, d.stream);
+  if (softmax_rows > 0)
+    gonn::launch_softmax(A->dptr, B ? B->dptr : nullptr, C->dptr, uint64_t(softmax_rows),
+                         uint64_t(n / softmax_rows), B != nullptr, d.stream);
+  else if (softmax_rows < 0)
+    gonn::launch_elementwise(op, A->dptr, B ? B->dptr : nullptr, C->dptr, uint64_t(n), scalar, d.stream);
   ++g_stats[3];
   wrote(C);
   return finish(d, err, -6, what);
@@ -1058,6 +1064,52 @@ int perform_activation_leaky_relu_backward(GPUPtr gradOut, GPUPtr actOut, long s
                                            GPUPtr gradIn, DevicePtr, CError* err) {
   return ew_unary(gonn::EW_LEAKY_BWD, "buffer pointers for Leaky ReLU backward", gradOut, actOut, gradIn,
                   size, alpha, err);
+}
+
+int perform_activation_softmax_1d_forward(GPUPtr in, long size, GPUPtr out, DevicePtr, CError* err) {
+  return ew_unary(0, "buffer pointers for Softmax 1D forward", in, nullptr, out, size, 0.f, err,
+                  size > 0 ? 1 : 0);
+}
+int perform_activation_softmax_1d_backward(GPUPtr gradOut, GPUPtr actOut, long size, GPUPtr gradIn,
+                                           DevicePtr, CError* err) {
+  return ew_unary(0, "buffer pointers for Softmax 1D backward", gradOut, actOut, gradIn, size, 0.f, err,
+                  size > 0 ? 1 : 0);
+}
+int perform_activation_softmax_2d_forward(GPUPtr in, long batchSize, long features, GPUPtr out, DevicePtr,
+                                          CError* err) {
+  const bool bad = batchSize < 0 || features < 0;
+  return ew_unary(0, "buffer pointers for Softmax 2D forward", in, nullptr, out,
+                  bad ? -1 : batchSize * features, 0.f, err, bad || features == 0 ? 0 : batchSize);
+}
+int perform_activation_softmax_2d_backward(GPUPtr gradOut, GPUPtr actOut, long batchSize, long features,
+                                           GPUPtr gradIn, DevicePtr, CError* err) {
+  const bool bad = batchSize < 0 || features < 0;
+  return ew_unary(0, "buffer pointers for Softmax 2D backward", gradOut, actOut, gradIn,
+                  bad ? -1 : batchSize * features, 0.f, err, bad || features == 0 ? 0 : batchSize);
+}
+int perform_activation_elu_forward(GPUPtr in, long size, float alpha, GPUPtr out, DevicePtr, CError* err) {
+  return ew_unary(gonn::EW_ELU, "buffer pointers for ELU forward", in, nullptr, out, size, alpha, err);
+}
+int perform_activation_elu_backward(GPUPtr gradOut, GPUPtr actOut, long size, float alpha, GPUPtr gradIn,
+                                    DevicePtr, CError* err) {
+  return ew_unary(gonn::EW_ELU_BWD, "buffer pointers for ELU backward", gradOut, actOut, gradIn, size,
+                  alpha, err);
+}
+int perform_activation_swish_forward(GPUPtr in, long size, GPUPtr out, DevicePtr, CError* err) {
+  return ew_unary(gonn::EW_SWISH, "buffer pointers for Swish forward", in, nullptr, out, size, 0.f, err);
+}
+int perform_activation_swish_backward(GPUPtr gradOut, GPUPtr actOut, long size, GPUPtr gradIn, DevicePtr,
+                                      CError* err) {
+  return ew_unary(gonn::EW_SWISH_BWD, "buffer pointers for Swish backward", gradOut, actOut, gradIn, size,
+                  0.f, err);
+}
+int perform_activation_gelu_forward(GPUPtr in, long size, GPUPtr out, DevicePtr, CError* err) {
+  return ew_unary(gonn::EW_GELU, "buffer pointers for GELU forward", in, nullptr, out, size, 0.f, err);
+}
+int perform_activation_gelu_backward(GPUPtr gradOut, GPUPtr actOut, long size, GPUPtr gradIn, DevicePtr,
+                                     CError* err) {
+  return ew_unary(gonn::EW_GELU_BWD, "buffer pointers for GELU backward", gradOut, actOut, gradIn, size,
+                  0.f, err);
 }
 
 int perform_batch_matmul_optimized(GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long batchSize, long M,

@@ -96,10 +96,15 @@ void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cu
 enum EwOp : int {
   EW_ADD = 0, EW_SUB, EW_MUL, EW_DIV, EW_SCALAR_ADD, EW_SCALAR_MUL,
   EW_SIGMOID, EW_SIGMOID_BWD, EW_TANH, EW_TANH_BWD, EW_LEAKY, EW_LEAKY_BWD,
+  EW_ELU, EW_ELU_BWD, EW_SWISH, EW_SWISH_BWD, EW_GELU, EW_GELU_BWD,
 };
 // c[i] = op(a[i], b[i], scalar); b may be null for the one-operand ops.
 void launch_elementwise(int op, const float* a, const float* b, float* c, uint64_t n, float scalar,
                         cudaStream_t stream);
+// Row softmax over [rows, features].  Forward: out = softmax(in_or_grad) (act unused).
+// Backward: out = act * (in_or_grad - dot(in_or_grad, act)) per row.
+void launch_softmax(const float* in_or_grad, const float* act, float* out, uint64_t rows,
+                    uint64_t features, bool backward, cudaStream_t stream);
 // *out = min(*out, smallest i with b[i] == 0); the caller presets *out to ~0.
 void launch_first_zero(const float* b, uint64_t n, unsigned long long* out, cudaStream_t stream);
 

@@ -61,6 +61,16 @@ SIGNATURES = {
     "perform_activation_tanh_backward": (_c_int, [_vp, _vp, _c_long, _vp, _vp, _errp]),
     "perform_activation_leaky_relu_forward": (_c_int, [_vp, _c_long, _c_float, _vp, _vp, _errp]),
     "perform_activation_leaky_relu_backward": (_c_int, [_vp, _vp, _c_long, _c_float, _vp, _vp, _errp]),
+    "perform_activation_softmax_1d_forward": (_c_int, [_vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_softmax_1d_backward": (_c_int, [_vp, _vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_softmax_2d_forward": (_c_int, [_vp, _c_long, _c_long, _vp, _vp, _errp]),
+    "perform_activation_softmax_2d_backward": (_c_int, [_vp, _vp, _c_long, _c_long, _vp, _vp, _errp]),
+    "perform_activation_elu_forward": (_c_int, [_vp, _c_long, _c_float, _vp, _vp, _errp]),
+    "perform_activation_elu_backward": (_c_int, [_vp, _vp, _c_long, _c_float, _vp, _vp, _errp]),
+    "perform_activation_swish_forward": (_c_int, [_vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_swish_backward": (_c_int, [_vp, _vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_gelu_forward": (_c_int, [_vp, _c_long, _vp, _vp, _errp]),
+    "perform_activation_gelu_backward": (_c_int, [_vp, _vp, _c_long, _vp, _vp, _errp]),
     "perform_fused_linear_activation": (
         _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _vp, _c_int, _c_float, _vp, _vp, _errp]),
     "perform_optimized_gemm": (
@@ -291,7 +301,7 @@ def scalar_op(name, a, shape, scalar, c):
 
 
 def activation_forward(name, inp, size, out, alpha=None):
-    """name in {sigmoid, tanh, leaky_relu}."""
+    """name in {sigmoid, tanh, swish, gelu, softmax_1d} or, with alpha, {leaky_relu, elu}."""
     err = CError()
     fn = getattr(lib(), f"perform_activation_{name}_forward")
     if alpha is None:
@@ -307,6 +317,18 @@ def activation_backward(name, grad_out, act_out, size, grad_in, alpha=None):
         _check(fn(grad_out.handle, act_out.handle, size, grad_in.handle, None, ctypes.byref(err)), err)
     else:
         _check(fn(grad_out.handle, act_out.handle, size, alpha, grad_in.handle, None, ctypes.byref(err)), err)
+
+
+def softmax_2d(inp, batch, features, out):
+    err = CError()
+    _check(lib().perform_activation_softmax_2d_forward(inp.handle, batch, features, out.handle, None,
+                                                       ctypes.byref(err)), err)
+
+
+def softmax_2d_backward(grad_out, act_out, batch, features, grad_in):
+    err = CError()
+    _check(lib().perform_activation_softmax_2d_backward(grad_out.handle, act_out.handle, batch, features,
+                                                        grad_in.handle, None, ctypes.byref(err)), err)
 
 
 def batch_matmul(a, b, c, batch, m, n, k):

@@ -144,6 +144,34 @@ GONNGPU_API int perform_activation_leaky_relu_forward(GPUPtr inputPtr, long size
 GONNGPU_API int perform_activation_leaky_relu_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr,
                                            long size, float alpha, GPUPtr gradInputPtr,
                                            DevicePtr mtlDevicePtr, CError *err);
+/* metal_bridge.h:304-331.  Softmax of one vector (1d) or of each row of
+ * [batchSize, features] (2d): exp(x - rowmax) / sum; backward is
+ * grad_in = y * (grad_out - dot(grad_out, y)) per row.  Errors: -1 bad buffer. */
+GONNGPU_API int perform_activation_softmax_1d_forward(GPUPtr inputPtr, long size, GPUPtr outputPtr,
+                                          DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_softmax_1d_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr,
+                                           long size, GPUPtr gradInputPtr, DevicePtr mtlDevicePtr,
+                                           CError *err);
+GONNGPU_API int perform_activation_softmax_2d_forward(GPUPtr inputPtr, long batchSize, long features,
+                                          GPUPtr outputPtr, DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_softmax_2d_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr,
+                                           long batchSize, long features, GPUPtr gradInputPtr,
+                                           DevicePtr mtlDevicePtr, CError *err);
+/* metal_bridge.h:351-395.  ELU(alpha), Swish and tanh-GELU.  The backward
+ * forms take the activation OUTPUT; Swish and GELU recover the input from it
+ * with three Newton steps, as metal_bridge_activation.m:570-600, 665-699 do. */
+GONNGPU_API int perform_activation_elu_forward(GPUPtr inputPtr, long size, float alpha, GPUPtr outputPtr,
+                                   DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_elu_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr, long size,
+                                    float alpha, GPUPtr gradInputPtr, DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_swish_forward(GPUPtr inputPtr, long size, GPUPtr outputPtr,
+                                     DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_swish_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr, long size,
+                                      GPUPtr gradInputPtr, DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_gelu_forward(GPUPtr inputPtr, long size, GPUPtr outputPtr,
+                                    DevicePtr mtlDevicePtr, CError *err);
+GONNGPU_API int perform_activation_gelu_backward(GPUPtr gradOutputPtr, GPUPtr activationOutputPtr, long size,
+                                     GPUPtr gradInputPtr, DevicePtr mtlDevicePtr, CError *err);
 
 /* metal_bridge.h:1348-1353.  output[b,o] = act(sum_i input[b,i]*weight[i,o] +
  * bias[o]); `bias` may be NULL.  activation_type is decoded as the reference's

@@ -278,3 +278,90 @@ void oracle_activation_backward(int kind, const float *grad_out, const float *ac
     }
   }
 }
+
+/* internal/cgo/metal_bridge_activation.m:435-703: ELU, Swish, tanh-GELU.
+ * kind: 3 ELU, 4 Swish, 5 GELU.  The backward forms take the activation
+ * output; Swish and GELU recover the input with three Newton steps. */
+static float clamp88(float x) { return fmaxf(-88.0f, fminf(88.0f, x)); }
+
+void oracle_activation2_forward(int kind, const float *in, float *out, long n, float alpha) {
+  const float k = 0.7978845608028654f, c3 = 0.044715f;
+  for (long i = 0; i < n; i++) {
+    float x = in[i];
+    if (kind == 3) {
+      out[i] = (x > 0.0f) ? x : alpha * (expf(fmaxf(-88.0f, x)) - 1.0f);
+    } else if (kind == 4) {
+      x = clamp88(x);
+      out[i] = x * (1.0f / (1.0f + expf(-x)));
+    } else {
+      float inner = clamp88(k * (x + c3 * (x * x * x)));
+      out[i] = 0.5f * x * (1.0f + tanhf(inner));
+    }
+  }
+}
+
+void oracle_activation2_backward(int kind, const float *grad_out, const float *act_out, float *grad_in,
+                                 long n, float alpha) {
+  const float k = 0.7978845608028654f, c3 = 0.044715f;
+  for (long i = 0; i < n; i++) {
+    const float y = act_out[i];
+    float derivative;
+    if (kind == 3) {
+      derivative = (y > 0.0f) ? 1.0f : y + alpha;
+    } else if (kind == 4) {
+      if (fabsf(y) < 1e-8f) {
+        grad_in[i] = grad_out[i] * 0.5f;
+        continue;
+      }
+      float x = y;
+      for (int it = 0; it < 3; it++) {
+        float sg = 1.0f / (1.0f + expf(-x));
+        float f = x * sg - y;
+        float df = sg + x * sg * (1.0f - sg);
+        if (fabsf(df) > 1e-8f) x = x - f / df;
+      }
+      float sg = 1.0f / (1.0f + expf(-x));
+      derivative = sg + x * sg * (1.0f - sg);
+    } else {
+      float x = y;
+      for (int it = 0; it < 3; it++) {
+        float th = tanhf(clamp88(k * (x + c3 * (x * x * x))));
+        float f = 0.5f * x * (1.0f + th) - y;
+        float df = 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * (k * (1.0f + 3.0f * c3 * x * x));
+        if (fabsf(df) > 1e-8f) x = x - f / df;
+      }
+      float th = tanhf(clamp88(k * (x + c3 * (x * x * x))));
+      derivative = 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * (k * (1.0f + 3.0f * c3 * x * x));
+    }
+    grad_in[i] = grad_out[i] * derivative;
+  }
+}
+
+/* internal/cgo/metal_bridge_activation.m:283-369 (the 1-D forms, :206-281, are
+ * the batch == 1 case): per row, max, exp and running sum, divide; backward
+ * grad_in = y * (grad_out - dot(grad_out, y)). */
+void oracle_softmax_forward(const float *in, float *out, long batch, long features) {
+  for (long b = 0; b < batch; b++) {
+    const float *x = in + b * features;
+    float *y = out + b * features;
+    float m = x[0];
+    for (long i = 1; i < features; i++) m = fmaxf(m, x[i]);
+    float sum = 0.0f;
+    for (long i = 0; i < features; i++) {
+      y[i] = expf(x[i] - m);
+      sum += y[i];
+    }
+    for (long i = 0; i < features; i++) y[i] /= sum;
+  }
+}
+
+void oracle_softmax_backward(const float *grad_out, const float *act, float *grad_in, long batch,
+                             long features) {
+  for (long b = 0; b < batch; b++) {
+    const float *g = grad_out + b * features;
+    const float *y = act + b * features;
+    float dot = 0.0f;
+    for (long i = 0; i < features; i++) dot += g[i] * y[i];
+    for (long i = 0; i < features; i++) grad_in[b * features + i] = y[i] * (g[i] - dot);
+  }
+}

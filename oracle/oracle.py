@@ -280,21 +280,46 @@ def scalar_op(multiply, x, scalar):
 
 
 def activation_forward(kind, x, alpha=0.0):
-    """kind: 0 sigmoid, 1 tanh, 2 leaky ReLU."""
+    """kind: 0 sigmoid, 1 tanh, 2 leaky ReLU, 3 ELU, 4 Swish, 5 GELU."""
     h = lib()
-    h.oracle_activation_forward.argtypes = [_i, _f32p, _f32p, _l, _f]
-    h.oracle_activation_forward.restype = None
+    fn = h.oracle_activation_forward if kind < 3 else h.oracle_activation2_forward
+    fn.argtypes = [_i, _f32p, _f32p, _l, _f]
+    fn.restype = None
     x = _c32(x)
     out = np.empty_like(x)
-    h.oracle_activation_forward(kind, _p32(x), _p32(out), x.size, alpha)
+    fn(kind, _p32(x), _p32(out), x.size, alpha)
     return out
 
 
 def activation_backward(kind, grad_out, act_out, alpha=0.0):
     h = lib()
-    h.oracle_activation_backward.argtypes = [_i, _f32p, _f32p, _f32p, _l, _f]
-    h.oracle_activation_backward.restype = None
+    fn = h.oracle_activation_backward if kind < 3 else h.oracle_activation2_backward
+    fn.argtypes = [_i, _f32p, _f32p, _f32p, _l, _f]
+    fn.restype = None
     g, a = _c32(grad_out), _c32(act_out)
     out = np.empty_like(g)
-    h.oracle_activation_backward(kind, _p32(g), _p32(a), _p32(out), g.size, alpha)
+    fn(kind, _p32(g), _p32(a), _p32(out), g.size, alpha)
     return out
+
+
+def softmax_forward(x):
+    """Row softmax of a [batch, features] array (a vector counts as one row)."""
+    h = lib()
+    h.oracle_softmax_forward.argtypes = [_f32p, _f32p, _l, _l]
+    h.oracle_softmax_forward.restype = None
+    x = _c32(x)
+    x2 = x.reshape(1, -1) if x.ndim == 1 else x
+    out = np.empty_like(x2)
+    h.oracle_softmax_forward(_p32(x2), _p32(out), x2.shape[0], x2.shape[1])
+    return out.reshape(x.shape)
+
+
+def softmax_backward(grad_out, act):
+    h = lib()
+    h.oracle_softmax_backward.argtypes = [_f32p, _f32p, _f32p, _l, _l]
+    h.oracle_softmax_backward.restype = None
+    g, a = _c32(grad_out), _c32(act)
+    g2 = g.reshape(1, -1) if g.ndim == 1 else g
+    out = np.empty_like(g2)
+    h.oracle_softmax_backward(_p32(g2), _p32(a), _p32(out), g2.shape[0], g2.shape[1])
+    return out.reshape(g.shape)

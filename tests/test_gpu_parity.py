@@ -605,3 +605,64 @@ def test_activation_family_matches_oracle(gpu, golden):
     assert abs(vo.retrieve(v.shape)[2] - 0.5) <= 1e-6
     gpu.activation_forward("tanh", vi, v.size, vo)
     assert abs(vo.retrieve(v.shape)[2]) <= 1e-6
+
+
+def test_elu_swish_gelu_match_oracle(gpu, golden):
+    ref, _ = golden
+    rng = np.random.default_rng(10)
+    x = np.concatenate([rng.standard_normal(8190) * 3, [-1e30, -100.0, 0.0, -0.0, 100.0, 1e30]]).astype(np.float32)
+    go = rng.standard_normal(x.size).astype(np.float32)
+    xi, gi = gpu.Buffer.from_host(x), gpu.Buffer.from_host(go)
+    out, gin = gpu.Buffer.empty(x.nbytes), gpu.Buffer.empty(x.nbytes)
+    for kind, name, alpha in ((3, "elu", 0.7), (4, "swish", None), (5, "gelu", None)):
+        gpu.activation_forward(name, xi, x.size, out, alpha)
+        y = out.retrieve(x.shape)
+        assert np.allclose(y, oracle.activation_forward(kind, x, alpha or 0.0), rtol=3e-6, atol=1e-6), name
+        # the backward form is a function of the activation OUTPUT: feed both sides the same one
+        gpu.activation_backward(name, gi, out, x.size, gin, alpha)
+        want = oracle.activation_backward(kind, go, y, alpha or 0.0)
+        got = gin.retrieve(x.shape)
+        ok = np.isfinite(want)
+        # Newton on a flat stretch amplifies an ulp of expf/tanhf: tolerance 1e-4 of the gradient scale
+        assert np.allclose(got[ok], want[ok], rtol=1e-4, atol=1e-4), name
+        assert np.array_equal(np.isfinite(got), ok), name
+    for key, name, alpha in (("elu_forward", "elu", 1.0), ("swish_forward", "swish", None), ("gelu_forward", "gelu", None)):
+        k = ref[key]
+        v = np.array(k["input"], np.float32)
+        vi, vo = gpu.Buffer.from_host(v), gpu.Buffer.empty(v.nbytes)
+        gpu.activation_forward(name, vi, v.size, vo, alpha)
+        r = vo.retrieve(v.shape)
+        if "index_of_zero" in k:
+            assert abs(r[k["index_of_zero"]]) <= 1e-6
+        else:
+            assert abs(r[k["index_of_one"]] - 1.0) <= 1e-6 and r[0] < 0 and r[1] < 0
+
+
+@pytest.mark.parametrize("shape", [(1, 4), (2, 3), (1, 1), (9, 10), (512, 10), (33, 512), (5, 513), (3, 5000), (1, 100000)])
+def test_softmax_rows_match_oracle(gpu, golden, shape):
+    ref, _ = golden
+    rng = np.random.default_rng(shape[0] + shape[1])
+    X = (rng.standard_normal(shape) * 4).astype(np.float32)
+    if shape == (1, 4):
+        X = np.array(ref["softmax_forward"]["input"], np.float32).reshape(shape)
+    if shape == (2, 3):
+        X = np.array(ref["softmax_2d_forward"]["input"], np.float32).reshape(shape)
+    G = rng.standard_normal(shape).astype(np.float32)
+    xi, gi = gpu.Buffer.from_host(X), gpu.Buffer.from_host(G)
+    out, gin = gpu.Buffer.empty(X.nbytes), gpu.Buffer.empty(X.nbytes)
+    gpu.softmax_2d(xi, shape[0], shape[1], out)
+    Y = out.retrieve(shape)
+    want = oracle.softmax_forward(X)
+    # the reference's running float32 sum drifts with the row length; the tree sum here does not
+    # (1.9e-4 at 100000 features, measured against float64), so the band widens with the length
+    assert np.allclose(Y, want, rtol=1e-5 + 3e-9 * shape[1], atol=1e-9)
+    e = np.exp(X.astype(np.float64) - X.max(axis=1, keepdims=True))
+    assert np.allclose(Y, e / e.sum(axis=1, keepdims=True), rtol=5e-6, atol=1e-12)
+    assert (np.abs(Y.sum(axis=1, dtype=np.float64) - 1.0) <= 1e-6).all() and (Y >= 0).all()
+    gpu.softmax_2d_backward(gi, out, shape[0], shape[1], gin)
+    assert np.allclose(gin.retrieve(shape), oracle.softmax_backward(G, Y), rtol=1e-5, atol=1e-6)  # g - dot cancels
+    if shape[0] == 1:
+        gpu.activation_forward("softmax_1d", xi, shape[1], out)
+        assert np.array_equal(out.retrieve(shape), Y)
+        gpu.activation_backward("softmax_1d", gi, out, shape[1], gin)
+        assert np.allclose(gin.retrieve(shape), oracle.softmax_backward(G, Y), rtol=1e-5, atol=1e-6)  # g - dot cancels

@@ -127,3 +127,35 @@ def test_elementwise_family_against_reference_kats_and_numpy(golden):
     # clamping: huge inputs neither overflow nor produce NaN
     big = np.array([-1e30, -100, 100, 1e30], np.float32)
     assert np.isfinite(oracle.activation_forward(0, big)).all() and np.isfinite(oracle.activation_forward(1, big)).all()
+
+
+def test_softmax_elu_swish_gelu_against_reference_properties(golden):
+    ref, _ = golden
+    k = ref["softmax_forward"]
+    s = oracle.softmax_forward(np.array(k["input"], np.float32))
+    assert abs(float(s.sum(dtype=np.float32)) - 1.0) <= 1e-6 and (s > 0).all()
+    k = ref["softmax_2d_forward"]
+    s = oracle.softmax_forward(np.array(k["input"], np.float32).reshape(k["shape"]))
+    assert (np.abs(s.sum(axis=1, dtype=np.float32) - 1.0) <= 1e-6).all()
+    k = ref["elu_forward"]
+    e = oracle.activation_forward(3, np.array(k["input"], np.float32), k["alpha"])
+    assert abs(e[k["index_of_one"]] - 1.0) <= 1e-6 and e[0] < 0 and e[1] < 0
+    for kind, key in ((4, "swish_forward"), (5, "gelu_forward")):
+        k = ref[key]
+        y = oracle.activation_forward(kind, np.array(k["input"], np.float32))
+        assert abs(y[k["index_of_zero"]]) <= 1e-6
+    # independent float64 statement of the same functions
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal(2000) * 3).astype(np.float32)
+    x64 = x.astype(np.float64)
+    assert np.allclose(oracle.activation_forward(3, x, 0.7), np.where(x64 > 0, x64, 0.7 * np.expm1(x64)), atol=1e-6)
+    assert np.allclose(oracle.activation_forward(4, x), x64 / (1 + np.exp(-x64)), atol=1e-6)
+    g = 0.5 * x64 * (1 + np.tanh(0.7978845608028654 * (x64 + 0.044715 * x64 ** 3)))
+    assert np.allclose(oracle.activation_forward(5, x), g, atol=1e-6)
+    X = rng.standard_normal((7, 33)).astype(np.float32)
+    e = np.exp(X.astype(np.float64) - X.max(axis=1, keepdims=True))
+    sm = e / e.sum(axis=1, keepdims=True)
+    assert np.allclose(oracle.softmax_forward(X), sm, atol=1e-6)
+    G = rng.standard_normal((7, 33)).astype(np.float32)
+    assert np.allclose(oracle.softmax_backward(G, sm.astype(np.float32)),
+                       sm * (G - (G * sm).sum(axis=1, keepdims=True)), atol=1e-6)
