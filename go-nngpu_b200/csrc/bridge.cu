@@ -1442,6 +1442,105 @@ int gonngpu_upload(GPUPtr buffer, const float* data, long length_bytes, CError* 
   return 0;
 }
 
+// float64 host data <-> float32 device buffer; the conversion runs on the device,
+// one scratch chunk at a time (stream order makes the reuse of the chunk safe).
+namespace {
+constexpr size_t kF64ChunkElems = size_t(32) << 20;  // 256 MiB of float64 per chunk
+}
+
+int gonngpu_upload_f64(GPUPtr buffer, const double* data, long count, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* b = as_buffer(buffer);
+  if (!b) {
+    set_error(err, "Invalid GPU buffer pointer.");
+    return -1;
+  }
+  if (count < 0 || size_t(count) * 4 > b->bytes || (count > 0 && !data)) {
+    set_error(err, "Buffer length mismatch during float64 upload.");
+    return -2;
+  }
+  if (ensure_device(b->device, err)) return -3;
+  Device& d = g_dev[b->device];
+  if (size_t(count) * 4 < b->bytes && !make_resident(d, b)) {
+    cudaGetLastError();
+    set_error(err, "Host to device copy failed.");
+    return -3;
+  }
+  const size_t n = size_t(count);
+  const size_t chunk = n < kF64ChunkElems ? n : kF64ChunkElems;
+  void* scratch = nullptr;
+  if (n > 0 && pool_alloc(b->device, &scratch, chunk * 8) != cudaSuccess) {
+    cudaGetLastError();
+    set_error(err, "Out of device memory for the float64 staging chunk (%zu bytes).", chunk * 8);
+    return -3;
+  }
+  bool ok = true;
+  for (size_t off = 0; ok && off < n; off += chunk) {
+    const size_t m = n - off < chunk ? n - off : chunk;
+    ok = copy_h2d(d, scratch, data + off, m * 8);
+    if (ok) {
+      gonn::launch_f64_to_f32(static_cast<const double*>(scratch), b->dptr + off, m, d.stream);
+      ++g_stats[3];
+    }
+  }
+  wrote(b);
+  // the scratch chunk goes back to the pool only once the stream is done with it
+  ok = ok && cudaStreamSynchronize(d.stream) == cudaSuccess && cudaGetLastError() == cudaSuccess;
+  if (scratch) pool_free(b->device, scratch, chunk * 8);
+  if (!ok) {
+    cudaGetLastError();
+    set_error(err, "Host to device copy failed.");
+    return -3;
+  }
+  return 0;
+}
+
+int gonngpu_retrieve_f64(GPUPtr buffer, double* data, long count, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  Buffer* b = as_buffer(buffer);
+  if (!b) {
+    set_error(err, "Invalid GPU buffer pointer.");
+    return -1;
+  }
+  if (count < 0 || size_t(count) * 4 > b->bytes || (count > 0 && !data)) {
+    set_error(err, "Buffer length mismatch during float64 retrieval.");
+    return -2;
+  }
+  if (ensure_device(b->device, err)) return -3;
+  Device& d = g_dev[b->device];
+  if (!make_resident(d, b)) {
+    cudaGetLastError();
+    set_error(err, "Host to device copy failed.");
+    return -3;
+  }
+  const size_t n = size_t(count);
+  const size_t chunk = n < kF64ChunkElems ? n : kF64ChunkElems;
+  void* scratch = nullptr;
+  if (n > 0 && pool_alloc(b->device, &scratch, chunk * 8) != cudaSuccess) {
+    cudaGetLastError();
+    set_error(err, "Out of device memory for the float64 staging chunk (%zu bytes).", chunk * 8);
+    return -3;
+  }
+  bool ok = true;
+  for (size_t off = 0; ok && off < n; off += chunk) {
+    const size_t m = n - off < chunk ? n - off : chunk;
+    gonn::launch_f32_to_f64(b->dptr + off, static_cast<double*>(scratch), m, d.stream);
+    ++g_stats[3];
+    ok = copy_d2h(d, data + off, scratch, m * 8);  // complete on return
+  }
+  ok = ok && cudaGetLastError() == cudaSuccess;
+  if (scratch) {
+    cudaStreamSynchronize(d.stream);
+    pool_free(b->device, scratch, chunk * 8);
+  }
+  if (!ok) {
+    cudaGetLastError();
+    set_error(err, "Device to host copy failed.");
+    return -3;
+  }
+  return 0;
+}
+
 int gonngpu_mark_modified(GPUPtr buffer) {
   std::lock_guard<std::recursive_mutex> lk(g_mu);
   Buffer* b = as_buffer(buffer);

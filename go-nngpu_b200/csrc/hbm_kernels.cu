@@ -214,6 +214,45 @@ __global__ void __launch_bounds__(256) relu_bwd_kernel(const float* __restrict__
     gi[i] = (act[i] > 0.0f) ? go[i] : 0.0f;
 }
 
+// float64 <-> float32 for the gonum facade (gpu/matrix/gonum-compat.go:14-42 does
+// float32(m.At(i, j)) per element on the host; :322-334 widens back).  Round to
+// nearest even, overflow to infinity, NaN kept: the conversion Go's float32(x) does.
+__global__ void __launch_bounds__(256) f64_to_f32_kernel(const double* __restrict__ in,
+                                                         float* __restrict__ out, uint64_t n, int vec) {
+  const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+  uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  if (vec) {  // 2 x 16-byte loads, one 16-byte store per thread and step
+    const uint64_t q = n >> 2;
+    for (; i < q; i += stride) {
+      const double2 a = __ldcs(reinterpret_cast<const double2*>(in) + 2 * i);
+      const double2 b = __ldcs(reinterpret_cast<const double2*>(in) + 2 * i + 1);
+      reinterpret_cast<float4*>(out)[i] = make_float4(__double2float_rn(a.x), __double2float_rn(a.y),
+                                                      __double2float_rn(b.x), __double2float_rn(b.y));
+    }
+    const uint64_t t = (q << 2) + blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+    if (t < n) out[t] = __double2float_rn(in[t]);
+  } else {
+    for (; i < n; i += stride) out[i] = __double2float_rn(in[i]);
+  }
+}
+__global__ void __launch_bounds__(256) f32_to_f64_kernel(const float* __restrict__ in,
+                                                         double* __restrict__ out, uint64_t n, int vec) {
+  const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+  uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  if (vec) {
+    const uint64_t q = n >> 2;
+    for (; i < q; i += stride) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(in) + i);
+      reinterpret_cast<double2*>(out)[2 * i] = make_double2(double(v.x), double(v.y));
+      reinterpret_cast<double2*>(out)[2 * i + 1] = make_double2(double(v.z), double(v.w));
+    }
+    const uint64_t t = (q << 2) + blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+    if (t < n) out[t] = double(in[t]);
+  } else {
+    for (; i < n; i += stride) out[i] = double(in[i]);
+  }
+}
+
 // Column sum (bias gradient, gpu/matrix/layers.go:281-294): rows are added in
 // index order per partial, partials in order, so the result is deterministic.
 __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ in,
@@ -300,6 +339,18 @@ void launch_relu_backward(const float* grad_out, const float* act_out, float* gr
                           cudaStream_t stream) {
   if (n == 0) return;
   relu_bwd_kernel<<<stream_grid(n, 256, 148 * 16), 256, 0, stream>>>(grad_out, act_out, grad_in, n);
+}
+
+void launch_f64_to_f32(const double* in, float* out, uint64_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  const int vec = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0 && n >= 4;
+  f64_to_f32_kernel<<<stream_grid(vec ? n >> 2 : n, 256, 148 * 16), 256, 0, stream>>>(in, out, n, vec);
+}
+
+void launch_f32_to_f64(const float* in, double* out, uint64_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  const int vec = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0 && n >= 4;
+  f32_to_f64_kernel<<<stream_grid(vec ? n >> 2 : n, 256, 148 * 16), 256, 0, stream>>>(in, out, n, vec);
 }
 
 void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream,

@@ -92,6 +92,10 @@ void launch_relu_backward(const float* grad_out, const float* act_out, float* gr
 void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream,
                    const float* mask = nullptr);
 
+// float64 <-> float32 (round to nearest even), for the gonum facade's host data.
+void launch_f64_to_f32(const double* in, float* out, uint64_t n, cudaStream_t stream);
+void launch_f32_to_f64(const float* in, double* out, uint64_t n, cudaStream_t stream);
+
 // ---- element-wise family ----------------------------------------------------------
 enum EwOp : int {
   EW_ADD = 0, EW_SUB, EW_MUL, EW_DIV, EW_SCALAR_ADD, EW_SCALAR_MUL,

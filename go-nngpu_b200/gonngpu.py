@@ -95,6 +95,8 @@ SIGNATURES = {
     "gonngpu_wrap_device_memory": (_c_int, [_vp, _c_long, ctypes.POINTER(_vp), _errp]),
     "gonngpu_device_address": (_vp, [_vp]),
     "gonngpu_upload": (_c_int, [_vp, _vp, _c_long, _errp]),
+    "gonngpu_upload_f64": (_c_int, [_vp, _vp, _c_long, _errp]),
+    "gonngpu_retrieve_f64": (_c_int, [_vp, _vp, _c_long, _errp]),
     "gonngpu_mark_modified": (_c_int, [_vp]),
     "gonngpu_host_alloc": (_vp, [_c_long]),
     "gonngpu_host_free": (None, [_vp]),
@@ -176,6 +178,20 @@ class Buffer:
         a = np.ascontiguousarray(array, dtype=np.float32)
         err = CError()
         _check(lib().gonngpu_upload(self.handle, _np_ptr(a), a.nbytes, ctypes.byref(err)), err)
+
+    def upload_f64(self, array):
+        """float64 host data, narrowed to float32 on the device."""
+        a = np.ascontiguousarray(array, dtype=np.float64)
+        err = CError()
+        _check(lib().gonngpu_upload_f64(self.handle, _np_ptr(a), a.size, ctypes.byref(err)), err)
+
+    def retrieve_f64(self, shape, out=None):
+        """The float32 contents widened to float64 on the device."""
+        if out is None:
+            out = np.empty(shape, dtype=np.float64)
+        err = CError()
+        _check(lib().gonngpu_retrieve_f64(self.handle, _np_ptr(out), out.size, ctypes.byref(err)), err)
+        return out
 
     def retrieve(self, shape):
         out = np.empty(shape, dtype=np.float32)

@@ -113,6 +113,16 @@ class Tensor {
     isOnGPU_ = false;
   }
 
+  // Takes over a device buffer that already holds this tensor's values (Data is
+  // stale until RetrieveCPU).  No counterpart in the reference, whose buffers
+  // always alias Data; used by the float64 facade to skip the host conversion.
+  void AdoptGPU(GPUPtr p, DevicePtr d) {
+    ReleaseGPU();
+    gpuPtr_ = p;
+    devicePtr_ = d;
+    isOnGPU_ = true;
+  }
+
   GPUPtr GPUPointer() const { return gpuPtr_; }        // tensor.go:206 (GPUPtr)
   DevicePtr DevicePointer() const { return devicePtr_; }  // tensor.go:212 (DevicePtr)
   bool IsOnGPU() const { return isOnGPU_; }
@@ -477,8 +487,17 @@ class GPUDense : public mat::Matrix {
   void Mul(const mat::Matrix& a, const mat::Matrix& b);  // :83-110
 
   std::shared_ptr<mat::Dense> ToGonum() const {  // :322-334
-    tensor_->RetrieveCPU();
     const auto [rows, cols] = Dims();
+    if (tensor_->IsOnGPU() && tensor_->GPUPointer()) {
+      // widened on the device and copied out as float64: no float32 host pass
+      std::vector<double> d(size_t(rows) * cols);
+      CError err{nullptr};
+      const int rc = gonngpu_retrieve_f64(tensor_->GPUPointer(), d.data(), long(d.size()), &err);
+      if (rc != 0)
+        throw gonngpu::Panic("failed to retrieve GPU buffer data (code " + std::to_string(rc) +
+                             "): " + gonngpu::detail::take_message(err));
+      return mat::NewDense(rows, cols, std::move(d));
+    }
     std::vector<double> d(tensor_->Data.begin(), tensor_->Data.end());
     return mat::NewDense(rows, cols, std::move(d));
   }
@@ -503,6 +522,24 @@ inline std::shared_ptr<GPUDense> NewGPUDense(int rows, int cols, const std::vect
 // gonum-compat.go:30-42
 inline std::shared_ptr<GPUDense> FromGonum(const mat::Matrix& m) {
   const auto [rows, cols] = m.Dims();
+  if (auto* dense = dynamic_cast<const mat::Dense*>(&m)) {
+    // A gonum Dense exposes its float64 backing slice (RawMatrix().Data): it goes to
+    // the device as it is and is narrowed there, instead of rows*cols At() calls.
+    const std::vector<double>& raw = dense->RawData();
+    auto t = tensor::NewTensor({rows, cols}, std::vector<float>(raw.size()));
+    CError err{nullptr};
+    GPUPtr p = nullptr;
+    int rc = gonngpu_alloc_device_buffer(long(raw.size() * sizeof(float)), &p, &err);
+    if (rc == 0) {
+      rc = gonngpu_upload_f64(p, raw.data(), long(raw.size()), &err);
+      if (rc != 0) release_gpu_buffer(p);
+    }
+    if (rc != 0)
+      throw gonngpu::Panic("failed to create GPU buffer (code " + std::to_string(rc) +
+                           "): " + gonngpu::detail::take_message(err));
+    t->AdoptGPU(p, nullptr);
+    return std::make_shared<GPUDense>(t);
+  }
   std::vector<double> data(size_t(rows) * cols);
   for (int i = 0; i < rows; ++i)
     for (int j = 0; j < cols; ++j) data[size_t(i) * cols + j] = m.At(i, j);
@@ -541,12 +578,10 @@ inline std::shared_ptr<mat::Dense> GPUMatMul(const mat::Matrix& a, const mat::Ma
   TensorPtr result;
   try {
     result = MatMul(ga->GetTensor(), gb->GetTensor());
-    result->RetrieveCPU();
   } catch (const gonngpu::Error& e) {
     throw gonngpu::Panic(e.what());
   }
-  std::vector<double> d(result->Data.begin(), result->Data.end());
-  auto out = mat::NewDense(result->Shape[0], result->Shape[1], std::move(d));
+  auto out = GPUDense(result).ToGonum();  // float64 straight from the device
   result->ReleaseGPU();
   ga->ReleaseGPU();
   gb->ReleaseGPU();

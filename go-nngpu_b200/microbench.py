@@ -1,6 +1,6 @@
 """Per-configuration timings of the dense path on one GPU (device-resident inputs).
 
-    python go-nngpu_b200/microbench.py [--config c1|c2|c2t|transpose|c3|c4|all] [--iters N]
+    python go-nngpu_b200/microbench.py [--config c1|c2|c2nn|transpose|c3|c4|gonum|elementwise|all] [--iters N]
 
 Prints one JSON line per measured operation: time, TFLOP/s or GB/s, and the
 fraction of the measured peaks when MEASURED_PEAKS.json lies beside the
@@ -140,6 +140,67 @@ def config4(iters):
     gemm_case("c4 fp16-in/fp32-acc 8192^3 A.B", A, B, False, False, g.FP16_RN, iters)
 
 
+def gonum_facade(iters, n=4096):
+    """GPUDense.Mul as a gonum user calls it: float64 matrices on the host in,
+    float64 product out, everything inside the timed region.  `host` narrows and
+    widens on the CPU (what FromGonum / ToGonum do in the reference, here with
+    numpy's vector loops instead of per-element At calls); `device` sends the
+    float64 data as it is and converts on the GPU."""
+    rng = np.random.default_rng(1)
+    A = rng.standard_normal((n, n)) / 64
+    B = rng.standard_normal((n, n)) / 64
+    pa, pb, pc = (g.pinned_array((n, n), np.float64)[0] for _ in range(3))
+    pa[:], pb[:] = A, B
+    a, b, c = g.Buffer.empty(n * n * 4), g.Buffer.empty(n * n * 4), g.Buffer.empty(n * n * 4)
+    fa, fb, fc = (g.pinned_array((n, n), np.float32)[0] for _ in range(3))
+    iters = max(3, iters // 10)
+
+    def host_path():
+        np.copyto(fa, pa, casting="same_kind")
+        np.copyto(fb, pb, casting="same_kind")
+        a.upload(fa)
+        b.upload(fb)
+        g.matmul(a, (n, n), b, (n, n), c, (n, n))
+        c.retrieve_into(fc)
+        np.copyto(pc, fc)
+
+    def device_path():
+        a.upload_f64(pa)
+        b.upload_f64(pb)
+        g.matmul(a, (n, n), b, (n, n), c, (n, n))
+        c.retrieve_f64((n, n), out=pc)
+
+    for name, fn in (("host conversion", host_path), ("device conversion", device_path)):
+        fn()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            fn()
+        dt = (time.perf_counter() - t0) / iters
+        emit(f"gonum facade {n}^3 float64 in/out, {name}", dt, flops=2.0 * n ** 3,
+             extra={"pcie_bytes": (3 * n * n * 8) if fn is device_path else (3 * n * n * 4)})
+    for x in (a, b, c):
+        x.release()
+
+
+def elementwise_family(iters, n=8192):
+    """HBM-bound members of the family on [n, n] float32 (256 MiB per operand)."""
+    rng = np.random.default_rng(6)
+    X = rng.standard_normal((n, n)).astype(np.float32)
+    a, b, c = g.Buffer.from_host(X), g.Buffer.from_host(X + np.float32(3.0)), g.Buffer.empty(X.nbytes)
+    nb = float(X.nbytes)
+    emit(f"add {n}x{n}", timed(lambda s: g.elementwise("add", a, b, c, X.shape), iters), bytes_=3 * nb)
+    emit(f"scalar_multiply {n}x{n}", timed(lambda s: g.scalar_op("scalar_multiply", a, X.shape, 1.5, c), iters), bytes_=2 * nb)
+    emit(f"sigmoid {n}x{n}", timed(lambda s: g.activation_forward("sigmoid", a, X.size, c), iters), bytes_=2 * nb)
+    emit(f"gelu {n}x{n}", timed(lambda s: g.activation_forward("gelu", a, X.size, c), iters), bytes_=2 * nb)
+    emit(f"gelu backward {n}x{n}", timed(lambda s: g.activation_backward("gelu", a, c, X.size, b), iters), bytes_=3 * nb)
+    emit(f"softmax rows {n}x{n}", timed(lambda s: g.softmax_2d(a, n, n, c), iters), bytes_=2 * nb)
+    emit(f"softmax rows {n * n // 16}x16", timed(lambda s: g.softmax_2d(a, n * n // 16, 16, c), iters), bytes_=2 * nb)
+    emit(f"softmax rows {n * n // 10}x10", timed(lambda s: g.softmax_2d(a, n * n // 10, 10, c), iters),
+         bytes_=2.0 * (n * n // 10) * 40)
+    for x in (a, b, c):
+        x.release()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="all")
@@ -149,7 +210,8 @@ def main():
     run = {"c1": lambda: config1(args.iters), "c2": lambda: config2(args.iters),
            "c2nn": lambda: config2(args.iters, transposes=False),
            "transpose": lambda: transpose_case(args.iters), "c3": lambda: config3(args.iters),
-           "c4": lambda: config4(args.iters)}
+           "c4": lambda: config4(args.iters), "gonum": lambda: gonum_facade(args.iters),
+           "elementwise": lambda: elementwise_family(args.iters)}
     names = ["c1", "c2", "transpose", "c3", "c4"] if args.config == "all" else [args.config]
     for n in names:
         run[n]()

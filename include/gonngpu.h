@@ -286,6 +286,14 @@ GONNGPU_API int gonngpu_wrap_device_memory(void *device_ptr, long length_bytes, 
 GONNGPU_API void *gonngpu_device_address(GPUPtr buffer);
 /* Copies `length_bytes` from host `data` into the buffer now. */
 GONNGPU_API int gonngpu_upload(GPUPtr buffer, const float *data, long length_bytes, CError *err);
+/* float64 host data into / out of a float32 buffer, converted on the device
+ * (round to nearest even, as Go's float32(x)).  They replace the per-element
+ * host loops of FromGonum / ToGonum (gpu/matrix/gonum-compat.go:14-42, 322-334):
+ * the Go side passes mat.Dense.RawMatrix().Data.  `count` is in elements.
+ * Both return after the data has arrived.  Errors: -1 bad handle, -2 length,
+ * -3 copy or memory failure. */
+GONNGPU_API int gonngpu_upload_f64(GPUPtr buffer, const double *data, long count, CError *err);
+GONNGPU_API int gonngpu_retrieve_f64(GPUPtr buffer, double *data, long count, CError *err);
 /* Tells the library the caller changed the device contents behind a wrapped
  * handle, so cached operand planes are rebuilt. */
 GONNGPU_API int gonngpu_mark_modified(GPUPtr buffer);

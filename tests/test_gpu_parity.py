@@ -638,7 +638,10 @@ def test_elu_swish_gelu_match_oracle(gpu, golden):
             assert abs(r[k["index_of_one"]] - 1.0) <= 1e-6 and r[0] < 0 and r[1] < 0
 
 
-@pytest.mark.parametrize("shape", [(1, 4), (2, 3), (1, 1), (9, 10), (512, 10), (33, 512), (5, 513), (3, 5000), (1, 100000)])
+@pytest.mark.parametrize("shape", [(1, 4), (2, 3), (1, 1), (9, 10), (512, 10), (33, 512), (5, 513), (3, 5000),
+                                   (1, 100000), (1001, 3), (777, 8), (130, 20), (67, 100), (19, 300), (7, 1000),
+                                   (9, 2048), (5, 3000), (3, 4095), (300, 8192), (2, 9000), (2, 9001), (1003, 4), (517, 16),
+                                   (99, 28), (50, 128), (21, 260), (11, 512)])
 def test_softmax_rows_match_oracle(gpu, golden, shape):
     ref, _ = golden
     rng = np.random.default_rng(shape[0] + shape[1])
@@ -660,9 +663,50 @@ def test_softmax_rows_match_oracle(gpu, golden, shape):
     assert np.allclose(Y, e / e.sum(axis=1, keepdims=True), rtol=5e-6, atol=1e-12)
     assert (np.abs(Y.sum(axis=1, dtype=np.float64) - 1.0) <= 1e-6).all() and (Y >= 0).all()
     gpu.softmax_2d_backward(gi, out, shape[0], shape[1], gin)
-    assert np.allclose(gin.retrieve(shape), oracle.softmax_backward(G, Y), rtol=1e-5, atol=1e-6)  # g - dot cancels
+    # g - dot cancels, and the reference's running float32 dot drifts with the row length
+    GI = gin.retrieve(shape)
+    assert np.allclose(GI, oracle.softmax_backward(G, Y), rtol=1e-5, atol=1e-6 + 2e-9 * shape[1])
+    Y64, G64 = Y.astype(np.float64), G.astype(np.float64)
+    assert np.allclose(GI, Y64 * (G64 - (G64 * Y64).sum(axis=1, keepdims=True)), rtol=1e-5, atol=3e-7)
     if shape[0] == 1:
         gpu.activation_forward("softmax_1d", xi, shape[1], out)
         assert np.array_equal(out.retrieve(shape), Y)
         gpu.activation_backward("softmax_1d", gi, out, shape[1], gin)
-        assert np.allclose(gin.retrieve(shape), oracle.softmax_backward(G, Y), rtol=1e-5, atol=1e-6)  # g - dot cancels
+        assert np.array_equal(gin.retrieve(shape), GI)
+
+
+# ------------------------------------------------------------------ float64 facade data
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 1023, 4097, 1 << 20])
+def test_float64_upload_and_retrieve_are_bit_exact(gpu, n):
+    rng = np.random.default_rng(n + 17)
+    x = rng.standard_normal(n) * 10.0 ** rng.integers(-30, 30, n)
+    if n >= 1023:
+        x[:8] = [0.0, -0.0, np.inf, -np.inf, 1e39, -1e39, 1e-46, np.float64(np.float32(1.0)) + 2.0 ** -24]
+        x[8] = np.nan
+    buf = gpu.Buffer.empty(max(n, 1) * 4)
+    buf.upload_f64(x)
+    want = x.astype(np.float32)                    # IEEE round-to-nearest-even, like Go's float32(v)
+    got = buf.retrieve((n,))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    back = buf.retrieve_f64((n,))
+    assert np.array_equal(back.view(np.uint64), want.astype(np.float64).view(np.uint64))
+    # a partial upload keeps the tail
+    if n >= 4:
+        buf.upload_f64(np.full(n // 2, 2.5))
+        got = buf.retrieve((n,))
+        assert (got[: n // 2] == 2.5).all() and np.array_equal(got[n // 2:].view(np.uint32), want[n // 2:].view(np.uint32))
+    with pytest.raises(gpu.GonnError) as e:
+        buf.upload_f64(np.zeros(max(n, 1) + 1))
+    assert e.value.code == -2
+
+
+def test_float64_facade_feeds_the_gemm(gpu):
+    rng = np.random.default_rng(23)
+    A, B = rng.standard_normal((300, 200)), rng.standard_normal((200, 150))
+    a, b, c = gpu.Buffer.empty(A.size * 4), gpu.Buffer.empty(B.size * 4), gpu.Buffer.empty(300 * 150 * 4)
+    a.upload_f64(A)
+    b.upload_f64(B)
+    gpu.matmul(a, A.shape, b, B.shape, c, (300, 150))
+    C = c.retrieve_f64((300, 150))
+    ref = oracle.gemm_f64(A.astype(np.float32), B.astype(np.float32))
+    assert C.dtype == np.float64 and oracle.rel_frobenius(C, ref) <= FP32_TOL
