@@ -362,9 +362,20 @@ struct MatmulArgs {
 // retrieve_gpu_buffer_data into the same memory has nothing left to do.
 // Returns 1 when the product was done here, 0 when the caller should take the
 // ordinary path, -1 on a CUDA error.
-constexpr long kStreamRows = 8192;
+// Rows per block: small enough that the first upload and the last write-back, which
+// nothing overlaps, are short; large enough that a block's product fills the GPU.
+// GONNGPU_STREAM_ROWS (a multiple of 512, >= 1024) overrides it.
+long stream_rows() {
+  static const long rows = [] {
+    const char* e = std::getenv("GONNGPU_STREAM_ROWS");
+    const long v = e ? std::atol(e) : 0;
+    return (v >= 1024 && v % 512 == 0) ? v : 4096l;
+  }();
+  return rows;
+}
 int matmul_streamed(Device& d, Buffer* A, Buffer* B, Buffer* C, Buffer* bias, long M, long N, long K,
                     bool transB, int pkind, float alpha, int act, float act_param, const char** msg) {
+  const long kStreamRows = stream_rows();
   if (pkind == 2 || !g_blocking || !A->host_pending || !C->host || M < 2 * kStreamRows) return 0;
   if (!host_is_pinned(A->host) || !host_is_pinned(C->host)) return 0;
   if (!make_resident(d, B) || (bias && !make_resident(d, bias))) return -1;

@@ -227,63 +227,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
       }
     }
   } else if (warp == 1) {
-    // ---------------------------------------------------------- MMA issuer
-    uint32_t stage = 0, phase = 0;
-    uint32_t local = 0;
-    bool alive = true;
-    for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x, ++local) {
-      const uint32_t acc = local & 1u;
-      const uint32_t acc_phase = (local >> 1) & 1u;
-      bool ok = ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) {
-        if (lane == 0) {
+    // ------------------------------------------- MMA issuer: one thread
+    // (next stage's barrier tested without blocking, descriptors advanced by
+    // 32-bit adds: see gemm_tf32x3_kernel)
+    if (lane == 0) {
+      const uint32_t a_hi32 = uint32_t(p.a.desc >> 32), b_hi32 = uint32_t(p.b.desc >> 32);
+      const uint32_t a_lo0 = uint32_t(p.a.desc), b_lo0 = uint32_t(p.b.desc);
+      const uint32_t a_step = p.a.kstep_bytes >> 4, b_step = p.b.kstep_bytes >> 4;
+      uint32_t stage = 0, phase = 0;
+      uint32_t local = 0;
+      uint32_t ready = 0;
+      bool alive = true;
+      for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x, ++local) {
+        const uint32_t acc = local & 1u;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           *abort_flag = 1;
           report(p.status, 2, 0x100u | acc, t, 0);
-        }
-        break;
-      }
-      ptx::tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-      for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
-        ok = ptx::mbar_wait(full_bar(stage), phase, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-          if (lane == 0) {
-            *abort_flag = 1;
-            report(p.status, 2, stage, t, kb);
-          }
-          alive = false;
           break;
         }
         ptx::tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
-          const uint32_t b_addr = a_addr + PLANES * A_TILE_BYTES;
+        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
+          if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
+            *abort_flag = 1;
+            report(p.status, 2, stage, t, kb);
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
+          const uint32_t next_phase = (stage + 1 == STAGES) ? phase ^ 1u : phase;
+          const uint32_t ready_next = ptx::mbar_test_wait(full_bar(next_stage), next_phase);
+          const uint32_t st = smem_base + stage * STAGE_BYTES;
+          const uint32_t ah = a_lo0 + (st >> 4);
+          const uint32_t bh = b_lo0 + ((st + PLANES * A_TILE_BYTES) >> 4);
 #pragma unroll
           for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
             const uint32_t accum = (kb | ks) ? 1u : 0u;
-            const uint64_t a_hi = ptx::smem_desc_at(p.a.desc, a_addr + ks * p.a.kstep_bytes);
-            const uint64_t b_hi = ptx::smem_desc_at(p.b.desc, b_addr + ks * p.b.kstep_bytes);
             if (KIND == int(Kind::F16)) {
-              ptx::mma_f16(d_tmem, a_hi, b_hi, p.idesc, accum);
+              ptx::mma_f16_lohi(d_tmem, ah + ks * a_step, a_hi32, bh + ks * b_step, b_hi32, p.idesc, accum);
             } else {
-              const uint64_t a_lo =
-                  ptx::smem_desc_at(p.a.desc, a_addr + A_TILE_BYTES + ks * p.a.kstep_bytes);
-              const uint64_t b_lo =
-                  ptx::smem_desc_at(p.b.desc, b_addr + B_TILE_BYTES + ks * p.b.kstep_bytes);
-              ptx::mma_tf32(d_tmem, a_lo, b_hi, p.idesc, accum);
-              ptx::mma_tf32(d_tmem, a_hi, b_lo, p.idesc, 1u);
-              ptx::mma_tf32(d_tmem, a_hi, b_hi, p.idesc, 1u);
+              const uint32_t al = ah + (A_TILE_BYTES >> 4), bl = bh + (B_TILE_BYTES >> 4);
+              ptx::mma_tf32_lohi(d_tmem, al + ks * a_step, a_hi32, bh + ks * b_step, b_hi32, p.idesc, accum);
+              ptx::mma_tf32_lohi(d_tmem, ah + ks * a_step, a_hi32, bl + ks * b_step, b_hi32, p.idesc, 1u);
+              ptx::mma_tf32_lohi(d_tmem, ah + ks * a_step, a_hi32, bh + ks * b_step, b_hi32, p.idesc, 1u);
             }
           }
           ptx::mma_commit(empty_bar(stage));  // stage reusable once these MMAs retired
           if (kb + 1 == p.num_kblocks) ptx::mma_commit(tfull_bar(acc));
-        }
-        __syncwarp();
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1u;
+          stage = next_stage;
+          phase = next_phase;
+          ready = ready_next;
         }
       }
     }
@@ -1171,62 +1166,58 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
       }
     }
   } else if (warp == 1) {
-    // ---------------------------------------------------------- MMA issuer
-    uint32_t stage = 0, phase = 0;
-    uint32_t chunk = 0;  // running chunk count: selects accumulator and barrier parity
-    bool alive = true;
-    for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
-      for (uint32_t kb0 = 0; alive && kb0 < p.num_kblocks; kb0 += CHUNK_KB, ++chunk) {
-        const uint32_t acc = chunk & 1u;
-        const uint32_t acc_phase = (chunk >> 1) & 1u;
-        bool ok = ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-          if (lane == 0) {
+    // ------------------------------------------- MMA issuer: one thread
+    // The next stage's barrier is tested without blocking before this stage's
+    // MMAs go out, and descriptors advance by 32-bit adds, so that issuing a
+    // 64-cycle MMA costs the thread less than the MMA takes.
+    if (lane == 0) {
+      const uint32_t a_hi32 = uint32_t(p.a.desc >> 32), b_hi32 = uint32_t(p.b.desc >> 32);
+      const uint32_t a_lo0 = uint32_t(p.a.desc), b_lo0 = uint32_t(p.b.desc);
+      const uint32_t a_step = p.a.kstep_bytes >> 4, b_step = p.b.kstep_bytes >> 4;
+      uint32_t stage = 0, phase = 0;
+      uint32_t chunk = 0;  // running chunk count: selects accumulator and barrier parity
+      uint32_t ready = 0;
+      bool alive = true;
+      for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
+        for (uint32_t kb0 = 0; alive && kb0 < p.num_kblocks; kb0 += CHUNK_KB, ++chunk) {
+          const uint32_t acc = chunk & 1u;
+          const uint32_t acc_phase = (chunk >> 1) & 1u;
+          if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
             *abort_flag = 1;
             report(p.status, 2, 0x100u | acc, t, kb0);
-          }
-          alive = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-        const uint32_t kb_end = min(kb0 + CHUNK_KB, p.num_kblocks);
-        for (uint32_t kb = kb0; kb < kb_end; ++kb) {
-          ok = ptx::mbar_wait(full_bar(stage), phase, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) {
-            if (lane == 0) {
-              *abort_flag = 1;
-              report(p.status, 2, stage, t, kb);
-            }
             alive = false;
             break;
           }
           ptx::tc_fence_after();
-          if (lane == 0) {
-            const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
-            const uint32_t b_addr = a_addr + 2 * A_TILE_BYTES;
+          const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+          const uint32_t kb_end = min(kb0 + CHUNK_KB, p.num_kblocks);
+          for (uint32_t kb = kb0; kb < kb_end; ++kb) {
+            if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
+              *abort_flag = 1;
+              report(p.status, 2, stage, t, kb);
+              alive = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
+            const uint32_t next_phase = (stage + 1 == STAGES) ? phase ^ 1u : phase;
+            const uint32_t ready_next = ptx::mbar_test_wait(full_bar(next_stage), next_phase);
+            const uint32_t st = smem_base + stage * STAGE_BYTES;
+            const uint32_t ah = a_lo0 + (st >> 4), al = a_lo0 + ((st + A_TILE_BYTES) >> 4);
+            const uint32_t bh = b_lo0 + ((st + 2 * A_TILE_BYTES) >> 4);
+            const uint32_t bl = b_lo0 + ((st + 2 * A_TILE_BYTES + B_TILE_BYTES) >> 4);
 #pragma unroll
             for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
               const uint32_t accum = ((kb - kb0) | ks) ? 1u : 0u;
-              const uint64_t a_hi = ptx::smem_desc_at(p.a.desc, a_addr + ks * p.a.kstep_bytes);
-              const uint64_t b_hi = ptx::smem_desc_at(p.b.desc, b_addr + ks * p.b.kstep_bytes);
-              const uint64_t a_lo =
-                  ptx::smem_desc_at(p.a.desc, a_addr + A_TILE_BYTES + ks * p.a.kstep_bytes);
-              const uint64_t b_lo =
-                  ptx::smem_desc_at(p.b.desc, b_addr + B_TILE_BYTES + ks * p.b.kstep_bytes);
-              ptx::mma_tf32(d_tmem, a_lo, b_hi, p.idesc, accum);
-              ptx::mma_tf32(d_tmem, a_hi, b_lo, p.idesc, 1u);
-              ptx::mma_tf32(d_tmem, a_hi, b_hi, p.idesc, 1u);
+              ptx::mma_tf32_lohi(d_tmem, al + ks * a_step, a_hi32, bh + ks * b_step, b_hi32, p.idesc, accum);
+              ptx::mma_tf32_lohi(d_tmem, ah + ks * a_step, a_hi32, bl + ks * b_step, b_hi32, p.idesc, 1u);
+              ptx::mma_tf32_lohi(d_tmem, ah + ks * a_step, a_hi32, bh + ks * b_step, b_hi32, p.idesc, 1u);
             }
             ptx::mma_commit(empty_bar(stage));
             if (kb + 1 == kb_end) ptx::mma_commit(tfull_bar(acc));
-          }
-          __syncwarp();
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+            stage = next_stage;
+            phase = next_phase;
+            ready = ready_next;
           }
         }
       }

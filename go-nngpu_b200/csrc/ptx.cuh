@@ -171,6 +171,38 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 // Arrive on `bar` once every tcgen05.mma issued so far by this thread retired.
+// The same MMAs with each descriptor given as two 32-bit halves: the issuing
+// thread advances the start-address field with 32-bit adds.
+__device__ __forceinline__ void mma_f16_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                             uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      ".reg .b64 DA, DB;\n\t"
+      "mov.b64 DA, {%1, %2};\n\t"
+      "mov.b64 DB, {%3, %4};\n\t"
+      "setp.ne.b32 P, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], DA, DB, %5, P;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_tf32_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                              uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      ".reg .b64 DA, DB;\n\t"
+      "mov.b64 DA, {%1, %2};\n\t"
+      "mov.b64 DB, {%3, %4};\n\t"
+      "setp.ne.b32 P, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], DA, DB, %5, P;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                ::"r"(bar) : "memory");
