@@ -60,6 +60,8 @@ struct Device {
   GemmStatus* status_dev = nullptr;
   GemmStatus last_status{};
   unsigned long long* first_zero_dev = nullptr;  // scratch word of the element-wise divide
+  float* splitk_ws = nullptr;                    // partial sums of split fp32 products
+  uint32_t* splitk_counters = nullptr;           // per-tile arrival counters (zero between launches)
   void* stage[2] = {nullptr, nullptr};
   cudaEvent_t stage_ev[2] = {nullptr, nullptr};
 };
@@ -69,6 +71,20 @@ int g_current = 0;
 bool g_blocking = true;
 bool g_plane_cache = true;
 gonn::GemmTuning g_tune;
+// Split-K workspace per device: room for one wave of 128 x 256 partial tiles.
+constexpr size_t kSplitKBytes = size_t(24) << 20;
+constexpr uint32_t kSplitKSlots = 4096;
+
+// The tuning of a launch on the device's own compute stream: the global settings
+// plus that device's split-K workspace (launches on one stream never overlap).
+gonn::GemmTuning tune_for(const Device& d) {
+  gonn::GemmTuning t = g_tune;
+  t.splitk_ws = d.splitk_ws;
+  t.splitk_ws_bytes = kSplitKBytes;
+  t.splitk_counters = d.splitk_counters;
+  t.splitk_counter_slots = kSplitKSlots;
+  return t;
+}
 std::unordered_set<Buffer*> g_buffers;
 long g_stats[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 
@@ -155,7 +171,10 @@ int ensure_device(int ordinal, CError* err) {
                           cudaHostAllocMapped) == cudaSuccess &&
             cudaHostGetDevicePointer(reinterpret_cast<void**>(&d.status_dev), d.status_host, 0) ==
                 cudaSuccess &&
-            cudaMalloc(reinterpret_cast<void**>(&d.first_zero_dev), 8) == cudaSuccess;
+            cudaMalloc(reinterpret_cast<void**>(&d.first_zero_dev), 8) == cudaSuccess &&
+            cudaMalloc(reinterpret_cast<void**>(&d.splitk_ws), kSplitKBytes) == cudaSuccess &&
+            cudaMalloc(reinterpret_cast<void**>(&d.splitk_counters), kSplitKSlots * 4) == cudaSuccess &&
+            cudaMemset(d.splitk_counters, 0, kSplitKSlots * 4) == cudaSuccess;
   for (int i = 0; ok && i < 2; ++i) {
     ok = cudaHostAlloc(&d.stage[i], kStageBytes, cudaHostAllocDefault) == cudaSuccess &&
          cudaEventCreateWithFlags(&d.stage_ev[i], cudaEventDisableTiming) == cudaSuccess;
@@ -558,7 +577,7 @@ int matmul_core(const MatmulArgs& m, const int codes[6], const char* what, CErro
   epi.act_param = m.act_param;
   const char* msg = gonn::launch_gemm(pkind == 2 ? gonn::Kind::TF32x3 : gonn::Kind::F16, uint32_t(M),
                                       uint32_t(N), uint32_t(K), oa, ob, C->dptr, uint64_t(N), epi,
-                                      d.status_dev, d.sm_count, g_tune, d.stream);
+                                      d.status_dev, d.sm_count, tune_for(d), d.stream);
   if (msg) {
     cudaGetLastError();
     set_error(err, "%s: %s", what, msg);
@@ -1202,7 +1221,7 @@ int perform_batch_matmul_optimized(GPUPtr aPtr, GPUPtr bPtr, GPUPtr cPtr, long b
   }
   gonn::GemmEpilogue epi;
   const char* msg = gonn::launch_gemm(gonn::Kind::TF32x3, uint32_t(M), uint32_t(N), uint32_t(K), oa, ob,
-                                      C->dptr, uint64_t(N), epi, d.status_dev, d.sm_count, g_tune,
+                                      C->dptr, uint64_t(N), epi, d.status_dev, d.sm_count, tune_for(d),
                                       d.stream, &gb);
   if (thi) {
     pool_free(C->device, thi, tbytes);
@@ -1307,7 +1326,7 @@ int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOu
         b.mn_major = true;
         msg = gonn::launch_gemm(gonn::Kind::TF32x3, uint32_t(in_size), uint32_t(out_size),
                                 uint32_t(batch), a, b, dW->dptr, uint64_t(out_size), epi, d.status_dev,
-                                d.sm_count, g_tune, d.stream);
+                                d.sm_count, tune_for(d), d.stream);
         if (!msg) {
           ++g_stats[3];
           ++g_stats[4];
@@ -1330,7 +1349,7 @@ int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOu
         b.mn_major = false;
         msg = gonn::launch_gemm(gonn::Kind::TF32x3, uint32_t(batch), uint32_t(in_size),
                                 uint32_t(out_size), a, b, dX->dptr, uint64_t(in_size), epi,
-                                d.status_dev, d.sm_count, g_tune, d.stream);
+                                d.status_dev, d.sm_count, tune_for(d), d.stream);
         if (!msg) {
           ++g_stats[3];
           ++g_stats[4];
@@ -1631,6 +1650,13 @@ int gonngpu_set_gemm_tuning(int block_n, int max_ctas) {
   if (block_n != 0 && block_n != 32 && block_n != 64 && block_n != 128 && block_n != 256) return -1;
   g_tune.block_n = block_n;
   g_tune.max_ctas = max_ctas < 0 ? 0 : max_ctas;
+  return 0;
+}
+
+int gonngpu_set_gemm_split_k(int splits) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (splits < 0 || splits > 64) return -1;
+  g_tune.split_k = splits;
   return 0;
 }
 

@@ -64,6 +64,12 @@ struct KernelParams {
   // row-coordinate step per batch of the A and B tensor maps; M is then per batch
   uint32_t batch_tiles;
   int32_t a_batch_c1, b_batch_c1;
+  // split-K (fp32 single-CTA kernel): a tile's k blocks are shared by `splits` work
+  // units of `kb_per_split` k blocks each; partial sums go through `sk_ws`, and the
+  // unit that arrives last on the tile's counter adds them up and writes C
+  uint32_t splits, kb_per_split;
+  float* sk_ws;
+  uint32_t* sk_count;
   GemmStatus* status;
 };
 
@@ -1073,8 +1079,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
   auto empty_bar = [&](uint32_t s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  const uint32_t sk_all_bar = bar_base + 8u * (2 * STAGES + 4);   // split-K: partials written
+  const uint32_t sk_lead_bar = bar_base + 8u * (2 * STAGES + 5);  // split-K: verdict published
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 6);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* sk_flag = tmem_slot + 2;
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -1088,6 +1097,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
       ptx::mbar_init(tfull_bar(a), 1);
       ptx::mbar_init(tempty_bar(a), 8);  // one arrival per drain warp
     }
+    ptx::mbar_init(sk_all_bar, 8);
+    ptx::mbar_init(sk_lead_bar, 1);
     *abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
@@ -1106,17 +1117,25 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t chunks_per_tile = (p.num_kblocks + CHUNK_KB - 1) / CHUNK_KB;
+  // work units: unit u is split (u % splits) of tile (u / splits); splits == 1 is one unit per tile
+  const uint32_t num_units = p.num_tiles * p.splits;
+  auto unit_range = [&](uint32_t u, uint32_t& t, uint32_t& kb_lo, uint32_t& kb_hi) {
+    t = u / p.splits;
+    kb_lo = (u - t * p.splits) * p.kb_per_split;
+    kb_hi = min(kb_lo + p.kb_per_split, p.num_kblocks);
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     uint32_t stage = 0, phase = 0;
     bool alive = true;
-    for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
+    for (uint32_t u = blockIdx.x; alive && u < num_units; u += gridDim.x) {
+      uint32_t t, kb_lo, kb_hi;
+      unit_range(u, t, kb_lo, kb_hi);
       uint32_t tm, tn;
       uint32_t bt;
       tile_coords(p, t, tm, tn, bt);
-      for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
+      for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         bool ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -1178,8 +1197,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
       uint32_t chunk = 0;  // running chunk count: selects accumulator and barrier parity
       uint32_t ready = 0;
       bool alive = true;
-      for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
-        for (uint32_t kb0 = 0; alive && kb0 < p.num_kblocks; kb0 += CHUNK_KB, ++chunk) {
+      for (uint32_t u = blockIdx.x; alive && u < num_units; u += gridDim.x) {
+        uint32_t t, kb_lo, kb_hi;
+        unit_range(u, t, kb_lo, kb_hi);
+        for (uint32_t kb0 = kb_lo; alive && kb0 < kb_hi; kb0 += CHUNK_KB, ++chunk) {
           const uint32_t acc = chunk & 1u;
           const uint32_t acc_phase = (chunk >> 1) & 1u;
           if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
@@ -1190,7 +1211,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
           }
           ptx::tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-          const uint32_t kb_end = min(kb0 + CHUNK_KB, p.num_kblocks);
+          const uint32_t kb_end = min(kb0 + CHUNK_KB, kb_hi);
           for (uint32_t kb = kb0; kb < kb_end; ++kb) {
             if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
               *abort_flag = 1;
@@ -1227,8 +1248,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
     const uint32_t quarter = warp & 3u;
     const uint32_t half = (warp - 2u) >> 2;  // which half of the tile's columns
     uint32_t chunk = 0;
+    uint32_t sk_parity = 0;
+    const uint32_t tid_d = threadIdx.x - 64u;  // 0..255 among the drain threads
     bool alive = true;
-    for (uint32_t t = blockIdx.x; alive && t < p.num_tiles; t += gridDim.x) {
+    for (uint32_t u = blockIdx.x; alive && u < num_units; u += gridDim.x) {
+      uint32_t t, kb_lo, kb_hi;
+      unit_range(u, t, kb_lo, kb_hi);
+      const uint32_t chunks_per_tile = (kb_hi - kb_lo + CHUNK_KB - 1) / CHUNK_KB;
       uint32_t tm, tn;
       uint32_t bt;
       tile_coords(p, t, tm, tn, bt);
@@ -1255,6 +1281,63 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
         if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
       }
       if (!alive) break;
+      if (p.splits > 1) {
+        // Partial sums to the workspace, [unit][4 columns][thread] so that a warp's
+        // 16-byte stores are contiguous; then the tile's counter says who came last.
+        float4* mine = reinterpret_cast<float4*>(p.sk_ws) + size_t(u) * (NC / 4) * 256u;
+#pragma unroll
+        for (int j = 0; j < NC / 4; ++j)
+          __stcg(mine + j * 256 + tid_d, make_float4(sums[4 * j], sums[4 * j + 1], sums[4 * j + 2], sums[4 * j + 3]));
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(sk_all_bar);
+        if (warp == 2) {
+          bool all_in = ptx::mbar_wait(sk_all_bar, sk_parity, abort_flag);
+          all_in = __all_sync(0xffffffffu, all_in);
+          if (lane == 0) {
+            uint32_t verdict = 2u;  // 2 = gave up
+            if (all_in) {
+              const uint32_t before = atomicAdd(p.sk_count + t, 1u);
+              verdict = (before + 1u == p.splits) ? 1u : 0u;
+              if (verdict) p.sk_count[t] = 0u;  // nobody else touches this tile again: ready for the next launch
+            } else {
+              *abort_flag = 1;
+              report(p.status, 3, 0x200u, t, 0);
+            }
+            *sk_flag = verdict;
+            ptx::mbar_arrive(sk_lead_bar);
+          }
+        }
+        bool ok = ptx::mbar_wait(sk_lead_bar, sk_parity, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        sk_parity ^= 1u;
+        const uint32_t verdict = *sk_flag;
+        if (!ok || verdict == 2u) {
+          if (lane == 0 && !ok) {
+            *abort_flag = 1;
+            report(p.status, 3, 0x201u, t, 0);
+          }
+          alive = false;
+          break;
+        }
+        if (verdict == 0u) continue;  // another unit of this tile finishes it
+        __threadfence();
+        // the last unit adds the partial sums in split order: the result does not
+        // depend on which unit came last
+#pragma unroll
+        for (int i = 0; i < NC; ++i) sums[i] = 0.f;
+        const float4* part = reinterpret_cast<const float4*>(p.sk_ws) + size_t(t) * p.splits * (NC / 4) * 256u;
+        for (uint32_t sp = 0; sp < p.splits; ++sp, part += (NC / 4) * 256u) {
+#pragma unroll
+          for (int j = 0; j < NC / 4; ++j) {
+            const float4 v = __ldcg(part + j * 256 + tid_d);
+            sums[4 * j] += v.x;
+            sums[4 * j + 1] += v.y;
+            sums[4 * j + 2] += v.z;
+            sums[4 * j + 3] += v.w;
+          }
+        }
+      }
       const uint32_t row = tm * BLOCK_M + quarter * 32u + lane;  // within its batch
       const uint64_t grow = uint64_t(bt) * p.M + row;            // in the stacked C
       const uint32_t col0 = tn * BLOCK_N + half * NC;
@@ -1689,28 +1772,46 @@ const char* launch_variant(const CUtensorMap* maps, const KernelParams& kp, uint
   return nullptr;
 }
 
-int choose_block_n(Kind kind, uint32_t M, uint32_t N, uint32_t K, int sms) {
-  // Cheapest estimated time: waves x per-tile cost, where a tile costs the
-  // larger of its tensor-pipe time and its shared-memory read time per k step,
-  // plus a fixed prologue/epilogue share.
+// Tile width and split count with the cheapest estimated time.  A work unit costs,
+// per k block, the largest of its tensor-pipe time, the MMAs' shared-memory read time
+// and the time to load its operand bytes (one SM takes about 48 bytes per cycle from
+// L2, measured), plus a fixed prologue/epilogue share; a split tile pays for the trip
+// of its partial sums through the workspace.  Splits are whole accumulation chunks.
+struct TileChoice {
+  int bn;
+  uint32_t splits, kb_per_split;
+};
+TileChoice choose_tiles(Kind kind, uint32_t M, uint32_t N, uint32_t K, int sms, uint32_t batch_count,
+                        int forced_bn, int max_splits) {
+  const bool f32 = (kind == Kind::TF32x3);
   const uint32_t tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
-  const double mma_per_step = (kind == Kind::TF32x3) ? 3.0 : 1.0;
-  const double rate = (kind == Kind::TF32x3) ? 0.5 : 1.0;  // tf32 runs at half the f16 rate
-  int best = 32;
+  const uint32_t block_k = f32 ? 32u : 64u;
+  const uint32_t kblocks = (K + block_k - 1) / block_k;
+  const double mmas = f32 ? 12.0 : 4.0;        // per k block
+  TileChoice best{32, 1u, kblocks};
   double best_cost = 1e300;
   const int cands[4] = {256, 128, 64, 32};
   for (int bn : cands) {
-    if (bn > 32 && uint32_t(bn) >= 2 * ((N + 31) / 32) * 32) continue;  // mostly padding
+    if (forced_bn && bn != forced_bn) continue;
+    if (!forced_bn && bn > 32 && uint32_t(bn) >= 2 * ((N + 31) / 32) * 32) continue;  // mostly padding
     const uint32_t tiles_n = (N + bn - 1) / bn;
-    const double tiles = double(tiles_m) * tiles_n;
-    const double waves = std::ceil(tiles / sms);
-    const double pipe = mma_per_step * (128.0 * bn * 32.0) / (8192.0 * rate);  // cycles / k step
-    const double smem = mma_per_step * (4096.0 + bn * 32.0) / 128.0;           // cycles / k step
-    const double ksteps = std::ceil(double(K) / (kind == Kind::TF32x3 ? 8.0 : 16.0));
-    const double cost = waves * (std::max(pipe, smem) * ksteps + 2000.0 + 8.0 * bn);
-    if (cost < best_cost) {
-      best_cost = cost;
-      best = bn;
+    const double tiles = double(tiles_m) * tiles_n * batch_count;
+    const double pipe = mmas * bn / 2.0;                          // 128 x bn x (8|16): bn/2 cycles
+    const double smem = mmas * (4096.0 + bn * 32.0) / 128.0;
+    const double load = 128.0 * (f32 ? 2.0 : 1.0) * (128.0 + bn) / 48.0;
+    const double per_kb = std::max(pipe, std::max(smem, load));
+    for (uint32_t want = 1; want <= uint32_t(std::max(1, max_splits)); ++want) {
+      uint32_t per = (kblocks + want - 1) / want;
+      if (want > 1) per = (per + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB;
+      const uint32_t splits = (kblocks + per - 1) / per;
+      if (splits != want) continue;  // rounding merged two candidates
+      const double waves = std::ceil(tiles * splits / sms);
+      double cost = waves * (per_kb * per + 2000.0 + 8.0 * bn);
+      if (splits > 1) cost += 1500.0 + (splits + 1.0) * 128.0 * bn * 4.0 / 64.0;
+      if (cost < best_cost) {
+        best_cost = cost;
+        best = TileChoice{bn, splits, per};
+      }
     }
   }
   return best;
@@ -1882,9 +1983,21 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
   if (f32 && (!A.plane1 || !B.plane1)) return "TF32x3 needs the low planes";
 
   // (for a batched product the tiles of all batches fill the machine together)
-  int bn = tune.block_n ? tune.block_n
-                        : choose_block_n(kind, batch ? M * batch->count : M, N, K, sm_count);
-  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return "unsupported BLOCK_N";
+  if (tune.block_n && tune.block_n != 32 && tune.block_n != 64 && tune.block_n != 128 && tune.block_n != 256)
+    return "unsupported BLOCK_N";
+  // split-K only where the fp32 kernel has a workspace to put partial sums in
+  int max_splits = 1;
+  if (f32 && tune.split_k != 1 && tune.splitk_ws && tune.splitk_counters)
+    max_splits = tune.split_k > 1 ? tune.split_k : 16;
+  TileChoice choice = choose_tiles(kind, M, N, K, sm_count, batch ? batch->count : 1u, tune.block_n, max_splits);
+  if (tune.split_k > 1 && max_splits > 1) {  // forced: as close to the asked count as whole chunks allow
+    const uint32_t kblocks = (K + block_k - 1) / block_k;
+    uint32_t per = (kblocks + uint32_t(tune.split_k) - 1) / uint32_t(tune.split_k);
+    per = (per + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB;
+    choice.kb_per_split = per;
+    choice.splits = (kblocks + per - 1) / per;
+  }
+  int bn = choice.bn;
   // An N-major fp16 tile narrower than one 128-byte swizzle row (64 columns)
   // would need the 64-byte swizzle; use the 64-wide tile instead.
   if (!f32 && B.mn_major && bn == 32) bn = 64;
@@ -1912,6 +2025,8 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
                  (!kp.c_in || reinterpret_cast<uintptr_t>(kp.c_in) % 16 == 0) &&
                  (!kp.bias || reinterpret_cast<uintptr_t>(kp.bias) % 16 == 0);
   kp.status = status;
+  kp.splits = 1;
+  kp.kb_per_split = kp.num_kblocks;
 
   // Large fp16 problems run on CTA pairs (256-row tiles); small ones, where the
   // pair tiles would not fill the machine, stay on single-CTA tiles.
@@ -1969,7 +2084,17 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
     maps[3] = maps[2];
   }
 
-  uint32_t grid = std::min<uint32_t>(kp.num_tiles, uint32_t(tune.max_ctas > 0 ? tune.max_ctas : sm_count));
+  if (f32 && choice.splits > 1) {
+    const size_t need = size_t(kp.num_tiles) * choice.splits * BLOCK_M * size_t(bn) * sizeof(float);
+    if (need <= tune.splitk_ws_bytes && kp.num_tiles <= tune.splitk_counter_slots) {
+      kp.splits = choice.splits;
+      kp.kb_per_split = choice.kb_per_split;
+      kp.sk_ws = tune.splitk_ws;
+      kp.sk_count = tune.splitk_counters;
+    }
+  }
+  uint32_t grid = std::min<uint32_t>(kp.num_tiles * kp.splits,
+                                     uint32_t(tune.max_ctas > 0 ? tune.max_ctas : sm_count));
   if (kind == Kind::F16) {
     switch (bn) {
       case 256: return launch_variant<0, 256>(maps, kp, grid, stream);

@@ -1,6 +1,7 @@
 // Internal C++ interface between the C-ABI bridge and the sm_100a kernels.
 // Nothing here is exported from the shared library.
 #pragma once
+#include <cstddef>
 #include <cstdint>
 #include <cuda_runtime.h>
 
@@ -51,6 +52,15 @@ struct GemmTuning {
   int block_n = 0;   // 0 = choose; else 32/64/128/256
   int max_ctas = 0;  // 0 = one per SM
   int pair = -1;     // fp16 CTA-pair kernel: -1 = choose by size, 0 = never, 1 = always
+  // Split-K of the fp32 single-CTA kernel, for products with too few tiles to fill the
+  // GPU: 0 = choose, 1 = never, n > 1 = n splits.  Needs the workspace below (device
+  // memory, owned by the caller, used by one launch at a time; the counters start at
+  // zero and every launch leaves them at zero).  Without it there is no split.
+  int split_k = 0;
+  float* splitk_ws = nullptr;
+  size_t splitk_ws_bytes = 0;
+  uint32_t* splitk_counters = nullptr;
+  uint32_t splitk_counter_slots = 0;
 };
 
 // Batched product C[b] = A[b].B[b] over stacked matrices (fp32 path, A[b,M,K] and

@@ -321,6 +321,10 @@ GONNGPU_API int gonngpu_set_gemm_tuning(int block_n, int max_ctas);
  * 0 never, 1 force 256-row tiles (block_n 0, 128 or 256), 2 force 512-row
  * tiles (block_n 0 or 256). */
 GONNGPU_API int gonngpu_set_gemm_pair_mode(int mode);
+/* Split-K of the fp32 GEMM (products with too few tiles to fill the GPU share a
+ * tile's K range among several SMs and add the partial sums in a fixed order):
+ * 0 (default) chosen by problem size, 1 never, n > 1 force n splits. */
+GONNGPU_API int gonngpu_set_gemm_split_k(int splits);
 
 /* Released buffers and operand planes are kept in a per-device cache (the
  * reference's callers create and release a result buffer per MatMul, and

@@ -710,3 +710,61 @@ def test_float64_facade_feeds_the_gemm(gpu):
     C = c.retrieve_f64((300, 150))
     ref = oracle.gemm_f64(A.astype(np.float32), B.astype(np.float32))
     assert C.dtype == np.float64 and oracle.rel_frobenius(C, ref) <= FP32_TOL
+
+
+# ------------------------------------------------------------------ split-K (fp32, few tiles)
+@pytest.mark.parametrize("shape", [(128, 128, 1024), (512, 1024, 784), (1024, 1024, 1024), (300, 200, 2000),
+                                   (64, 10, 4096), (257, 129, 520)])
+@pytest.mark.parametrize("splits", [2, 3, 4, 8])
+def test_split_k_matches_float64_reference_and_is_deterministic(gpu, shape, splits):
+    m, n, k = shape
+    rng = np.random.default_rng(m + 3 * n + 7 * k + splits)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    C0 = rng.standard_normal((m, n)).astype(np.float32)
+    ref = np.maximum(0.5 * oracle.gemm_f64(A, B) + 0.25 * C0 + bias, 0)
+    L = gpu.lib()
+    try:
+        assert L.gonngpu_set_gemm_pair_mode(0) == 0          # keep the product on the single-CTA kernel
+        assert L.gonngpu_set_gemm_split_k(splits) == 0
+        kw = dict(precision=gpu.FP32_3XTF32, alpha=0.5, beta=0.25, C0=C0, bias=bias, act=0)
+        first = run_matmul(gpu, A, B, **kw)
+        again = run_matmul(gpu, A, B, **kw)
+        assert oracle.rel_frobenius(first, ref) <= FP32_TOL
+        assert np.array_equal(first.view(np.uint32), again.view(np.uint32))
+        # transposed storage takes the same route
+        got = run_matmul(gpu, np.ascontiguousarray(A.T), np.ascontiguousarray(B.T), True, True, **kw)
+        assert oracle.rel_frobenius(got, ref) <= FP32_TOL
+        # the counters are back at zero: an unsplit product and another split one follow cleanly
+        assert L.gonngpu_set_gemm_split_k(1) == 0
+        plain = run_matmul(gpu, A, B, **kw)
+        assert oracle.rel_frobenius(plain, ref) <= FP32_TOL
+        assert L.gonngpu_set_gemm_split_k(0) == 0            # chosen by size
+        auto = run_matmul(gpu, A, B, **kw)
+        assert oracle.rel_frobenius(auto, ref) <= FP32_TOL
+    finally:
+        L.gonngpu_set_gemm_split_k(0)
+        L.gonngpu_set_gemm_pair_mode(-1)
+
+
+def test_split_k_with_more_units_than_sms_and_in_batches(gpu):
+    rng = np.random.default_rng(77)
+    L = gpu.lib()
+    try:
+        assert L.gonngpu_set_gemm_pair_mode(0) == 0
+        assert L.gonngpu_set_gemm_split_k(4) == 0
+        A = rng.standard_normal((1500, 600)).astype(np.float32)     # 12 x 5 tiles x 4 splits > 148 CTAs
+        B = rng.standard_normal((600, 600)).astype(np.float32)
+        assert oracle.rel_frobenius(run_matmul(gpu, A, B, precision=gpu.FP32_3XTF32), oracle.gemm_f64(A, B)) <= FP32_TOL
+        nb, bm, bk, bn = 5, 70, 400, 90
+        bA = rng.standard_normal((nb, bm, bk)).astype(np.float32)
+        bB = rng.standard_normal((nb, bk, bn)).astype(np.float32)
+        a, b, c = gpu.Buffer.from_host(bA), gpu.Buffer.from_host(bB), gpu.Buffer.empty(nb * bm * bn * 4)
+        gpu.batch_matmul(a, b, c, nb, bm, bn, bk)
+        got = c.retrieve((nb, bm, bn))
+        for i in range(nb):
+            assert oracle.rel_frobenius(got[i], oracle.gemm_f64(bA[i], bB[i])) <= FP32_TOL
+    finally:
+        L.gonngpu_set_gemm_split_k(0)
+        L.gonngpu_set_gemm_pair_mode(-1)
