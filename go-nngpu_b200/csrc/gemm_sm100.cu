@@ -728,6 +728,91 @@ __device__ __forceinline__ void epilogue_store32(const KernelParams& p, const ui
   }
 }
 
+// The same 32 x 32 block of results, written so that a warp's store instruction
+// covers whole rows: the 32 threads (one output row each) put their raw
+// accumulators into a 4 KB staging tile in shared memory (16-byte chunks XOR-ed
+// with the row, so neither side has bank conflicts), then each instruction takes
+// four rows x 128 bytes back out, applies alpha/beta/bias/activation and stores.
+// A row-per-thread store instruction touches 32 different lines and the
+// load/store unit handles them one by one; for the one-tile-per-CTA products of
+// the small shapes that serial tail was a fifth of the kernel.
+// `row_base` is the first of the warp's 32 rows within M, `grow_base` the same
+// row in the (possibly batch-stacked) C.  All 32 lanes must call.
+__device__ __forceinline__ void epilogue_store32_coalesced(const KernelParams& p,
+                                                           const uint32_t (&r)[32], uint32_t staging,
+                                                           uint32_t row_base, uint64_t grow_base,
+                                                           uint32_t col0, uint32_t lane) {
+  if (row_base >= p.M || col0 >= p.N) return;  // the same for the whole warp
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j) {
+    const uint32_t addr = staging + lane * 128u + ((j ^ (lane & 7u)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r[4 * j]), "r"(r[4 * j + 1]),
+                 "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
+  }
+  __syncwarp();
+  if (p.vec_store) {
+    const uint32_t q = lane & 7u, rsub = lane >> 3;
+    const uint32_t col = col0 + q * 4u;
+#pragma unroll
+    for (uint32_t it = 0; it < 8; ++it) {
+      const uint32_t rl = it * 4u + rsub;
+      float4 v;
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                   : "r"(staging + rl * 128u + ((q ^ (rl & 7u)) << 4)));
+      if (row_base + rl >= p.M || col >= p.N) continue;
+      float* c = p.C + (grow_base + rl) * p.ldc + col;
+      const float* cin = p.c_in ? p.c_in + (grow_base + rl) * p.ldc + col : nullptr;
+      v.x *= p.alpha; v.y *= p.alpha; v.z *= p.alpha; v.w *= p.alpha;
+      if (col + 4u <= p.N) {
+        if (cin) {
+          const float4 o = *reinterpret_cast<const float4*>(cin);
+          v.x += p.beta * o.x; v.y += p.beta * o.y; v.z += p.beta * o.z; v.w += p.beta * o.w;
+        }
+        if (p.bias) {
+          const float4 b = *reinterpret_cast<const float4*>(p.bias + col);
+          v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        }
+        if (p.act >= 0) {
+          v.x = apply_act(v.x, p.act, p.act_param);
+          v.y = apply_act(v.y, p.act, p.act_param);
+          v.z = apply_act(v.z, p.act, p.act_param);
+          v.w = apply_act(v.w, p.act, p.act_param);
+        }
+        *reinterpret_cast<float4*>(c) = v;
+      } else {
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k) {
+          if (col + k < p.N) {
+            float x = e[k];
+            if (cin) x += p.beta * cin[k];
+            if (p.bias) x += p.bias[col + k];
+            if (p.act >= 0) x = apply_act(x, p.act, p.act_param);
+            c[k] = x;
+          }
+        }
+      }
+    }
+  } else {
+    const uint32_t col = col0 + lane;
+#pragma unroll 4
+    for (uint32_t rl = 0; rl < 32; ++rl) {
+      float x;
+      asm volatile("ld.shared.f32 %0, [%1];"
+                   : "=f"(x)
+                   : "r"(staging + rl * 128u + (((lane >> 2) ^ (rl & 7u)) << 4) + (lane & 3u) * 4u));
+      if (row_base + rl >= p.M || col >= p.N) continue;
+      x *= p.alpha;
+      if (p.c_in) x += p.beta * p.c_in[(grow_base + rl) * p.ldc + col];
+      if (p.bias) x += p.bias[col];
+      if (p.act >= 0) x = apply_act(x, p.act, p.act_param);
+      p.C[(grow_base + rl) * p.ldc + col] = x;
+    }
+  }
+  __syncwarp();  // the staging tile may be overwritten by the next block
+}
+
 // Same values, but written to a 32-row x 128-byte staging tile in shared memory
 // (rows = this warp's 32 output rows) in the 128-byte-swizzle order a TMA store
 // expects, so that the store to C moves whole 128-byte lines.  No beta term.
@@ -1084,6 +1169,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 6);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* sk_flag = tmem_slot + 2;
+  // Epilogue staging, one 4 KB tile per drain warp: the first 32 KB of the pipeline
+  // stages, used only by a CTA's LAST work unit (by then the producer has issued its
+  // last load and every MMA that reads the stages has retired).
+  const uint32_t staging_base = smem_base;
+  static_assert(STAGES * STAGE_BYTES >= 8 * 4096, "staging tiles fit in the stages");
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -1338,13 +1428,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
           }
         }
       }
-      const uint32_t row = tm * BLOCK_M + quarter * 32u + lane;  // within its batch
-      const uint64_t grow = uint64_t(bt) * p.M + row;            // in the stacked C
+      const uint32_t row_base = tm * BLOCK_M + quarter * 32u;        // within its batch
+      const uint64_t grow_base = uint64_t(bt) * p.M + row_base;      // in the stacked C
       const uint32_t col0 = tn * BLOCK_N + half * NC;
-      if (row < p.M && col0 < p.N) {
-        float* c_row = p.C + grow * p.ldc;
-        const float* cin_row = p.c_in ? p.c_in + grow * p.ldc : nullptr;
-        if (col0 + NC <= p.N && p.vec_store) {
+      const uint32_t row = row_base + lane;
+      if (col0 + NC <= p.N && p.vec_store) {
+        // whole, aligned row segment: 16-byte stores from the row's own thread
+        if (row < p.M) {
+          float* c_row = p.C + (grow_base + lane) * p.ldc;
+          const float* cin_row = p.c_in ? p.c_in + (grow_base + lane) * p.ldc : nullptr;
 #pragma unroll
           for (int j = 0; j < NC; j += 4) {
             float4 v;
@@ -1374,17 +1466,32 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
             }
             *reinterpret_cast<float4*>(c_row + col0 + j) = v;
           }
-        } else {
+        }
+      } else if (NC >= 32 && u + gridDim.x >= num_units) {
+        // Ragged or unaligned columns on the CTA's last unit: a row-per-thread scalar
+        // store touches 32 lines per instruction, which the load/store unit handles one
+        // by one (measured: 43 against 35 us for N = 784 against N = 768); the staging
+        // tile turns them into whole-row stores.
+        const uint32_t staging = staging_base + (warp - 2u) * 4096u;
 #pragma unroll
-          for (int j = 0; j < NC; ++j) {
-            const uint32_t col = col0 + j;
-            if (col < p.N) {
-              float v = sums[j] * p.alpha;
-              if (cin_row) v += p.beta * cin_row[col];
-              if (p.bias) v += p.bias[col];
-              if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
-              c_row[col] = v;
-            }
+        for (int j = 0; j < (NC >= 32 ? NC / 32 : 0); ++j) {
+          uint32_t r[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(sums[(j * 32 + i) % NC]);
+          epilogue_store32_coalesced(p, r, staging, row_base, grow_base, col0 + j * 32, lane);
+        }
+      } else if (row < p.M && col0 < p.N) {
+        float* c_row = p.C + (grow_base + lane) * p.ldc;
+        const float* cin_row = p.c_in ? p.c_in + (grow_base + lane) * p.ldc : nullptr;
+#pragma unroll
+        for (int j = 0; j < NC; ++j) {
+          const uint32_t col = col0 + j;
+          if (col < p.N) {
+            float v = sums[j] * p.alpha;
+            if (cin_row) v += p.beta * cin_row[col];
+            if (p.bias) v += p.bias[col];
+            if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
+            c_row[col] = v;
           }
         }
       }
@@ -1729,11 +1836,17 @@ OperandPlan plan_operand(bool f32, bool mn_major, uint32_t tile_mn, uint32_t blo
   return o;
 }
 
+// Shared memory behind the pipeline stages: the barrier words.
+template <int KIND>
+constexpr uint32_t extra_smem_for() {
+  return 256u;
+}
+
 template <int KIND, int BLOCK_N>
 constexpr int stages_for() {
   constexpr uint32_t planes = (KIND == int(Kind::TF32x3)) ? 2 : 1;
   constexpr uint32_t stage = planes * (A_TILE_BYTES + BLOCK_N * SLAB_ROW_BYTES);
-  constexpr uint32_t avail = SMEM_LIMIT - 1024 /*align*/ - 256 /*barriers*/;
+  constexpr uint32_t avail = SMEM_LIMIT - 1024 /*align*/ - extra_smem_for<KIND>();
   constexpr int s = int(avail / stage);
   return s > 8 ? 8 : s;
 }
@@ -1743,7 +1856,8 @@ const char* launch_variant(const CUtensorMap* maps, const KernelParams& kp, uint
                            cudaStream_t stream) {
   constexpr int STAGES = stages_for<KIND, BLOCK_N>();
   constexpr uint32_t planes = (KIND == int(Kind::TF32x3)) ? 2 : 1;
-  constexpr uint32_t smem = STAGES * planes * (A_TILE_BYTES + BLOCK_N * SLAB_ROW_BYTES) + 1024 + 256;
+  constexpr uint32_t smem =
+      STAGES * planes * (A_TILE_BYTES + BLOCK_N * SLAB_ROW_BYTES) + 1024 + extra_smem_for<KIND>();
   static_assert(STAGES >= 2, "pipeline too shallow");
   static_assert(smem <= SMEM_LIMIT, "shared memory");
   void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
