@@ -45,6 +45,16 @@ struct OperandPlan {
   int32_t c1_tile, c1_k;           // box coordinate 1 = tile*c1_tile + kb*c1_k
   uint32_t kstep_bytes;  // descriptor start-address advance per MMA k step
   uint64_t desc;         // shared-memory descriptor without the start address
+  // MN-major operands whose plane pitch allows it are loaded as ONE 3-D box per tile and
+  // k block (128 bytes of MN, block_k rows of K, all slabs) instead of one 2-D box per
+  // slab: coordinates (0, coordinate 1, tile * c2_tile).  Fewer, larger boxes load faster.
+  uint32_t box3d;
+  int32_t c2_tile;
+  // K-major operands of the kernels whose stage holds several k blocks: ONE 3-D box
+  // (128 bytes of K, the tile's rows, `kgroup` consecutive k blocks) per stage, so that
+  // every row is fetched as kgroup x 128 contiguous bytes: coordinates
+  // (0, tile * c1_tile, first k block).  0 = one box per k block.
+  uint32_t kgroup;
 };
 
 struct KernelParams {
@@ -91,6 +101,23 @@ __device__ __forceinline__ void tile_coords(const KernelParams& p, uint32_t t, u
                                             uint32_t& tn, uint32_t& batch) {
   batch = p.batch_tiles ? t / p.batch_tiles : 0u;
   tile_coords(p, t - batch * p.batch_tiles, tm, tn);
+}
+
+// One operand tile's k block into shared memory at `dst` (completion bytes on `bar`).
+template <bool PAIR>
+__device__ __forceinline__ void load_operand(const OperandPlan& o, const CUtensorMap* m, uint32_t dst,
+                                             int32_t tile, int32_t kb, int32_t c1_extra, uint32_t bar) {
+  const int32_t c1 = tile * o.c1_tile + kb * o.c1_k + c1_extra;
+  if (o.box3d) {
+    if (PAIR) ptx::tma_load_3d_pair(dst, m, 0, c1, tile * o.c2_tile, bar);
+    else ptx::tma_load_3d(dst, m, 0, c1, tile * o.c2_tile, bar);
+    return;
+  }
+  for (uint32_t s = 0; s < o.slabs; ++s) {
+    const int32_t c0 = tile * o.c0_tile + int32_t(s) * o.c0_slab + kb * o.c0_k;
+    if (PAIR) ptx::tma_load_2d_pair(dst + s * o.slab_bytes, m, c0, c1, bar);
+    else ptx::tma_load_2d(dst + s * o.slab_bytes, m, c0, c1, bar);
+  }
 }
 
 __device__ __forceinline__ float apply_act(float v, int act, float param) {
@@ -204,24 +231,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
           uint32_t dst = smem_base + stage * STAGE_BYTES;
 #pragma unroll
           for (uint32_t pl = 0; pl < PLANES; ++pl) {
-            const CUtensorMap* ma = pl ? &tm_a1 : &tm_a0;
-            for (uint32_t s = 0; s < p.a.slabs; ++s) {
-              ptx::tma_load_2d(dst + s * p.a.slab_bytes, ma,
-                               int32_t(tm) * p.a.c0_tile + int32_t(s) * p.a.c0_slab +
-                                   int32_t(kb) * p.a.c0_k,
-                               int32_t(tm) * p.a.c1_tile + int32_t(kb) * p.a.c1_k, fb);
-            }
+            load_operand<false>(p.a, pl ? &tm_a1 : &tm_a0, dst, int32_t(tm), int32_t(kb), 0, fb);
             dst += A_TILE_BYTES;
           }
 #pragma unroll
           for (uint32_t pl = 0; pl < PLANES; ++pl) {
-            const CUtensorMap* mb = pl ? &tm_b1 : &tm_b0;
-            for (uint32_t s = 0; s < p.b.slabs; ++s) {
-              ptx::tma_load_2d(dst + s * p.b.slab_bytes, mb,
-                               int32_t(tn) * p.b.c0_tile + int32_t(s) * p.b.c0_slab +
-                                   int32_t(kb) * p.b.c0_k,
-                               int32_t(tn) * p.b.c1_tile + int32_t(kb) * p.b.c1_k, fb);
-            }
+            load_operand<false>(p.b, pl ? &tm_b1 : &tm_b0, dst, int32_t(tn), int32_t(kb), 0, fb);
             dst += B_TILE_BYTES;
           }
         }
@@ -417,8 +432,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ KernelParams p) {
   constexpr uint32_t B_TILE_BYTES = (BLOCK_N / 2) * SLAB_ROW_BYTES;  // this CTA's half
-  constexpr uint32_t SUB_BYTES = A_TILE_BYTES + B_TILE_BYTES;        // one k block
-  constexpr uint32_t STAGE_BYTES = SUB * SUB_BYTES;
+  constexpr uint32_t STAGE_BYTES = SUB * (A_TILE_BYTES + B_TILE_BYTES);  // SUB k blocks
   constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512 && TMEM_COLS >= 32, "TMEM");
 
@@ -495,22 +509,24 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (lane == 0) {
           if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
           const uint32_t fb = ptx::mapa_shared(full_bar(stage), 0);  // the leader's barrier
+          // stage layout: A of k blocks 0..SUB-1, then B of k blocks 0..SUB-1
+          // (k blocks past the end of K are fetched too: TMA fills them with zeros)
+          const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + SUB * A_TILE_BYTES;
+          const int32_t kb0 = int32_t(rd * SUB);
+          if (p.a.kgroup) {
+            ptx::tma_load_3d_pair(a_dst, &tm_a, 0, a_tile * p.a.c1_tile, kb0, fb);
+          } else {
 #pragma unroll
-          for (uint32_t j = 0; j < SUB; ++j) {
-            // k blocks past the end of K are fetched too: TMA fills them with zeros
-            const int32_t kb = int32_t(rd * SUB + j);
-            uint32_t dst = smem_base + stage * STAGE_BYTES + j * SUB_BYTES;
-            for (uint32_t sl = 0; sl < p.a.slabs; ++sl) {
-              ptx::tma_load_2d_pair(dst + sl * p.a.slab_bytes, &tm_a,
-                                    a_tile * p.a.c0_tile + int32_t(sl) * p.a.c0_slab + kb * p.a.c0_k,
-                                    a_tile * p.a.c1_tile + kb * p.a.c1_k, fb);
-            }
-            dst += A_TILE_BYTES;
-            for (uint32_t sl = 0; sl < p.b.slabs; ++sl) {
-              ptx::tma_load_2d_pair(dst + sl * p.b.slab_bytes, &tm_b,
-                                    b_tile * p.b.c0_tile + int32_t(sl) * p.b.c0_slab + kb * p.b.c0_k,
-                                    b_tile * p.b.c1_tile + kb * p.b.c1_k, fb);
-            }
+            for (uint32_t j = 0; j < SUB; ++j)
+              load_operand<true>(p.a, &tm_a, a_dst + j * A_TILE_BYTES, a_tile, kb0 + int32_t(j), 0, fb);
+          }
+          if (p.b.kgroup) {
+            ptx::tma_load_3d_pair(b_dst, &tm_b, 0, b_tile * p.b.c1_tile, kb0, fb);
+          } else {
+#pragma unroll
+            for (uint32_t j = 0; j < SUB; ++j)
+              load_operand<true>(p.b, &tm_b, b_dst + j * B_TILE_BYTES, b_tile, kb0 + int32_t(j), 0, fb);
           }
         }
         __syncwarp();
@@ -556,9 +572,9 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t ready_next = ptx::mbar_test_wait(full_bar(next_stage), next_phase);
 #pragma unroll
           for (uint32_t j = 0; j < SUB; ++j) {
-            const uint32_t a_addr = smem_base + stage * STAGE_BYTES + j * SUB_BYTES;
-            const uint32_t a_lo = a_lo0 + (a_addr >> 4);
-            const uint32_t b_lo = b_lo0 + ((a_addr + A_TILE_BYTES) >> 4);
+            const uint32_t st = smem_base + stage * STAGE_BYTES;
+            const uint32_t a_lo = a_lo0 + ((st + j * A_TILE_BYTES) >> 4);
+            const uint32_t b_lo = b_lo0 + ((st + SUB * A_TILE_BYTES + j * B_TILE_BYTES) >> 4);
 #pragma unroll
             for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
               ptx::mma_f16_pair_lohi(d_tmem, a_lo + ks * a_step, a_hi, b_lo + ks * b_step, b_hi,
@@ -937,20 +953,10 @@ gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll
           for (uint32_t u = 0; u < 2; ++u) {
             const int32_t a_tile = int32_t(tm * 4 + u * 2 + cta_rank);  // units of 128 rows
-            for (uint32_t sl = 0; sl < p.a.slabs; ++sl) {
-              ptx::tma_load_2d_pair(dst + sl * p.a.slab_bytes, &tm_a,
-                                    a_tile * p.a.c0_tile + int32_t(sl) * p.a.c0_slab +
-                                        int32_t(kb) * p.a.c0_k,
-                                    a_tile * p.a.c1_tile + int32_t(kb) * p.a.c1_k, fb);
-            }
+            load_operand<true>(p.a, &tm_a, dst, a_tile, int32_t(kb), 0, fb);
             dst += A_TILE_BYTES;
           }
-          for (uint32_t sl = 0; sl < p.b.slabs; ++sl) {
-            ptx::tma_load_2d_pair(dst + sl * p.b.slab_bytes, &tm_b,
-                                  b_tile * p.b.c0_tile + int32_t(sl) * p.b.c0_slab +
-                                      int32_t(kb) * p.b.c0_k,
-                                  b_tile * p.b.c1_tile + int32_t(kb) * p.b.c1_k, fb);
-          }
+          load_operand<true>(p.b, &tm_b, dst, b_tile, int32_t(kb), 0, fb);
         }
         __syncwarp();
         if (++stage == STAGES) {
@@ -1242,28 +1248,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
           uint32_t dst = smem_base + stage * STAGE_BYTES;
 #pragma unroll
           for (uint32_t pl = 0; pl < 2; ++pl) {
-            const CUtensorMap* ma = pl ? &tm_a1 : &tm_a0;
-            for (uint32_t s = 0; s < p.a.slabs; ++s) {
-              ptx::tma_load_2d(dst + s * p.a.slab_bytes, ma,
-                               int32_t(tm) * p.a.c0_tile + int32_t(s) * p.a.c0_slab +
-                                   int32_t(kb) * p.a.c0_k,
-                               int32_t(tm) * p.a.c1_tile + int32_t(kb) * p.a.c1_k +
-                                   int32_t(bt) * p.a_batch_c1,
-                               fb);
-            }
+            load_operand<false>(p.a, pl ? &tm_a1 : &tm_a0, dst, int32_t(tm), int32_t(kb),
+                                int32_t(bt) * p.a_batch_c1, fb);
             dst += A_TILE_BYTES;
           }
 #pragma unroll
           for (uint32_t pl = 0; pl < 2; ++pl) {
-            const CUtensorMap* mb = pl ? &tm_b1 : &tm_b0;
-            for (uint32_t s = 0; s < p.b.slabs; ++s) {
-              ptx::tma_load_2d(dst + s * p.b.slab_bytes, mb,
-                               int32_t(tn) * p.b.c0_tile + int32_t(s) * p.b.c0_slab +
-                                   int32_t(kb) * p.b.c0_k,
-                               int32_t(tn) * p.b.c1_tile + int32_t(kb) * p.b.c1_k +
-                                   int32_t(bt) * p.b_batch_c1,
-                               fb);
-            }
+            load_operand<false>(p.b, pl ? &tm_b1 : &tm_b0, dst, int32_t(tn), int32_t(kb),
+                                int32_t(bt) * p.b_batch_c1, fb);
             dst += B_TILE_BYTES;
           }
         }
@@ -1612,24 +1604,12 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
           uint32_t dst = smem_base + stage * STAGE_BYTES;
 #pragma unroll
           for (uint32_t pl = 0; pl < 2; ++pl) {
-            const CUtensorMap* ma = pl ? &tm_a1 : &tm_a0;
-            for (uint32_t sl = 0; sl < p.a.slabs; ++sl) {
-              ptx::tma_load_2d_pair(dst + sl * p.a.slab_bytes, ma,
-                                    a_tile * p.a.c0_tile + int32_t(sl) * p.a.c0_slab +
-                                        int32_t(kb) * p.a.c0_k,
-                                    a_tile * p.a.c1_tile + int32_t(kb) * p.a.c1_k, fb);
-            }
+            load_operand<true>(p.a, pl ? &tm_a1 : &tm_a0, dst, a_tile, int32_t(kb), 0, fb);
             dst += A_TILE_BYTES;
           }
 #pragma unroll
           for (uint32_t pl = 0; pl < 2; ++pl) {
-            const CUtensorMap* mb = pl ? &tm_b1 : &tm_b0;
-            for (uint32_t sl = 0; sl < p.b.slabs; ++sl) {
-              ptx::tma_load_2d_pair(dst + sl * p.b.slab_bytes, mb,
-                                    b_tile * p.b.c0_tile + int32_t(sl) * p.b.c0_slab +
-                                        int32_t(kb) * p.b.c0_k,
-                                    b_tile * p.b.c1_tile + int32_t(kb) * p.b.c1_k, fb);
-            }
+            load_operand<true>(p.b, pl ? &tm_b1 : &tm_b0, dst, b_tile, int32_t(kb), 0, fb);
             dst += B_TILE_BYTES;
           }
         }
@@ -1836,6 +1816,82 @@ OperandPlan plan_operand(bool f32, bool mn_major, uint32_t tile_mn, uint32_t blo
   return o;
 }
 
+// 3-D map over an MN-major plane (rows = K, `inner` contiguous MN elements): dimension 0 is
+// one 128-byte slab row, dimension 1 the K rows, dimension 2 the slab index, so that one box
+// (128 bytes, block_k rows, all slabs of a tile) lands slab after slab in shared memory,
+// exactly where the per-slab 2-D boxes would put it.  The last slab of a ragged MN extent
+// reads the plane's row padding: those values only reach output rows / columns that are
+// never stored.
+bool make_map_3d(CUtensorMap* map, bool f32, const void* base, uint64_t inner, uint64_t outer,
+                 uint64_t pitch_elems, uint32_t block_k, uint32_t tile_slabs) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return false;
+  const uint32_t esz = f32 ? 4 : 2;
+  const uint32_t row_elems = SLAB_ROW_BYTES / esz;
+  cuuint64_t dims[3] = {row_elems, outer, (inner + row_elems - 1) / row_elems};
+  cuuint64_t strides[2] = {pitch_elems * esz, SLAB_ROW_BYTES};
+  cuuint32_t box[3] = {row_elems, block_k, tile_slabs};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  f32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// 3-D map over a K-major plane (rows = MN, `inner` contiguous K elements, a multiple of the
+// 128-byte slab row): dimension 0 is 128 bytes of K, dimension 1 the rows, dimension 2 the k
+// block index; one box of (128 bytes, tile rows, kgroup) lands as kgroup consecutive K-major
+// tiles.  k blocks past the end of K are zero-filled.
+bool make_map_kgroup(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
+                     uint64_t pitch_elems, uint32_t tile_rows, uint32_t kgroup) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return false;
+  const uint32_t row_elems = SLAB_ROW_BYTES / 2;
+  cuuint64_t dims[3] = {row_elems, outer, inner / row_elems};
+  cuuint64_t strides[2] = {pitch_elems * 2, SLAB_ROW_BYTES};
+  cuuint32_t box[3] = {row_elems, tile_rows, kgroup};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool box3d_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("GONNGPU_BOX3D");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+// The tensor map(s) of one operand (plane1 only for the fp32 path) and, where the operand is
+// MN-major with a pitch of whole slab rows, the switch of its plan to single 3-D boxes.
+bool make_operand_maps(bool f32, const GemmOperand& op, uint64_t inner, uint64_t outer,
+                       uint32_t box_rows, OperandPlan& plan, CUtensorMap* m0, CUtensorMap* m1,
+                       uint32_t kgroup = 0) {
+  const uint32_t row_elems = SLAB_ROW_BYTES / (f32 ? 4 : 2);
+  plan.kgroup = 0;
+  if (!f32 && !op.mn_major && kgroup > 1 && inner % row_elems == 0 && box3d_enabled() &&
+      make_map_kgroup(m0, op.plane0, inner, outer, op.pitch, box_rows, kgroup)) {
+    plan.kgroup = kgroup;
+    plan.box3d = 0;
+    return true;
+  }
+  if (op.mn_major && plan.slabs > 1 && op.pitch % row_elems == 0 && box3d_enabled()) {
+    if (make_map_3d(m0, f32, op.plane0, inner, outer, op.pitch, box_rows, plan.slabs) &&
+        (!m1 || make_map_3d(m1, f32, op.plane1, inner, outer, op.pitch, box_rows, plan.slabs))) {
+      plan.box3d = 1;
+      plan.c2_tile = int32_t(plan.slabs);
+      return true;
+    }
+  }
+  plan.box3d = 0;
+  return make_map(m0, f32, op.plane0, inner, outer, op.pitch, box_rows, op.mn_major) &&
+         (!m1 || make_map(m1, f32, op.plane1, inner, outer, op.pitch, box_rows, op.mn_major));
+}
+
 // Shared memory behind the pipeline stages: the barrier words.
 template <int KIND>
 constexpr uint32_t extra_smem_for() {
@@ -1995,10 +2051,13 @@ const char* launch_gemm_pair(uint32_t M, uint32_t N, uint32_t K, int bn, bool ta
   std::memset(&mb, 0, sizeof(mb));
   const uint32_t a_box_rows = A.mn_major ? block_k : BLOCK_M;
   const uint32_t b_box_rows = B.mn_major ? block_k : uint32_t(bn / 2);
-  if (!make_map(&ma, false, A.plane0, A.mn_major ? M : K, A.mn_major ? K : M, A.pitch, a_box_rows,
-                A.mn_major) ||
-      !make_map(&mb, false, B.plane0, B.mn_major ? N : K, B.mn_major ? K : N, B.pitch, b_box_rows,
-                B.mn_major))
+  static const int sub = [] {
+    const char* e = std::getenv("GONNGPU_PAIR_SUB");  // experiment switch: k blocks per stage
+    return e ? std::atoi(e) : 2;
+  }();
+  const uint32_t kgroup = (!tall && sub != 1) ? 2u : 0u;
+  if (!make_operand_maps(false, A, A.mn_major ? M : K, A.mn_major ? K : M, a_box_rows, kp.a, &ma, nullptr, kgroup) ||
+      !make_operand_maps(false, B, B.mn_major ? N : K, B.mn_major ? K : N, b_box_rows, kp.b, &mb, nullptr, kgroup))
     return "cuTensorMapEncodeTiled failed";
   const uint32_t limit = uint32_t(max_ctas > 0 ? max_ctas : sm_count) / 2;
   const uint32_t pairs = std::max<uint32_t>(1u, std::min<uint32_t>(kp.num_tiles, limit));
@@ -2024,10 +2083,6 @@ const char* launch_gemm_pair(uint32_t M, uint32_t N, uint32_t K, int bn, bool ta
     }
     return launch_pair512(ma, mb, mc, kp, pairs, stream);
   }
-  static const int sub = [] {
-    const char* e = std::getenv("GONNGPU_PAIR_SUB");  // experiment switch: k blocks per stage
-    return e ? std::atoi(e) : 2;
-  }();
   if (bn == 256)
     return sub == 1 ? launch_pair_variant<256, 1>(ma, mb, kp, pairs, stream)
                     : launch_pair_variant<256, 2>(ma, mb, kp, pairs, stream);
@@ -2057,10 +2112,8 @@ const char* launch_tf32_pair(uint32_t M, uint32_t N, uint32_t K, const GemmOpera
   const uint32_t a_box = A.mn_major ? block_k : BLOCK_M, b_box = B.mn_major ? block_k : 128;
   const uint64_t a_in = A.mn_major ? M : K, a_out = A.mn_major ? K : M;
   const uint64_t b_in = B.mn_major ? N : K, b_out = B.mn_major ? K : N;
-  if (!make_map(&maps[0], true, A.plane0, a_in, a_out, A.pitch, a_box, A.mn_major) ||
-      !make_map(&maps[1], true, A.plane1, a_in, a_out, A.pitch, a_box, A.mn_major) ||
-      !make_map(&maps[2], true, B.plane0, b_in, b_out, B.pitch, b_box, B.mn_major) ||
-      !make_map(&maps[3], true, B.plane1, b_in, b_out, B.pitch, b_box, B.mn_major))
+  if (!make_operand_maps(true, A, a_in, a_out, a_box, kp.a, &maps[0], &maps[1]) ||
+      !make_operand_maps(true, B, b_in, b_out, b_box, kp.b, &maps[2], &maps[3]))
     return "cuTensorMapEncodeTiled failed";
   auto kern = gemm_tf32x3_pair_kernel<STAGES>;
   static bool attr_done_dev[64] = {};
@@ -2186,14 +2239,10 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
     kp.a_batch_c1 = int32_t(M);
     kp.b_batch_c1 = int32_t(batch->b_rows);
   }
-  if (!make_map(&maps[0], f32, A.plane0, a_inner, a_outer, A.pitch, a_box_rows, A.mn_major) ||
-      !make_map(&maps[2], f32, B.plane0, b_inner, b_outer, B.pitch, b_box_rows, B.mn_major))
+  if (!make_operand_maps(f32, A, a_inner, a_outer, a_box_rows, kp.a, &maps[0], f32 ? &maps[1] : nullptr) ||
+      !make_operand_maps(f32, B, b_inner, b_outer, b_box_rows, kp.b, &maps[2], f32 ? &maps[3] : nullptr))
     return "cuTensorMapEncodeTiled failed";
-  if (f32) {
-    if (!make_map(&maps[1], f32, A.plane1, a_inner, a_outer, A.pitch, a_box_rows, A.mn_major) ||
-        !make_map(&maps[3], f32, B.plane1, b_inner, b_outer, B.pitch, b_box_rows, B.mn_major))
-      return "cuTensorMapEncodeTiled failed";
-  } else {
+  if (!f32) {
     maps[1] = maps[0];
     maps[3] = maps[2];
   }

@@ -109,6 +109,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(bar)
       : "memory");
 }
+// 3-D tiled load (used for MN-major operands: all 128-byte-wide slabs of a tile in one box).
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* m, int32_t c0,
+                                            int32_t c1, int32_t c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
 // 2-D tiled store shared -> global (bulk-group completion).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, int32_t c0, int32_t c1,
                                              uint32_t smem_src) {
@@ -268,6 +277,15 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(bar_cluster)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* m,
+                                                 int32_t c0, int32_t c1, int32_t c2,
+                                                 uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2), "r"(bar_cluster)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
