@@ -2201,10 +2201,11 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
     const uint64_t half_sms = uint64_t(sm_count) / 2;
     // 512-row tiles need a quarter fewer operand bytes per flop than 256-row
     // tiles but cannot overlap their epilogue with the next tile (TMEM is full),
-    // so they pay off only for deep K (measured: ahead at K=8192, behind at 4096).
+    // so they pay off only for very deep K (measured with 3-D operand boxes: 4 % ahead at
+    // K=16384, level at 8192^3, 4-10 % behind at K <= 8192 with N = 4096).
     const uint64_t tall_tiles = uint64_t((M + 511) / 512) * ((N + 255) / 256);
     const bool tall_ok = (tune.block_n == 0 || tune.block_n == 256);
-    if (tall_ok && (tune.pair == 2 || (tune.pair < 0 && M >= 512 && N >= 128 && K >= 6144 && tall_tiles >= half_sms))) {
+    if (tall_ok && (tune.pair == 2 || (tune.pair < 0 && M >= 512 && N >= 128 && K >= 12288 && tall_tiles >= half_sms))) {
       return launch_gemm_pair(M, N, K, 256, true, A, B, kp, sm_count, tune.max_ctas, stream);
     }
     const int pbn = (tune.block_n == 128) ? 128 : 256;
