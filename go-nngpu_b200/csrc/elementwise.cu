@@ -6,6 +6,8 @@
 // here they are HBM-bound streaming kernels (16-byte accesses, grid-stride), so
 // that a chain of eager layers stays on the device between its GEMMs.
 #include "kernels.h"
+#include "launch.cuh"
+#include "ptx.cuh"
 
 namespace gonn {
 
@@ -80,6 +82,8 @@ template <int OP>
 __global__ void __launch_bounds__(256) ew_kernel(const float* __restrict__ a,
                                                  const float* __restrict__ b, float* __restrict__ c,
                                                  uint64_t n, float s, int vec) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
   uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
   if (vec) {
@@ -106,6 +110,8 @@ __global__ void __launch_bounds__(256) ew_kernel(const float* __restrict__ a,
 // Smallest index whose value is exactly zero (either sign), or n.
 __global__ void __launch_bounds__(256) first_zero_kernel(const float* __restrict__ b, uint64_t n,
                                                          unsigned long long* __restrict__ out) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   unsigned long long best = ~0ull;
   for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < n;
        i += uint64_t(gridDim.x) * blockDim.x) {
@@ -146,6 +152,8 @@ __device__ __forceinline__ float group_reduce(float v, float* smem) {
 template <int GROUP, bool VEC>
 __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* in, float* out, uint64_t rows,
                                                           uint64_t features) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   __shared__ float smem[8];
   constexpr int per_block = 256 / GROUP;
   const int sub = threadIdx.x / GROUP, lane = threadIdx.x % GROUP;
@@ -187,6 +195,8 @@ template <int GROUP, bool VEC>
 __global__ void __launch_bounds__(256) softmax_bwd_kernel(const float* grad_out, const float* act,
                                                           float* grad_in, uint64_t rows,
                                                           uint64_t features) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   __shared__ float smem[8];
   constexpr int per_block = 256 / GROUP;
   const int sub = threadIdx.x / GROUP, lane = threadIdx.x % GROUP;
@@ -229,7 +239,7 @@ void launch_elementwise(int op, const float* a, const float* b, float* c, uint64
   if (grid > 148 * 16) grid = 148 * 16;
   if (grid < 1) grid = 1;
 #define GONN_EW(OPC) \
-  case OPC: ew_kernel<OPC><<<uint32_t(grid), 256, 0, stream>>>(a, b, c, n, scalar, vec); break;
+  case OPC: launch_kernel(ew_kernel<OPC>, dim3(uint32_t(grid)), dim3(256), 0, stream, a, b, c, n, scalar, vec); break;
   switch (op) {
     GONN_EW(EW_ADD) GONN_EW(EW_SUB) GONN_EW(EW_MUL) GONN_EW(EW_DIV) GONN_EW(EW_SCALAR_ADD)
     GONN_EW(EW_SCALAR_MUL) GONN_EW(EW_SIGMOID) GONN_EW(EW_SIGMOID_BWD) GONN_EW(EW_TANH)
@@ -246,6 +256,8 @@ void launch_elementwise(int op, const float* a, const float* b, float* c, uint64
 template <int GROUP, int PER, bool VEC, int R, bool BWD>
 __global__ void __launch_bounds__(256) softmax_reg_kernel(const float* in_or_grad, const float* act,
                                                           float* out, uint64_t rows, uint64_t features) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   __shared__ float smem[8];
   constexpr int per_block = 256 / GROUP;
   constexpr int W = VEC ? 4 : 1;
@@ -345,9 +357,9 @@ void softmax_reg_dispatch(const float* in_or_grad, const float* act, float* out,
   uint64_t grid = (rows + per_iter - 1) / per_iter;
   if (grid > 148 * 8) grid = 148 * 8;
   if (backward)
-    softmax_reg_kernel<GROUP, PER, VEC, R, true><<<uint32_t(grid), 256, 0, stream>>>(in_or_grad, act, out, rows, features);
+    launch_kernel(softmax_reg_kernel<GROUP, PER, VEC, R, true>, dim3(uint32_t(grid)), dim3(256), 0, stream, in_or_grad, act, out, rows, features);
   else
-    softmax_reg_kernel<GROUP, PER, VEC, R, false><<<uint32_t(grid), 256, 0, stream>>>(in_or_grad, act, out, rows, features);
+    launch_kernel(softmax_reg_kernel<GROUP, PER, VEC, R, false>, dim3(uint32_t(grid)), dim3(256), 0, stream, in_or_grad, act, out, rows, features);
 }
 
 template <int GROUP, bool VEC>
@@ -357,9 +369,9 @@ void softmax_dispatch(const float* in_or_grad, const float* act, float* out, uin
   uint64_t grid = (rows + per_block - 1) / per_block;
   if (grid > 148 * 8) grid = 148 * 8;
   if (backward)
-    softmax_bwd_kernel<GROUP, VEC><<<uint32_t(grid), 256, 0, stream>>>(in_or_grad, act, out, rows, features);
+    launch_kernel(softmax_bwd_kernel<GROUP, VEC>, dim3(uint32_t(grid)), dim3(256), 0, stream, in_or_grad, act, out, rows, features);
   else
-    softmax_fwd_kernel<GROUP, VEC><<<uint32_t(grid), 256, 0, stream>>>(in_or_grad, out, rows, features);
+    launch_kernel(softmax_fwd_kernel<GROUP, VEC>, dim3(uint32_t(grid)), dim3(256), 0, stream, in_or_grad, out, rows, features);
 }
 
 void launch_softmax(const float* in_or_grad, const float* act, float* out, uint64_t rows,
@@ -393,7 +405,7 @@ void launch_first_zero(const float* b, uint64_t n, unsigned long long* out, cuda
   if (n == 0) return;
   uint64_t grid = (n + 255) / 256;
   if (grid > 148 * 8) grid = 148 * 8;
-  first_zero_kernel<<<uint32_t(grid), 256, 0, stream>>>(b, n, out);
+  launch_kernel(first_zero_kernel, dim3(uint32_t(grid)), dim3(256), 0, stream, b, n, out);
 }
 
 }  // namespace gonn

@@ -24,6 +24,7 @@
 #include <mutex>
 
 #include "kernels.h"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace gonn {
@@ -206,6 +207,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched no global memory: from here on the previous kernel's results
+  // are needed (and its reads of our output buffers must be over)
+  ptx::grid_dependency_release();
+  ptx::grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -485,6 +490,10 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   ptx::cluster_sync_all();  // the peer's barriers and TMEM exist before anyone signals them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched no global memory: from here on the previous kernel's results
+  // are needed (and its reads of our output buffers must be over)
+  ptx::grid_dependency_release();
+  ptx::grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -926,6 +935,10 @@ gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
   ptx::cluster_sync_all();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched no global memory: from here on the previous kernel's results
+  // are needed (and its reads of our output buffers must be over)
+  ptx::grid_dependency_release();
+  ptx::grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -1171,7 +1184,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
   auto tfull_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t sk_all_bar = bar_base + 8u * (2 * STAGES + 4);   // split-K: partials written
-  const uint32_t sk_lead_bar = bar_base + 8u * (2 * STAGES + 5);  // split-K: verdict published
+  const uint32_t sk_lead_bar = bar_base + 8u * (2 * STAGES + 5);  // split-K: outcome published
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 6);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* sk_flag = tmem_slot + 2;
@@ -1213,6 +1226,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched no global memory: from here on the previous kernel's results
+  // are needed (and its reads of our output buffers must be over)
+  ptx::grid_dependency_release();
+  ptx::grid_dependency_wait();
   // work units: unit u is split (u % splits) of tile (u / splits); splits == 1 is one unit per tile
   const uint32_t num_units = p.num_tiles * p.splits;
   auto unit_range = [&](uint32_t u, uint32_t& t, uint32_t& kb_lo, uint32_t& kb_hi) {
@@ -1377,24 +1394,24 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
           bool all_in = ptx::mbar_wait(sk_all_bar, sk_parity, abort_flag);
           all_in = __all_sync(0xffffffffu, all_in);
           if (lane == 0) {
-            uint32_t verdict = 2u;  // 2 = gave up
+            uint32_t outcome = 2u;  // 2 = gave up
             if (all_in) {
               const uint32_t before = atomicAdd(p.sk_count + t, 1u);
-              verdict = (before + 1u == p.splits) ? 1u : 0u;
-              if (verdict) p.sk_count[t] = 0u;  // nobody else touches this tile again: ready for the next launch
+              outcome = (before + 1u == p.splits) ? 1u : 0u;
+              if (outcome) p.sk_count[t] = 0u;  // nobody else touches this tile again: ready for the next launch
             } else {
               *abort_flag = 1;
               report(p.status, 3, 0x200u, t, 0);
             }
-            *sk_flag = verdict;
+            *sk_flag = outcome;
             ptx::mbar_arrive(sk_lead_bar);
           }
         }
         bool ok = ptx::mbar_wait(sk_lead_bar, sk_parity, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         sk_parity ^= 1u;
-        const uint32_t verdict = *sk_flag;
-        if (!ok || verdict == 2u) {
+        const uint32_t outcome = *sk_flag;
+        if (!ok || outcome == 2u) {
           if (lane == 0 && !ok) {
             *abort_flag = 1;
             report(p.status, 3, 0x201u, t, 0);
@@ -1402,7 +1419,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
           alive = false;
           break;
         }
-        if (verdict == 0u) continue;  // another unit of this tile finishes it
+        if (outcome == 0u) continue;  // another unit of this tile finishes it
         __threadfence();
         // the last unit adds the partial sums in split order: the result does not
         // depend on which unit came last
@@ -1577,6 +1594,10 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
   ptx::cluster_sync_all();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched no global memory: from here on the previous kernel's results
+  // are needed (and its reads of our output buffers must be over)
+  ptx::grid_dependency_release();
+  ptx::grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -1937,8 +1958,11 @@ const char* launch_variant(const CUtensorMap* maps, const KernelParams& kp, uint
     }
     attr_done = true;
   }
-  kern<<<grid, threads, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], kp);
-  if (cudaGetLastError() != cudaSuccess) return "GEMM kernel launch failed";
+  if (launch_kernel(kern, dim3(grid), dim3(threads), smem, stream, maps[0], maps[1], maps[2], maps[3], kp) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return "GEMM kernel launch failed";
+  }
   return nullptr;
 }
 
@@ -2005,8 +2029,11 @@ const char* launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, co
       return "cudaFuncSetAttribute(max dynamic shared memory) failed";
     attr_done_dev[dev & 63] = true;
   }
-  kern<<<2 * pairs, NUM_THREADS, smem, stream>>>(ma, mb, kp);  // cluster size 2 is compiled in
-  if (cudaGetLastError() != cudaSuccess) return "GEMM pair kernel launch failed";
+  // (cluster size 2 is compiled in)
+  if (launch_kernel(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ma, mb, kp) != cudaSuccess) {
+    cudaGetLastError();
+    return "GEMM pair kernel launch failed";
+  }
   return nullptr;
 }
 
@@ -2027,8 +2054,10 @@ const char* launch_pair512(const CUtensorMap& ma, const CUtensorMap& mb, const C
       return "cudaFuncSetAttribute(max dynamic shared memory) failed";
     attr_done_dev[dev & 63] = true;
   }
-  kern<<<2 * pairs, NUM_THREADS, smem, stream>>>(ma, mb, mc, kp);
-  if (cudaGetLastError() != cudaSuccess) return "GEMM pair512 kernel launch failed";
+  if (launch_kernel(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ma, mb, mc, kp) != cudaSuccess) {
+    cudaGetLastError();
+    return "GEMM pair512 kernel launch failed";
+  }
   return nullptr;
 }
 
@@ -2127,8 +2156,11 @@ const char* launch_tf32_pair(uint32_t M, uint32_t N, uint32_t K, const GemmOpera
   }
   const uint32_t limit = uint32_t(max_ctas > 0 ? max_ctas : sm_count) / 2;
   const uint32_t pairs = std::max<uint32_t>(1u, std::min<uint32_t>(kp.num_tiles, limit));
-  kern<<<2 * pairs, TF32_THREADS, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], kp);
-  if (cudaGetLastError() != cudaSuccess) return "GEMM tf32 pair kernel launch failed";
+  if (launch_kernel(kern, dim3(2 * pairs), dim3(TF32_THREADS), smem, stream, maps[0], maps[1], maps[2],
+                    maps[3], kp) != cudaSuccess) {
+    cudaGetLastError();
+    return "GEMM tf32 pair kernel launch failed";
+  }
   return nullptr;
 }
 

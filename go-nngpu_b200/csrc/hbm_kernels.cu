@@ -5,6 +5,8 @@
 #include <cuda_fp16.h>
 
 #include "kernels.h"
+#include "launch.cuh"
+#include "ptx.cuh"
 
 namespace gonn {
 
@@ -20,6 +22,8 @@ template <bool VEC_IN, bool VEC_OUT>
 __global__ void __launch_bounds__(256) transpose_kernel(const float* __restrict__ in,
                                                         float* __restrict__ out, uint32_t rows,
                                                         uint32_t cols, uint32_t tiles_c) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   __shared__ float tile[TT][TT + 1];  // tile[c][r]
   const uint32_t tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
   const uint32_t r0 = tr * TT, c0 = tc * TT;
@@ -105,6 +109,8 @@ __device__ __forceinline__ uint16_t f32_to_f16(float f, int mode) {
 __global__ void __launch_bounds__(256) cvt_f16_kernel(const float* __restrict__ src, uint64_t rows,
                                                       uint64_t cols, uint16_t* __restrict__ dst,
                                                       uint64_t pitch, int mode, int vec) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   if (vec) {  // cols % 4 == 0 and both bases 16-byte aligned; pitch % 8 == 0 always
     const uint64_t q = cols >> 2, total = rows * q;
     for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
@@ -142,6 +148,8 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
                                                          float* __restrict__ hi,
                                                          float* __restrict__ lo, uint64_t pitch,
                                                          int vec) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   if (vec) {
     const uint64_t q = cols >> 2, total = rows * q;
     for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
@@ -184,6 +192,8 @@ __global__ void __launch_bounds__(256) add_broadcast_kernel(const float* __restr
                                                             const float* __restrict__ b,
                                                             float* __restrict__ c, uint64_t rows,
                                                             uint64_t cols, int mode) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   const uint64_t total = rows * cols;
   for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
        i += uint64_t(gridDim.x) * blockDim.x) {
@@ -202,6 +212,8 @@ __global__ void __launch_bounds__(256) add_broadcast_kernel(const float* __restr
 // ReLU forward / backward: internal/cgo/metal_bridge_activation.m:44-47, 74-77.
 __global__ void __launch_bounds__(256) relu_fwd_kernel(const float* __restrict__ in,
                                                        float* __restrict__ out, uint64_t n) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < n;
        i += uint64_t(gridDim.x) * blockDim.x)
     out[i] = fmaxf(0.0f, in[i]);
@@ -209,6 +221,8 @@ __global__ void __launch_bounds__(256) relu_fwd_kernel(const float* __restrict__
 __global__ void __launch_bounds__(256) relu_bwd_kernel(const float* __restrict__ go,
                                                        const float* __restrict__ act,
                                                        float* __restrict__ gi, uint64_t n) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < n;
        i += uint64_t(gridDim.x) * blockDim.x)
     gi[i] = (act[i] > 0.0f) ? go[i] : 0.0f;
@@ -219,6 +233,8 @@ __global__ void __launch_bounds__(256) relu_bwd_kernel(const float* __restrict__
 // nearest even, overflow to infinity, NaN kept: the conversion Go's float32(x) does.
 __global__ void __launch_bounds__(256) f64_to_f32_kernel(const double* __restrict__ in,
                                                          float* __restrict__ out, uint64_t n, int vec) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
   uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
   if (vec) {  // 2 x 16-byte loads, one 16-byte store per thread and step
@@ -237,6 +253,8 @@ __global__ void __launch_bounds__(256) f64_to_f32_kernel(const double* __restric
 }
 __global__ void __launch_bounds__(256) f32_to_f64_kernel(const float* __restrict__ in,
                                                          double* __restrict__ out, uint64_t n, int vec) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
   uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
   if (vec) {
@@ -258,6 +276,8 @@ __global__ void __launch_bounds__(256) f32_to_f64_kernel(const float* __restrict
 __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ in,
                                                      const float* __restrict__ mask, uint64_t rows,
                                                      uint64_t cols, float* __restrict__ out) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
   __shared__ float part[8][33];
   const uint32_t cx = threadIdx.x & 31u, ry = threadIdx.x >> 5;
   const uint64_t col = blockIdx.x * 32ull + cx;
@@ -295,13 +315,13 @@ void launch_transpose(const float* in, uint64_t rows, uint64_t cols, float* out,
   const bool vin = (cols % 4 == 0) && aligned16(in);
   const bool vout = (rows % 4 == 0) && aligned16(out);
   if (vin && vout)
-    transpose_kernel<true, true><<<grid, 256, 0, stream>>>(in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+    launch_kernel(transpose_kernel<true, true>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_c);
   else if (vin)
-    transpose_kernel<true, false><<<grid, 256, 0, stream>>>(in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+    launch_kernel(transpose_kernel<true, false>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_c);
   else if (vout)
-    transpose_kernel<false, true><<<grid, 256, 0, stream>>>(in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+    launch_kernel(transpose_kernel<false, true>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_c);
   else
-    transpose_kernel<false, false><<<grid, 256, 0, stream>>>(in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+    launch_kernel(transpose_kernel<false, false>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_c);
 }
 
 void launch_cvt_f16(const float* src, uint64_t rows, uint64_t cols, void* dst, uint64_t pitch,
@@ -309,7 +329,7 @@ void launch_cvt_f16(const float* src, uint64_t rows, uint64_t cols, void* dst, u
   if (rows == 0 || cols == 0) return;
   const int vec = (cols % 4 == 0) && aligned16(src) && aligned16(dst) && (pitch % 4 == 0);
   const uint64_t items = vec ? rows * (cols / 4) : rows * cols;
-  cvt_f16_kernel<<<stream_grid(items, 256, 148 * 16), 256, 0, stream>>>(
+  launch_kernel(cvt_f16_kernel, dim3(stream_grid(items, 256, 148 * 16)), dim3(256), 0, stream, 
       src, rows, cols, static_cast<uint16_t*>(dst), pitch, mode, vec);
 }
 
@@ -319,44 +339,44 @@ void launch_split_tf32(const float* src, uint64_t rows, uint64_t cols, float* hi
   const int vec = (cols % 4 == 0) && aligned16(src) && aligned16(hi) && aligned16(lo) &&
                   (pitch % 4 == 0) && (!mask || aligned16(mask));
   const uint64_t items = vec ? rows * (cols / 4) : rows * cols;
-  split_tf32_kernel<<<stream_grid(items, 256, 148 * 16), 256, 0, stream>>>(src, mask, rows, cols, hi,
+  launch_kernel(split_tf32_kernel, dim3(stream_grid(items, 256, 148 * 16)), dim3(256), 0, stream, src, mask, rows, cols, hi,
                                                                            lo, pitch, vec);
 }
 
 void launch_add_broadcast(const float* a, const float* b, float* c, uint64_t rows, uint64_t cols,
                           int mode, cudaStream_t stream) {
   if (rows == 0 || cols == 0) return;
-  add_broadcast_kernel<<<stream_grid(rows * cols, 256, 148 * 16), 256, 0, stream>>>(a, b, c, rows,
+  launch_kernel(add_broadcast_kernel, dim3(stream_grid(rows * cols, 256, 148 * 16)), dim3(256), 0, stream, a, b, c, rows,
                                                                                     cols, mode);
 }
 
 void launch_relu_forward(const float* in, float* out, uint64_t n, cudaStream_t stream) {
   if (n == 0) return;
-  relu_fwd_kernel<<<stream_grid(n, 256, 148 * 16), 256, 0, stream>>>(in, out, n);
+  launch_kernel(relu_fwd_kernel, dim3(stream_grid(n, 256, 148 * 16)), dim3(256), 0, stream, in, out, n);
 }
 
 void launch_relu_backward(const float* grad_out, const float* act_out, float* grad_in, uint64_t n,
                           cudaStream_t stream) {
   if (n == 0) return;
-  relu_bwd_kernel<<<stream_grid(n, 256, 148 * 16), 256, 0, stream>>>(grad_out, act_out, grad_in, n);
+  launch_kernel(relu_bwd_kernel, dim3(stream_grid(n, 256, 148 * 16)), dim3(256), 0, stream, grad_out, act_out, grad_in, n);
 }
 
 void launch_f64_to_f32(const double* in, float* out, uint64_t n, cudaStream_t stream) {
   if (n == 0) return;
   const int vec = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0 && n >= 4;
-  f64_to_f32_kernel<<<stream_grid(vec ? n >> 2 : n, 256, 148 * 16), 256, 0, stream>>>(in, out, n, vec);
+  launch_kernel(f64_to_f32_kernel, dim3(stream_grid(vec ? n >> 2 : n, 256, 148 * 16)), dim3(256), 0, stream, in, out, n, vec);
 }
 
 void launch_f32_to_f64(const float* in, double* out, uint64_t n, cudaStream_t stream) {
   if (n == 0) return;
   const int vec = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0 && n >= 4;
-  f32_to_f64_kernel<<<stream_grid(vec ? n >> 2 : n, 256, 148 * 16), 256, 0, stream>>>(in, out, n, vec);
+  launch_kernel(f32_to_f64_kernel, dim3(stream_grid(vec ? n >> 2 : n, 256, 148 * 16)), dim3(256), 0, stream, in, out, n, vec);
 }
 
 void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream,
                    const float* mask) {
   if (cols == 0) return;
-  colsum_kernel<<<uint32_t((cols + 31) / 32), 256, 0, stream>>>(in, mask, rows, cols, out);
+  launch_kernel(colsum_kernel, dim3(uint32_t((cols + 31) / 32)), dim3(256), 0, stream, in, mask, rows, cols, out);
 }
 
 }  // namespace gonn

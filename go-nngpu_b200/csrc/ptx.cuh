@@ -97,6 +97,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
 }
 
 // ---------------------------------------------------------------- TMA
+// Programmatic dependent launch: release lets the next kernel on the stream be scheduled
+// early; wait holds this kernel until the previous one has completed (memory visible).
+// Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void grid_dependency_release() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
