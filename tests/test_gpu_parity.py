@@ -768,3 +768,40 @@ def test_split_k_with_more_units_than_sms_and_in_batches(gpu):
     finally:
         L.gonngpu_set_gemm_split_k(0)
         L.gonngpu_set_gemm_pair_mode(-1)
+
+
+# ------------------------------------------------------------------ seeded random sweep
+def test_random_shapes_layouts_and_epilogues(gpu):
+    """120 seeded random products (ragged sizes, all four layouts, both precisions, random
+    alpha / beta / bias / activation) against the float64 oracle: the tile chooser, split-K,
+    3-D operand boxes and both epilogue store paths all get hit by the mix."""
+    rng = np.random.default_rng(2024)
+    acts = [-1, 0, 1, 2, 3, 4]
+    bad = []
+    for case in range(120):
+        m = int(rng.integers(1, 700))
+        n = int(rng.integers(1, 700))
+        k = int(rng.integers(1, 1500)) if case % 3 else int(rng.integers(1, 5000))
+        ta, tb = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        prec = gpu.FP32_3XTF32 if case % 2 else gpu.FP16_RN
+        A = (rng.standard_normal((m, k)) / np.sqrt(k)).astype(np.float32)
+        B = rng.standard_normal((k, n)).astype(np.float32)
+        alpha = float(rng.choice([1.0, 0.5, -2.0]))
+        beta = float(rng.choice([0.0, 0.0, 0.75]))
+        bias = rng.standard_normal(n).astype(np.float32) if rng.integers(0, 2) else None
+        act = int(rng.choice(acts))
+        C0 = rng.standard_normal((m, n)).astype(np.float32)
+        As = np.ascontiguousarray(A.T) if ta else A
+        Bs = np.ascontiguousarray(B.T) if tb else B
+        got = run_matmul(gpu, As, Bs, ta, tb, precision=prec, alpha=alpha, beta=beta, C0=C0, bias=bias,
+                         act=act, act_param=0.1)
+        Ar, Br = (oracle.f16_rn(A), oracle.f16_rn(B)) if prec == gpu.FP16_RN else (A, B)
+        z = alpha * oracle.gemm_f64(Ar, Br) + beta * C0.astype(np.float64)
+        if bias is not None:
+            z = z + bias
+        ref = oracle.apply_act_f64(z, act, 0.1)
+        tol = 3e-5 if prec == gpu.FP16_RN else FP32_TOL   # fp16: fp32 accumulation error only
+        err = oracle.rel_frobenius(got, ref)
+        if not err <= tol:
+            bad.append((case, m, n, k, ta, tb, prec, alpha, beta, bias is not None, act, err))
+    assert not bad, bad[:5]
