@@ -191,6 +191,8 @@ def run_ours(args, rank, world, local_rank):
         # Measured on 8 GPUs: 2 slabs hide ~50 us of broadcast but the NCCL kernels
         # then share the SMs with the GEMM (0.41 -> 0.455 ms), no net gain: default 1.
         slabs = max(1, args.slabs) if world > 1 else 1
+        if args.gemm_ctas:
+            assert L.gonngpu_set_gemm_tuning(0, args.gemm_ctas) == 0
         assert N_DIM % (slabs * 256) == 0, "--slabs must leave whole 256-column tiles"
         w = N_DIM // slabs
         Bs = [torch.zeros((K_DIM, w), device=dev, dtype=torch.float16) for _ in range(slabs)]
@@ -377,6 +379,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--slabs", type=int, default=1,
                     help="column slabs B is broadcast in when there are several ranks (1, 2, 4 ...)")
+    ap.add_argument("--gemm-ctas", type=int, default=0,
+                    help="CTAs the GEMM may use (0 = one per SM); fewer leaves SMs to the broadcast kernels")
     ap.add_argument("--m-total", type=int, default=M_TOTAL,
                     help="rows of A (default: the benchmark's 131072; smaller only for profiler captures)")
     args = ap.parse_args()
