@@ -354,6 +354,8 @@ int finish(Device& d, CError* err, int exec_code, const char* what) {
   if (g_blocking && d.status_host->code != 0) {
     d.last_status = *d.status_host;
     std::memset(d.status_host, 0, sizeof(GemmStatus));
+    // a kernel that gave up may have left split-K arrival counters half counted
+    cudaMemsetAsync(d.splitk_counters, 0, kSplitKSlots * 4, d.stream);
     set_error(err,
               "%s: GEMM kernel gave up waiting (role %u, where 0x%x, tile %u, k block %u).", what,
               d.last_status.code, d.last_status.where, d.last_status.tile, d.last_status.kblock);
@@ -1285,7 +1287,8 @@ int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOu
   // bias gradient: column sums of the masked gradient
   if (db) {
     gonn::launch_colsum(dY->dptr, uint64_t(batch), uint64_t(out_size), db->dptr, d.stream,
-                        act ? act->dptr : nullptr);
+                        act ? act->dptr : nullptr, d.splitk_ws, kSplitKBytes / 4, d.splitk_counters,
+                        kSplitKSlots);
     ++g_stats[3];
     wrote(db);
   }
@@ -1391,7 +1394,8 @@ int gonngpu_column_sum(GPUPtr inPtr, long rows, long cols, GPUPtr outPtr, CError
     set_error(err, "column sum: host to device copy failed.");
     return -6;
   }
-  gonn::launch_colsum(in->dptr, uint64_t(rows), uint64_t(cols), out->dptr, d.stream);
+  gonn::launch_colsum(in->dptr, uint64_t(rows), uint64_t(cols), out->dptr, d.stream, nullptr, d.splitk_ws,
+                      kSplitKBytes / 4, d.splitk_counters, kSplitKSlots);
   ++g_stats[3];
   wrote(out);
   return finish(d, err, -6, "column sum");

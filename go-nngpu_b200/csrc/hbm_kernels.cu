@@ -2,6 +2,7 @@
 // (fp32 -> fp16 plane, fp32 -> tf32 hi/lo planes), bias broadcast add, ReLU
 // forward/backward and the bias-gradient column sum.  All are pure streaming
 // kernels: coalesced 16-byte accesses where alignment allows, scalar edges.
+#include <algorithm>
 #include <cuda_fp16.h>
 
 #include "kernels.h"
@@ -271,29 +272,57 @@ __global__ void __launch_bounds__(256) f32_to_f64_kernel(const float* __restrict
   }
 }
 
-// Column sum (bias gradient, gpu/matrix/layers.go:281-294): rows are added in
-// index order per partial, partials in order, so the result is deterministic.
+// Column sum (bias gradient, gpu/matrix/layers.go:281-294).  Block (x, y) adds rows
+// [y * chunk_rows, (y + 1) * chunk_rows) of 32 columns, eight row lanes each in row order,
+// lanes in lane order.  With one chunk that is the result.  With several, the partial sums
+// go to `partial` [chunk][col] and the block that arrives last on the column block's counter
+// adds them in chunk order (no block waits for another; the counter is left at zero), so
+// the result is the same from run to run whatever the arrival order.
 __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ in,
                                                      const float* __restrict__ mask, uint64_t rows,
-                                                     uint64_t cols, float* __restrict__ out) {
+                                                     uint64_t cols, float* __restrict__ out,
+                                                     uint64_t chunk_rows, float* partial,
+                                                     uint32_t* counters) {
   ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
   ptx::grid_dependency_wait();
   __shared__ float part[8][33];
+  __shared__ uint32_t last;
   const uint32_t cx = threadIdx.x & 31u, ry = threadIdx.x >> 5;
   const uint64_t col = blockIdx.x * 32ull + cx;
+  const uint64_t r0 = blockIdx.y * chunk_rows;
+  const uint64_t r1 = (r0 + chunk_rows < rows) ? r0 + chunk_rows : rows;
   float s = 0.f;
   if (col < cols)
-    for (uint64_t r = ry; r < rows; r += 8) {
+    for (uint64_t r = r0 + ry; r < r1; r += 8) {
       const float v = in[r * cols + col];
       s += (!mask || mask[r * cols + col] > 0.0f) ? v : 0.0f;
     }
   part[ry][cx] = s;
   __syncthreads();
-  if (ry == 0 && col < cols) {
-    float t = 0.f;
+  float t = 0.f;
+  if (ry == 0) {
 #pragma unroll
     for (int k = 0; k < 8; ++k) t += part[k][cx];
-    out[col] = t;
+  }
+  if (gridDim.y == 1) {
+    if (ry == 0 && col < cols) out[col] = t;
+    return;
+  }
+  if (ry == 0 && col < cols) __stcg(partial + uint64_t(blockIdx.y) * cols + col, t);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t before = atomicAdd(counters + blockIdx.x, 1u);
+    last = (before + 1u == gridDim.y) ? 1u : 0u;
+    if (last) counters[blockIdx.x] = 0u;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  if (ry == 0 && col < cols) {
+    float total = 0.f;
+    for (uint32_t c = 0; c < gridDim.y; ++c) total += __ldcg(partial + uint64_t(c) * cols + col);
+    out[col] = total;
   }
 }
 
@@ -374,9 +403,22 @@ void launch_f32_to_f64(const float* in, double* out, uint64_t n, cudaStream_t st
 }
 
 void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream,
-                   const float* mask) {
+                   const float* mask, float* ws, size_t ws_floats, uint32_t* counters,
+                   uint32_t counter_slots) {
   if (cols == 0) return;
-  launch_kernel(colsum_kernel, dim3(uint32_t((cols + 31) / 32)), dim3(256), 0, stream, in, mask, rows, cols, out);
+  const uint32_t col_blocks = uint32_t((cols + 31) / 32);
+  // row chunks of at least 64 rows, enough of them to put about two blocks on every SM
+  uint64_t chunks = 1;
+  if (ws && counters && col_blocks <= counter_slots && rows >= 128) {
+    chunks = std::min<uint64_t>(rows / 64, std::max<uint64_t>(1, 296 / col_blocks));
+    while (chunks > 1 && chunks * cols > ws_floats) --chunks;
+  }
+  uint64_t chunk_rows = (rows + chunks - 1) / chunks;
+  chunk_rows = (chunk_rows + 7) / 8 * 8;
+  chunks = rows ? (rows + chunk_rows - 1) / chunk_rows : 1;
+  if (chunks < 1) chunks = 1;
+  launch_kernel(colsum_kernel, dim3(col_blocks, uint32_t(chunks)), dim3(256), 0, stream, in, mask, rows, cols, out,
+                chunk_rows, ws, counters);
 }
 
 }  // namespace gonn

@@ -99,8 +99,11 @@ void launch_relu_forward(const float* in, float* out, uint64_t n, cudaStream_t s
 void launch_relu_backward(const float* grad_out, const float* act_out, float* grad_in, uint64_t n,
                           cudaStream_t stream);
 // out[j] = sum_i in[i, j]   (bias gradient)
+// With a workspace (`ws_floats` floats, `counter_slots` zeroed counters that every launch
+// leaves at zero; one launch at a time) the rows are split over several blocks.
 void launch_colsum(const float* in, uint64_t rows, uint64_t cols, float* out, cudaStream_t stream,
-                   const float* mask = nullptr);
+                   const float* mask = nullptr, float* ws = nullptr, size_t ws_floats = 0,
+                   uint32_t* counters = nullptr, uint32_t counter_slots = 0);
 
 // float64 <-> float32 (round to nearest even), for the gonum facade's host data.
 void launch_f64_to_f32(const double* in, float* out, uint64_t n, cudaStream_t stream);

@@ -805,3 +805,28 @@ def test_random_shapes_layouts_and_epilogues(gpu):
         if not err <= tol:
             bad.append((case, m, n, k, ta, tb, prec, alpha, beta, bias is not None, act, err))
     assert not bad, bad[:5]
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (7, 5), (127, 33), (128, 64), (512, 1024), (513, 10), (5000, 100),
+                                   (70000, 40), (300, 5000)])
+def test_column_sum_shapes_and_determinism(gpu, shape):
+    """Bias gradient: one row chunk or several (partials through the workspace), integer data exact,
+    random data within float32 summation error of float64, and the same bits on every run."""
+    rows, cols = shape
+    rng = np.random.default_rng(rows * 31 + cols)
+    Xi = rng.integers(-8, 9, shape).astype(np.float32)
+    x, o = gpu.Buffer.from_host(Xi), gpu.Buffer.empty(cols * 4)
+    gpu.column_sum(x, rows, cols, o)
+    assert np.array_equal(o.retrieve((cols,)), Xi.sum(axis=0, dtype=np.float64).astype(np.float32))
+    X = rng.standard_normal(shape).astype(np.float32)
+    x.upload(X)
+    gpu.column_sum(x, rows, cols, o)
+    first = o.retrieve((cols,))
+    ref = X.sum(axis=0, dtype=np.float64)
+    assert np.allclose(first, ref, rtol=1e-5, atol=1e-5 * np.sqrt(rows))
+    gpu.column_sum(x, rows, cols, o)
+    assert np.array_equal(first.view(np.uint32), o.retrieve((cols,)).view(np.uint32))
+    # a split fp32 product right after it finds the shared counters at zero
+    A = rng.standard_normal((128, 1024)).astype(np.float32)
+    B = rng.standard_normal((1024, 128)).astype(np.float32)
+    assert oracle.rel_frobenius(run_matmul(gpu, A, B, precision=gpu.FP32_3XTF32), oracle.gemm_f64(A, B)) <= FP32_TOL
