@@ -252,6 +252,177 @@ inline TensorPtr AddBroadcast(const TensorPtr& A, const TensorPtr& B) {
   return result;
 }
 
+namespace detail {
+using BinaryEntry = int (*)(GPUPtr, long, long, GPUPtr, long, long, GPUPtr, long, long, DevicePtr, CError*);
+using ScalarEntry = int (*)(GPUPtr, long, long, float, GPUPtr, DevicePtr, CError*);
+
+// Shared body of Sub / Mul / Div and of Add on equal shapes (matrix.go:464-702): a zeroed
+// result tensor, all three on the device, one native call.
+inline TensorPtr same_shape_op(const TensorPtr& A, const TensorPtr& B, BinaryEntry entry,
+                               const char* failed) {
+  const int rows = A->Shape[0], cols = A->Shape[1];
+  TensorPtr result = tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols));
+  A->EnsureGPU();
+  B->EnsureGPU();
+  result->EnsureGPU();
+  CError err{nullptr};
+  const int rc = entry(A->GPUPointer(), rows, cols, B->GPUPointer(), B->Shape[0], B->Shape[1],
+                       result->GPUPointer(), rows, cols, A->DevicePointer(), &err);
+  if (rc != 0)
+    throw gonngpu::Error(std::string(failed) + " failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
+inline void require_same_2d(const TensorPtr& A, const TensorPtr& B, const char* op, const char* noun) {
+  if (A->Shape.size() != 2 || B->Shape.size() != 2)
+    throw gonngpu::Error(std::string(op) + " requires 2D tensors (matrices)");
+  if (A->Shape[0] != B->Shape[0] || A->Shape[1] != B->Shape[1])
+    throw gonngpu::Error("incompatible matrix dimensions for " + std::string(noun) + ": A (" +
+                         std::to_string(A->Shape[0]) + "x" + std::to_string(A->Shape[1]) + ") != B (" +
+                         std::to_string(B->Shape[0]) + "x" + std::to_string(B->Shape[1]) + ")");
+}
+
+inline TensorPtr scalar_op(const TensorPtr& A, float scalar, ScalarEntry entry, const char* op,
+                           const char* failed) {
+  if (A->Shape.size() != 2) throw gonngpu::Error(std::string(op) + " requires 2D tensor (matrix)");
+  const int rows = A->Shape[0], cols = A->Shape[1];
+  TensorPtr result = tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols));
+  A->EnsureGPU();
+  result->EnsureGPU();
+  CError err{nullptr};
+  const int rc = entry(A->GPUPointer(), rows, cols, scalar, result->GPUPointer(), A->DevicePointer(), &err);
+  if (rc != 0)
+    throw gonngpu::Error(std::string(failed) + " failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+}  // namespace detail
+
+// matrix.go:407-427: equal shapes go to the element-wise entry, the four 2-D broadcast
+// patterns (matrix.go:429-461) to the broadcasting one.
+inline TensorPtr Add(const TensorPtr& A, const TensorPtr& B) {
+  if (A->Shape.size() != 2 || B->Shape.size() != 2)
+    throw gonngpu::Error("Add requires 2D tensors (matrices)");
+  const auto& a = A->Shape;
+  const auto& b = B->Shape;
+  const bool same = a[0] == b[0] && a[1] == b[1];
+  const bool rows_broadcast = a[0] != b[0] && (a[0] == 1 || b[0] == 1) && a[1] == b[1];
+  const bool cols_broadcast = a[0] == b[0] && a[1] != b[1] && (a[1] == 1 || b[1] == 1);
+  if (!same && !rows_broadcast && !cols_broadcast)
+    throw gonngpu::Error("incompatible matrix dimensions for addition: A (" + std::to_string(a[0]) + "x" +
+                         std::to_string(a[1]) + ") vs B (" + std::to_string(b[0]) + "x" +
+                         std::to_string(b[1]) + ")");
+  if (same) return detail::same_shape_op(A, B, perform_mps_matrix_add, "GPU matrix addition");
+  return AddBroadcast(A, B);
+}
+inline TensorPtr Sub(const TensorPtr& A, const TensorPtr& B) {  // matrix.go:551-600
+  detail::require_same_2d(A, B, "Sub", "subtraction");
+  return detail::same_shape_op(A, B, perform_mps_matrix_subtract, "GPU matrix subtraction");
+}
+inline TensorPtr Mul(const TensorPtr& A, const TensorPtr& B) {  // matrix.go:602-651 (element-wise)
+  detail::require_same_2d(A, B, "Mul", "element-wise multiplication");
+  return detail::same_shape_op(A, B, perform_mps_matrix_element_multiply,
+                               "GPU matrix element-wise multiplication");
+}
+inline TensorPtr Div(const TensorPtr& A, const TensorPtr& B) {  // matrix.go:653-702
+  detail::require_same_2d(A, B, "Div", "element-wise division");
+  return detail::same_shape_op(A, B, perform_mps_matrix_element_divide, "GPU matrix element-wise division");
+}
+inline TensorPtr ScalarAdd(const TensorPtr& A, float scalar) {  // matrix.go:704-746
+  return detail::scalar_op(A, scalar, perform_mps_matrix_scalar_add, "ScalarAdd", "GPU scalar addition");
+}
+inline TensorPtr ScalarMul(const TensorPtr& A, float scalar) {  // matrix.go:748-790
+  return detail::scalar_op(A, scalar, perform_mps_matrix_scalar_multiply, "ScalarMul",
+                           "GPU scalar multiplication");
+}
+
+// ---- gpu/matrix/activation.go:56-310 -------------------------------------------------
+// ActivationForward / ActivationBackward: one result tensor of the input's shape and the
+// native entry the activation type names; Softmax takes 1-D and 2-D tensors only.  The
+// backward forms receive the activation OUTPUT, as the native side expects.
+inline TensorPtr ActivationForward(const TensorPtr& input, ActivationType type, float alpha) {
+  if (input->Shape.empty()) throw gonngpu::Error("cannot apply activation to empty tensor");
+  // (checked before any device work here; the reference reports it after EnsureGPU)
+  if (type == Softmax && input->Shape.size() > 2)
+    throw gonngpu::Error("softmax currently supports only 1D and 2D tensors");
+  long n = 1;
+  for (int d : input->Shape) n *= d;
+  TensorPtr result = tensor::NewTensor(input->Shape, std::vector<float>(size_t(n)));
+  input->EnsureGPU();
+  result->EnsureGPU();
+  GPUPtr in = input->GPUPointer(), out = result->GPUPointer();
+  DevicePtr dev = input->DevicePointer();
+  CError err{nullptr};
+  int rc = 0;
+  switch (type) {
+    case ReLU: rc = perform_activation_relu_forward(in, n, out, dev, &err); break;
+    case Sigmoid: rc = perform_activation_sigmoid_forward(in, n, out, dev, &err); break;
+    case Tanh: rc = perform_activation_tanh_forward(in, n, out, dev, &err); break;
+    case LeakyReLU: rc = perform_activation_leaky_relu_forward(in, n, alpha, out, dev, &err); break;
+    case ELU: rc = perform_activation_elu_forward(in, n, alpha, out, dev, &err); break;
+    case Swish: rc = perform_activation_swish_forward(in, n, out, dev, &err); break;
+    case GELU: rc = perform_activation_gelu_forward(in, n, out, dev, &err); break;
+    case Softmax:
+      if (input->Shape.size() == 1)
+        rc = perform_activation_softmax_1d_forward(in, input->Shape[0], out, dev, &err);
+      else if (input->Shape.size() == 2)
+        rc = perform_activation_softmax_2d_forward(in, input->Shape[0], input->Shape[1], out, dev, &err);
+      else
+        throw gonngpu::Error("softmax currently supports only 1D and 2D tensors");
+      break;
+    default: throw gonngpu::Error("unsupported activation type: " + std::to_string(int(type)));
+  }
+  if (rc != 0)
+    throw gonngpu::Error("GPU activation forward failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
+inline TensorPtr ActivationBackward(const TensorPtr& gradOutput, const TensorPtr& activationOutput,
+                                    ActivationType type, float alpha) {
+  if (gradOutput->Shape.empty() || activationOutput->Shape.empty())
+    throw gonngpu::Error("cannot compute activation gradient for empty tensors");
+  if (gradOutput->Shape.size() != activationOutput->Shape.size())
+    throw gonngpu::Error("gradient and activation output must have same dimensions");
+  for (size_t i = 0; i < gradOutput->Shape.size(); ++i)
+    if (gradOutput->Shape[i] != activationOutput->Shape[i])
+      throw gonngpu::Error("gradient and activation output shape mismatch at dimension " + std::to_string(i));
+  long n = 1;
+  for (int d : gradOutput->Shape) n *= d;
+  TensorPtr result = tensor::NewTensor(gradOutput->Shape, std::vector<float>(size_t(n)));
+  gradOutput->EnsureGPU();
+  activationOutput->EnsureGPU();
+  result->EnsureGPU();
+  GPUPtr g = gradOutput->GPUPointer(), a = activationOutput->GPUPointer(), out = result->GPUPointer();
+  DevicePtr dev = gradOutput->DevicePointer();
+  CError err{nullptr};
+  int rc = 0;
+  switch (type) {
+    case ReLU: rc = perform_activation_relu_backward(g, a, n, out, dev, &err); break;
+    case Sigmoid: rc = perform_activation_sigmoid_backward(g, a, n, out, dev, &err); break;
+    case Tanh: rc = perform_activation_tanh_backward(g, a, n, out, dev, &err); break;
+    case LeakyReLU: rc = perform_activation_leaky_relu_backward(g, a, n, alpha, out, dev, &err); break;
+    case ELU: rc = perform_activation_elu_backward(g, a, n, alpha, out, dev, &err); break;
+    case Swish: rc = perform_activation_swish_backward(g, a, n, out, dev, &err); break;
+    case GELU: rc = perform_activation_gelu_backward(g, a, n, out, dev, &err); break;
+    case Softmax:
+      if (gradOutput->Shape.size() == 1)
+        rc = perform_activation_softmax_1d_backward(g, a, gradOutput->Shape[0], out, dev, &err);
+      else if (gradOutput->Shape.size() == 2)
+        rc = perform_activation_softmax_2d_backward(g, a, gradOutput->Shape[0], gradOutput->Shape[1], out,
+                                                    dev, &err);
+      else
+        throw gonngpu::Error("softmax currently supports only 1D and 2D tensors");
+      break;
+    default: throw gonngpu::Error("unsupported activation type: " + std::to_string(int(type)));
+  }
+  if (rc != 0)
+    throw gonngpu::Error("GPU activation backward failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
 // ---- gpu/matrix/optimized-kernels.go:21-75 ----------------------------------------
 inline TensorPtr OptimizedGEMM(const TensorPtr& A, const TensorPtr& B, float alpha, float beta) {
   if (A->Shape.size() != 2 || B->Shape.size() != 2)

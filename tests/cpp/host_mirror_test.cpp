@@ -61,6 +61,41 @@ static void host_only() {
   } catch (const gonngpu::Error& e) {
     CHECK(std::string(e.what()) == "Transpose requires 2D tensor (matrix)");
   }
+  // element-wise family: shape errors and their text (matrix.go:407-427, 551-558, 704-707)
+  {
+    auto c = tensor::NewTensor({3, 2}, std::vector<float>(6));
+    try {
+      matrix::Sub(a, c);
+      CHECK(false);
+    } catch (const gonngpu::Error& e) {
+      CHECK(std::string(e.what()) == "incompatible matrix dimensions for subtraction: A (2x3) != B (3x2)");
+    }
+    try {
+      matrix::Add(a, c);
+      CHECK(false);
+    } catch (const gonngpu::Error& e) {
+      CHECK(std::string(e.what()) == "incompatible matrix dimensions for addition: A (2x3) vs B (3x2)");
+    }
+    try {
+      matrix::ScalarMul(v, 2.0f);
+      CHECK(false);
+    } catch (const gonngpu::Error& e) {
+      CHECK(std::string(e.what()) == "ScalarMul requires 2D tensor (matrix)");
+    }
+    auto t3 = tensor::NewTensor({1, 2, 3}, std::vector<float>(6));
+    try {
+      matrix::ActivationForward(t3, matrix::Softmax, 0.f);
+      CHECK(false);
+    } catch (const gonngpu::Error& e) {
+      CHECK(std::string(e.what()) == "softmax currently supports only 1D and 2D tensors");
+    }
+    try {
+      matrix::ActivationBackward(a, c, matrix::ReLU, 0.f);
+      CHECK(false);
+    } catch (const gonngpu::Error& e) {
+      CHECK(std::string(e.what()) == "gradient and activation output shape mismatch at dimension 0");
+    }
+  }
   // gonum-style facade: bounds checks panic (gonum-compat.go:54-56)
   auto g = matrix::NewGPUDense(2, 2, {1, 2, 3, 4});
   CHECK(g->Dims().first == 2 && g->At(1, 0) == 3.0);
@@ -133,6 +168,53 @@ static void with_gpu() {
   auto h = matrix::ForwardFloat16(tA, tB);
   h->RetrieveCPU();
   CHECK(rel_frob(h->Data, ref) <= 1e-2);
+
+  // element-wise family and activations through the Go-shaped API
+  {
+    auto s1 = matrix::Add(tA, tA);                       // equal shapes: element-wise entry
+    auto s2 = matrix::Sub(s1, tA);
+    s2->RetrieveCPU();
+    for (size_t i = 0; i < A.size(); ++i) CHECK(s2->Data[i] == (A[i] + A[i]) - A[i]);
+    auto row = tensor::NewTensor({1, K}, std::vector<float>(size_t(K), 0.5f));
+    auto s3 = matrix::Add(tA, row);                      // [M,K] + [1,K]: broadcasting entry
+    s3->RetrieveCPU();
+    CHECK(s3->Data[7] == A[7] + 0.5f);
+    auto p = matrix::Mul(tA, tA);
+    auto q = matrix::ScalarAdd(matrix::ScalarMul(p, 2.0f), 1.0f);
+    q->RetrieveCPU();
+    for (size_t i = 0; i < A.size(); i += 97) CHECK(q->Data[i] == (A[i] * A[i]) * 2.0f + 1.0f);
+    auto ones = tensor::NewTensor({M, K}, std::vector<float>(A.size(), 1.0f));
+    auto d = matrix::Div(tA, ones);
+    d->RetrieveCPU();
+    CHECK(d->Data[11] == A[11]);
+    auto zeros = tensor::NewTensor({M, K}, std::vector<float>(A.size(), 0.0f));
+    try {
+      matrix::Div(tA, zeros);
+      CHECK(false);
+    } catch (const gonngpu::Error& e) {
+      CHECK(std::string(e.what()) ==
+            "GPU matrix element-wise division failed (code -4): Division by zero encountered at element 0.");
+    }
+    auto sm = matrix::ActivationForward(tA, matrix::Softmax, 0.f);
+    sm->RetrieveCPU();
+    for (int i = 0; i < M; i += 13) {
+      double rs = 0;
+      for (int j = 0; j < K; ++j) rs += sm->Data[size_t(i) * K + j];
+      CHECK(std::fabs(rs - 1.0) <= 1e-5);
+    }
+    auto sg = matrix::ActivationForward(tA, matrix::Sigmoid, 0.f);
+    auto gsg = matrix::ActivationBackward(ones, sg, matrix::Sigmoid, 0.f);
+    sg->RetrieveCPU();
+    gsg->RetrieveCPU();
+    for (size_t i = 0; i < A.size(); i += 101) {
+      const double want = 1.0 / (1.0 + std::exp(-double(A[i])));
+      CHECK(std::fabs(sg->Data[i] - want) <= 1e-6);
+      CHECK(std::fabs(gsg->Data[i] - want * (1.0 - want)) <= 1e-6);
+    }
+    auto lk = matrix::ActivationForward(tA, matrix::LeakyReLU, 0.1f);
+    lk->RetrieveCPU();
+    for (size_t i = 0; i < A.size(); i += 89) CHECK(lk->Data[i] == (A[i] > 0 ? A[i] : 0.1f * A[i]));
+  }
 
   // gonum-style drop-in
   std::vector<double> Ad(A.begin(), A.end()), Bd(B.begin(), B.end());
