@@ -10,12 +10,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libgonngpu_cuda.so")
 SOURCES = ["gemm_sm100.cu", "hbm_kernels.cu", "elementwise.cu", "bridge.cu", "static_scratch.cu"]
-HEADERS = ["ptx.cuh", "kernels.h", os.path.join("..", "..", "include", "gonngpu.h")]
+HEADERS = ["ptx.cuh", "kernels.h", "launch.cuh", os.path.join("..", "..", "include", "gonngpu.h")]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "-shared", "-cudart", "static",
+    "--threads", "0",  # the sources compile in parallel
 ]
 
 

@@ -1,6 +1,6 @@
 """Per-configuration timings of the dense path on one GPU (device-resident inputs).
 
-    python go-nngpu_b200/microbench.py [--config c1|c2|c2nn|transpose|c3|c4|gonum|elementwise|all] [--iters N]
+    python go-nngpu_b200/microbench.py [--config c1|c2|c2nn|transpose|c3|c4|gonum|elementwise|all] [--iters N] [--cpu]
 
 Prints one JSON line per measured operation: time, TFLOP/s or GB/s, and the
 fraction of the measured peaks when MEASURED_PEAKS.json lies beside the
@@ -20,6 +20,9 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 import gonngpu as g  # noqa: E402
+
+
+CPU_LEG = False
 
 
 def peaks():
@@ -69,7 +72,26 @@ def gemm_case(name, A, B, ta, tb, precision, iters):
     a, b = g.Buffer.from_host(A), g.Buffer.from_host(B)
     c = g.Buffer.empty(M * N * 4)
     dt = timed(lambda s: g.matmul_ex(a, A.shape, ta, b, B.shape, tb, c, (M, N), precision=precision), iters)
-    emit(name, dt, flops=2.0 * M * N * K)
+    extra = {}
+    if precision == g.FP32_3XTF32:
+        # three tf32 MMAs are issued per useful product; 1100 TFLOP/s is the nominal dense tf32 rate
+        issued = 3 * 2.0 * M * N * K / dt / 1e12
+        extra.update({"tf32_issued_tflops": round(issued, 1), "frac_of_nominal_tf32_issued": round(issued / 1100.0, 3),
+                      "frac_of_nominal_tf32_useful": round(issued / 3 / 1100.0, 3)})
+    if CPU_LEG:
+        # float64 product on the host cores: the comparator the benchmark names is gonum's
+        # mat.Dense.Mul, which is not installed here; numpy/OpenBLAS float64 stands in for it
+        A64 = (A.T if ta else A).astype(np.float64)
+        B64 = (B.T if tb else B).astype(np.float64)
+        t0 = time.perf_counter()
+        ref = A64 @ B64
+        cpu = time.perf_counter() - t0
+        got = c.retrieve((M, N))
+        err = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
+        extra.update({"cpu_f64_ms": round(cpu * 1e3, 2), "cpu_tflops": round(2.0 * M * N * K / cpu / 1e12, 3),
+                      "cpu_cores": os.cpu_count(), "cpu_impl": "numpy/OpenBLAS float64 (stand-in for gonum)",
+                      "rel_frobenius_vs_f64": err})
+    emit(name, dt, flops=2.0 * M * N * K, extra=extra)
     for x in (a, b, c):
         x.release()
 
@@ -205,7 +227,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="all")
     ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--cpu", action="store_true",
+                    help="also time the float64 product on the host cores and report the error against it")
     args = ap.parse_args()
+    global CPU_LEG
+    CPU_LEG = args.cpu
     assert g.lib().gonngpu_set_device(0) == 0, "no usable B200"
     run = {"c1": lambda: config1(args.iters), "c2": lambda: config2(args.iters),
            "c2nn": lambda: config2(args.iters, transposes=False),
