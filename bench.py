@@ -353,6 +353,9 @@ def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, cl
                          "peak_source": f"{peaks['source']} cuBLAS bf16 ({peak_kind})",
                          "kernel_ms": kernel_ms_max},
             "e2e": e2e,
+            # the same job with B already resident on every GPU (slowest rank's kernel time only):
+            # what the broadcast inside the step costs is the gap between this and `value`
+            "value_b_resident": 2.0 * M_TOTAL * K_DIM * N_DIM / (kernel_ms_max * 1e-3) / 1e12,
             "gpu_launches": int(launches),  # GEMM kernels of this library inside the timed region
             "parity_spot_check_rel_frobenius": check,
         }
