@@ -201,8 +201,20 @@ def run_ours(args, rank, world, local_rank):
                 Bs[j].copy_(B16[:, j * w:(j + 1) * w])
         stream.synchronize()
 
+        # B can also travel as scatter + all-gather: rank 0 sends each rank 1/world of B's rows,
+        # then every rank gathers the pieces, instead of NCCL's broadcast.  Measured: slower
+        # (8 GPUs 0.27 against 0.19 ms for the 32 MiB, 2 GPUs 0.19 against 0.07 ms): not the default.
+        two_step = world > 1 and args.bcast == "scatter_allgather" and slabs == 1 and K_DIM % world == 0
+        if two_step:
+            piece = torch.zeros((K_DIM // world, N_DIM), device=dev, dtype=torch.float16)
+            pieces = list(Bs[0].chunk(world, dim=0)) if rank == 0 else None
+
         def step(events=None):
-            works = [dist.broadcast(Bs[j], src=0, async_op=True) for j in range(slabs)] if world > 1 else []
+            if two_step:
+                dist.scatter(piece, pieces, src=0)
+                works = [dist.all_gather_into_tensor(Bs[0], piece, async_op=True)]
+            else:
+                works = [dist.broadcast(Bs[j], src=0, async_op=True) for j in range(slabs)] if world > 1 else []
             for j in range(slabs):
                 if works:
                     works[j].wait()          # orders the stream, does not block the host
@@ -346,7 +358,8 @@ def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, cl
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows_per_gpu": rows, "parallelism": f"row-shard x{world}",
                        "l2": "operands and result (>=384 MiB per GPU) exceed the 126 MB L2",
-                       "b_broadcast_in_step": world > 1, "b_slabs": args.slabs if world > 1 else 1},
+                       "b_broadcast_in_step": world > 1, "b_slabs": args.slabs if world > 1 else 1,
+                       "b_transport": args.bcast if world > 1 else "none"},
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
                          "frac": achieved / peaks[peak_kind], "traffic": traffic_estimate(rows),
@@ -382,6 +395,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--slabs", type=int, default=1,
                     help="column slabs B is broadcast in when there are several ranks (1, 2, 4 ...)")
+    ap.add_argument("--bcast", default="broadcast", choices=["broadcast", "scatter_allgather"],
+                    help="how B reaches the other ranks inside a step")
     ap.add_argument("--gemm-ctas", type=int, default=0,
                     help="CTAs the GEMM may use (0 = one per SM); fewer leaves SMs to the broadcast kernels")
     ap.add_argument("--m-total", type=int, default=M_TOTAL,
