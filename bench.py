@@ -150,6 +150,39 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def setup_multimem(torch, dist, dev, rank, world, required, ctas=0):
+    """Symmetric buffer for B (two slots + control words) with an NVSwitch multicast address.
+    torch's symmetric-memory allocator does the allocation, the exchange of handles between the
+    processes and the multicast binding; the copies and the signalling are this library's kernels.
+    Returns None (on every rank alike) when the GPUs offer no multicast address, unless
+    `required`."""
+    from replicate import Replicator, open_symmetric  # go-nngpu_b200/replicate.py
+    import gonngpu as g
+    slot_bytes = 2 * K_DIM * N_DIM
+    res, why = None, ""
+    try:
+        buf, hdl, ctrl = open_symmetric(torch, dist, dev, slot_bytes)
+        slots = [buf[i * slot_bytes:(i + 1) * slot_bytes].view(torch.float16).view(K_DIM, N_DIM)
+                 for i in range(2)]
+        rep = Replicator(g, world, rank, 0, int(hdl.buffer_ptrs_dev), int(hdl.multicast_ptr), slot_bytes,
+                         ctrl, ctas)
+        res = {"buf": buf, "hdl": hdl, "rep": rep, "slots": slots}
+    except Exception as e:  # noqa: BLE001 - any failure means "take the NCCL broadcast"
+        why = f"{type(e).__name__}: {e}"
+    ok = torch.tensor([1 if res is not None else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if int(ok[0]) == 0:
+        if required:
+            raise RuntimeError(f"--bcast multimem: symmetric multicast memory unavailable ({why})")
+        if rank == 0 and why:
+            print(f"[bench] multicast replication unavailable, using the NCCL broadcast: {why}",
+                  file=sys.stderr, flush=True)
+        return None
+    return res
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import gonngpu as g
@@ -181,8 +214,9 @@ def run_ours(args, rank, world, local_rank):
         B32 = torch.randn((K_DIM, N_DIM), generator=gen, device=dev, dtype=torch.float32) * scale
         L.gonngpu_set_blocking(0)
         g.convert_f16_device(A32.data_ptr(), rows, K_DIM, A16.data_ptr(), K_DIM)
-        if rank == 0:
-            g.convert_f16_device(B32.data_ptr(), K_DIM, N_DIM, B16.data_ptr(), N_DIM)
+        # every rank converts its own copy of B (same seed): rank 0's is the one that travels, the
+        # others' only serve to check, bit for bit, what arrived
+        g.convert_f16_device(B32.data_ptr(), K_DIM, N_DIM, B16.data_ptr(), N_DIM)
         stream.synchronize()
 
         # With several ranks B may travel as `slabs` column slabs: the broadcasts are
@@ -209,7 +243,27 @@ def run_ours(args, rank, world, local_rank):
             piece = torch.zeros((K_DIM // world, N_DIM), device=dev, dtype=torch.float16)
             pieces = list(Bs[0].chunk(world, dim=0)) if rank == 0 else None
 
+        # Default with several ranks: rank 0 pushes B once into NVSwitch with multimem stores
+        # (gonngpu_replicate_send) and the switch delivers it to every GPU; two slots alternate so
+        # that the next B can be written while products still read the previous one.
+        mm = None
+        transport = args.bcast if world > 1 else "none"
+        if world > 1 and slabs == 1 and args.bcast in ("auto", "multimem"):
+            mm = setup_multimem(torch, dist, dev, rank, world, args.bcast == "multimem", args.bcast_ctas)
+            transport = "multimem" if mm is not None else "broadcast"
+        elif transport == "auto":
+            transport = "broadcast"
+
         def step(events=None):
+            if mm is not None:
+                slot = mm["rep"].replicate(B16.data_ptr() if rank == 0 else None)
+                if events is not None:
+                    events[0][0].record(stream)
+                g.gemm_f16_device(A16.data_ptr(), (rows, K_DIM), K_DIM, False, mm["slots"][slot].data_ptr(),
+                                  (K_DIM, N_DIM), N_DIM, False, C.data_ptr(), N_DIM)
+                if events is not None:
+                    events[0][1].record(stream)
+                return
             if two_step:
                 dist.scatter(piece, pieces, src=0)
                 works = [dist.all_gather_into_tensor(Bs[0], piece, async_op=True)]
@@ -225,10 +279,18 @@ def run_ours(args, rank, world, local_rank):
                 if events is not None:
                     events[j][1].record(stream)
 
+        def current_b():
+            return mm["slots"][mm["rep"].slot] if mm is not None else torch.cat(Bs, dim=1)
+
         for _ in range(max(args.warmup, 3)):
             step()
         stream.synchronize()
+        g.synchronize()
+        replica_ok = None
         if world > 1:
+            okt = torch.tensor([1 if torch.equal(current_b(), B16) else 0], device=dev)
+            dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+            replica_ok = bool(int(okt[0]))
             dist.barrier()
         torch.cuda.synchronize()
 
@@ -263,7 +325,7 @@ def run_ours(args, rank, world, local_rank):
         if rank == 0:
             from oracle import oracle
             idx = torch.tensor([0, 1, rows // 2, rows - 1], device=dev)
-            ref = oracle.gemm_f64(A16[idx].float().cpu().numpy(), torch.cat(Bs, dim=1).float().cpu().numpy())
+            ref = oracle.gemm_f64(A16[idx].float().cpu().numpy(), current_b().float().cpu().numpy())
             check = oracle.rel_frobenius(C[idx].cpu().numpy(), ref)
 
         # ---- end to end through the handle-based C ABI from page-locked host memory
@@ -274,7 +336,8 @@ def run_ours(args, rank, world, local_rank):
         del A32
 
     if rank == 0:
-        report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, clocks, launches, check, e2e)
+        report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, clocks, launches, check, e2e,
+               transport, replica_ok)
     if world > 1:
         dist.destroy_process_group()
 
@@ -346,7 +409,8 @@ def traffic_estimate(rows):
     return per_row * rows + b_bytes
 
 
-def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, clocks, launches, check, e2e):
+def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, clocks, launches, check, e2e,
+           transport="none", replica_ok=None):
     if True:
         peaks = load_peaks()
         timed_s = total_ms * 1e-3
@@ -359,7 +423,7 @@ def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, cl
             "config": {"workload": WORKLOAD, "rows_per_gpu": rows, "parallelism": f"row-shard x{world}",
                        "l2": "operands and result (>=384 MiB per GPU) exceed the 126 MB L2",
                        "b_broadcast_in_step": world > 1, "b_slabs": args.slabs if world > 1 else 1,
-                       "b_transport": args.bcast if world > 1 else "none"},
+                       "b_transport": transport, "b_replica_bit_exact": replica_ok},
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
                          "frac": achieved / peaks[peak_kind], "traffic": traffic_estimate(rows),
@@ -395,8 +459,13 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--slabs", type=int, default=1,
                     help="column slabs B is broadcast in when there are several ranks (1, 2, 4 ...)")
-    ap.add_argument("--bcast", default="broadcast", choices=["broadcast", "scatter_allgather"],
-                    help="how B reaches the other ranks inside a step")
+    ap.add_argument("--bcast", default="auto",
+                    choices=["auto", "multimem", "broadcast", "scatter_allgather"],
+                    help="how B reaches the other ranks inside a step: multimem = this library's "
+                         "multicast-store kernel over NVSwitch, broadcast = NCCL; auto takes multimem "
+                         "when the GPUs offer a multicast address, else broadcast")
+    ap.add_argument("--bcast-ctas", type=int, default=0,
+                    help="thread blocks of the multimem push (0 = one per SM)")
     ap.add_argument("--gemm-ctas", type=int, default=0,
                     help="CTAs the GEMM may use (0 = one per SM); fewer leaves SMs to the broadcast kernels")
     ap.add_argument("--m-total", type=int, default=M_TOTAL,

@@ -9,7 +9,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libgonngpu_cuda.so")
-SOURCES = ["gemm_sm100.cu", "hbm_kernels.cu", "elementwise.cu", "bridge.cu", "static_scratch.cu"]
+SOURCES = ["gemm_sm100.cu", "hbm_kernels.cu", "elementwise.cu", "bridge.cu", "static_scratch.cu",
+           "replicate.cu"]
 HEADERS = ["ptx.cuh", "kernels.h", "launch.cuh", os.path.join("..", "..", "include", "gonngpu.h")]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -945,6 +945,63 @@ int gonngpu_convert_f16_device(const float* src, long rows, long cols, void* dst
   return finish(d, err, -6, "convert_f16_device");
 }
 
+// ---- replication of B for the row-sharded product ----------------------------------
+int gonngpu_replicate_send(const void* src, void* dst_multicast, long bytes, void* const* bases_dev,
+                           int world, int rank, long ctrl_offset, int slot, unsigned epoch,
+                           unsigned ack_needed, int ctas, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!src || !dst_multicast || !bases_dev) {
+    set_error(err, "replicate_send: NULL pointer.");
+    return -2;
+  }
+  if (bytes <= 0 || bytes % 16 || (reinterpret_cast<uintptr_t>(src) & 15) ||
+      (reinterpret_cast<uintptr_t>(dst_multicast) & 15) || world < 1 ||
+      world > gonn::kReplicaMaxRanks || rank < 0 || rank >= world || ctrl_offset < 0 ||
+      ctrl_offset % 16 || (slot != 0 && slot != 1) || ctas < 0 || ctas > 4096) {
+    set_error(err, "replicate_send: sizes and addresses must be multiples of 16 bytes, 1..%d ranks, "
+                   "slot 0 or 1.", gonn::kReplicaMaxRanks);
+    return -3;
+  }
+  if (ensure_device(g_current, err)) return -1;
+  Device& d = g_dev[g_current];
+  cudaError_t e = gonn::launch_replicate_send(src, dst_multicast, uint64_t(bytes), bases_dev, world, rank,
+                                              uint64_t(ctrl_offset), slot, epoch, ack_needed,
+                                              d.status_dev, ctas ? ctas : d.sm_count, d.stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error(err, "replicate_send: launch failed: %s", cudaGetErrorString(e));
+    return -4;
+  }
+  ++g_stats[3];
+  return finish(d, err, -6, "replicate_send");
+}
+
+int gonngpu_replicate_wait(void* const* bases_dev, int world, int owner, int rank, long ctrl_offset,
+                           int slot, unsigned epoch, unsigned ack_value, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!bases_dev) {
+    set_error(err, "replicate_wait: NULL pointer.");
+    return -2;
+  }
+  if (world < 1 || world > gonn::kReplicaMaxRanks || rank < 0 || rank >= world || owner < 0 ||
+      owner >= world || ctrl_offset < 0 || ctrl_offset % 16 || (slot != 0 && slot != 1)) {
+    set_error(err, "replicate_wait: 1..%d ranks, owner and rank inside the group, slot 0 or 1.",
+              gonn::kReplicaMaxRanks);
+    return -3;
+  }
+  if (ensure_device(g_current, err)) return -1;
+  Device& d = g_dev[g_current];
+  cudaError_t e = gonn::launch_replicate_wait(bases_dev, owner, rank, uint64_t(ctrl_offset), slot, epoch,
+                                              ack_value, d.status_dev, d.stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    set_error(err, "replicate_wait: launch failed: %s", cudaGetErrorString(e));
+    return -4;
+  }
+  ++g_stats[3];
+  return finish(d, err, -6, "replicate_wait");
+}
+
 // ---- element-wise family (internal/cgo/metal_bridge_matrix.m:172-543) -------------
 namespace {
 // Equal-shaped binary op.  Order of checks and codes as in the reference:

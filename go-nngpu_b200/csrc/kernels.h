@@ -125,4 +125,25 @@ void launch_softmax(const float* in_or_grad, const float* act, float* out, uint6
 // *out = min(*out, smallest i with b[i] == 0); the caller presets *out to ~0.
 void launch_first_zero(const float* b, uint64_t n, unsigned long long* out, cudaStream_t stream);
 
+// ---- replication of B over NVSwitch (row-sharded product) --------------------------
+// Control words every rank keeps at the same offset of its symmetric buffer.  arrived[s] is
+// the last epoch whose data is complete in slot s of this GPU (written by the owner);
+// ack[r] on the OWNER's GPU is the last epoch whose products rank r has completed.
+struct ReplicaControl {
+  uint32_t arrived[2];
+  uint32_t pad[14];
+  uint32_t ack[16];
+};
+constexpr int kReplicaMaxRanks = 16;
+// `bases` is a device array of each rank's buffer address as this GPU maps it; `mc_dst` the
+// multicast address of the destination.  Both kernels report a wait that ran out in `status`
+// (code 4: the owner waiting for acknowledgements, 5: a rank waiting for the data).
+cudaError_t launch_replicate_send(const void* src, void* mc_dst, uint64_t bytes, void* const* bases,
+                                  int world, int my_rank, uint64_t ctrl_offset, int slot,
+                                  uint32_t epoch, uint32_t ack_needed, GemmStatus* status, int ctas,
+                                  cudaStream_t stream);
+cudaError_t launch_replicate_wait(void* const* bases, int owner, int my_rank, uint64_t ctrl_offset,
+                                  int slot, uint32_t epoch, uint32_t ack_value, GemmStatus* status,
+                                  cudaStream_t stream);
+
 }  // namespace gonn

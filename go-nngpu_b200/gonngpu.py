@@ -88,6 +88,11 @@ SIGNATURES = {
     "gonngpu_convert_f16_device": (_c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_int, _errp]),
     "gonngpu_matmul_f16_static_scratch": (
         _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _vp, _errp]),
+    "gonngpu_replicate_send": (
+        _c_int, [_vp, _vp, _c_long, _vp, _c_int, _c_int, _c_long, _c_int, ctypes.c_uint, ctypes.c_uint,
+                 _c_int, _errp]),
+    "gonngpu_replicate_wait": (
+        _c_int, [_vp, _c_int, _c_int, _c_int, _c_long, _c_int, ctypes.c_uint, ctypes.c_uint, _errp]),
     "gonngpu_linear_backward": (
         _c_int, [_vp, _vp, _vp, _vp, _c_long, _c_long, _c_long, _vp, _vp, _vp, _errp]),
     "gonngpu_column_sum": (_c_int, [_vp, _c_long, _c_long, _vp, _errp]),
@@ -285,6 +290,24 @@ def convert_f16_device(src_ptr, rows, cols, dst_ptr, dst_pitch, mode=FP16_RN):
     err = CError()
     _check(lib().gonngpu_convert_f16_device(_vp(src_ptr), rows, cols, _vp(dst_ptr), dst_pitch, mode,
                                             ctypes.byref(err)), err)
+
+
+def replicate_send(src_ptr, dst_multicast_ptr, nbytes, bases_dev_ptr, world, rank, ctrl_offset, slot,
+                   epoch, ack_needed, ctas=0):
+    """Owner of B: pushes `nbytes` from src to the multicast address of the slot (one copy per
+    GPU of the group through NVSwitch) and publishes `epoch` on every rank."""
+    err = CError()
+    _check(lib().gonngpu_replicate_send(_vp(src_ptr), _vp(dst_multicast_ptr), nbytes, _vp(bases_dev_ptr),
+                                        world, rank, ctrl_offset, slot, epoch, ack_needed, ctas,
+                                        ctypes.byref(err)), err)
+
+
+def replicate_wait(bases_dev_ptr, world, owner, rank, ctrl_offset, slot, epoch, ack_value):
+    """Every rank: acknowledges `ack_value` to the owner, then holds the stream until the slot
+    holds `epoch`."""
+    err = CError()
+    _check(lib().gonngpu_replicate_wait(_vp(bases_dev_ptr), world, owner, rank, ctrl_offset, slot, epoch,
+                                        ack_value, ctypes.byref(err)), err)
 
 
 def matmul_f16_static_scratch(a_ptr, a_shape, b_ptr, b_shape, c_ptr, stream=None):

@@ -241,6 +241,45 @@ GONNGPU_API int gonngpu_gemm_f16_device(const void *a, long aRows, long aCols, l
 GONNGPU_API int gonngpu_convert_f16_device(const float *src, long rows, long cols, void *dst, long dstPitch,
                                int mode, CError *err);
 
+/* Replication of B for the row-sharded MatMul (one process per GPU, A split by
+ * rows, every GPU needs all of B).  The reference has one device and no such
+ * step; these two calls are the NVLink replication the multi-GPU path adds
+ * around gonngpu_gemm_f16_device.
+ *
+ * The ranks share a SYMMETRIC buffer: the same allocation on every GPU, mapped
+ * into every process (`bases_dev` is a DEVICE array of `world` addresses: rank
+ * r's buffer as the calling GPU maps it) and bound to an NVSwitch multicast
+ * address.  It holds two destination slots and, at byte `ctrl_offset`, 128
+ * bytes of control words that must be zero before the first call.  Allocation,
+ * mapping and the multicast binding are the caller's (CUDA virtual-memory API,
+ * or torch.distributed._symmetric_memory as bench.py does).
+ *
+ * gonngpu_replicate_send (owner of B only): copies `bytes` from `src` (device
+ * memory of the current GPU) to `dst_multicast` (the multicast address of the
+ * slot) with multimem.st, so every GPU of the group, the owner included,
+ * receives a copy while the owner's NVLink carries B once; then marks the slot
+ * as holding `epoch` on every rank.  Before writing it waits until every rank
+ * has acknowledged epoch `ack_needed` (pass the last epoch that used this slot,
+ * 0 if none).  `ctas`: thread blocks to use, 0 = one per SM.
+ * gonngpu_replicate_wait (every rank, the owner included, before the product
+ * that reads the slot): tells the owner that all work queued earlier on this
+ * library's stream is complete up to epoch `ack_value` (pass epoch - 1), then
+ * holds the stream until the slot holds `epoch`.
+ * Epochs start at 1 and grow by one per replication; slot = epoch % 2 lets the
+ * owner fill one slot while products still read the other.
+ *
+ * Both are enqueued on the library's stream like every other call.  Their waits
+ * are bounded (1.5 s): a wait that runs out is reported as -6 by this call (blocking
+ * mode) or by gonngpu_synchronize, with status code 4 (owner, acknowledgements) or
+ * 5 (data did not arrive).  Errors: -1 device, -2 NULL pointer, -3 arguments,
+ * -4 launch, -6 execution. */
+GONNGPU_API int gonngpu_replicate_send(const void *src, void *dst_multicast, long bytes,
+                           void *const *bases_dev, int world, int rank, long ctrl_offset, int slot,
+                           unsigned epoch, unsigned ack_needed, int ctas, CError *err);
+GONNGPU_API int gonngpu_replicate_wait(void *const *bases_dev, int world, int owner, int rank,
+                           long ctrl_offset, int slot, unsigned epoch, unsigned ack_value,
+                           CError *err);
+
 /* No counterpart in the reference.  C[M,N] = A[M,K] . B[K,N] on the fp16 path
  * (inputs rounded to fp16, fp32 accumulate, as GONNGPU_FP16_RN) for callers
  * that must not allocate: programs that gave all of HBM to their own arena at
