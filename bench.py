@@ -150,23 +150,31 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def setup_multimem(torch, dist, dev, rank, world, required, ctas=0):
-    """Symmetric buffer for B (two slots + control words) with an NVSwitch multicast address.
-    torch's symmetric-memory allocator does the allocation, the exchange of handles between the
-    processes and the multicast binding; the copies and the signalling are this library's kernels.
+def setup_multimem(torch, dist, dev, rank, world, required, slabs, ctas=0):
+    """Symmetric buffer for B with an NVSwitch multicast address: one channel per column slab
+    (two slots and 128 bytes of control words each).  torch's symmetric-memory allocator does
+    the allocation, the exchange of handles between the processes and the multicast binding;
+    the copies and the signalling are this library's kernels.  The owner's pushes go to a stream
+    of their own, so that slab j+1 travels while slab j is multiplied.
     Returns None (on every rank alike) when the GPUs offer no multicast address, unless
     `required`."""
     from replicate import Replicator, open_symmetric  # go-nngpu_b200/replicate.py
     import gonngpu as g
-    slot_bytes = 2 * K_DIM * N_DIM
+    total = 2 * K_DIM * N_DIM
+    slab_bytes, w = total // slabs, N_DIM // slabs
     res, why = None, ""
     try:
-        buf, hdl, ctrl = open_symmetric(torch, dist, dev, slot_bytes)
-        slots = [buf[i * slot_bytes:(i + 1) * slot_bytes].view(torch.float16).view(K_DIM, N_DIM)
-                 for i in range(2)]
-        rep = Replicator(g, world, rank, 0, int(hdl.buffer_ptrs_dev), int(hdl.multicast_ptr), slot_bytes,
-                         ctrl, ctas)
-        res = {"buf": buf, "hdl": hdl, "rep": rep, "slots": slots}
+        buf, hdl, ctrl = open_symmetric(torch, dist, dev, total)
+        side = torch.cuda.Stream(device=dev, priority=-1)   # placed ahead of queued product grids
+        chans = []
+        for j in range(slabs):
+            off = j * 2 * slab_bytes
+            rep = Replicator(g, world, rank, 0, int(hdl.buffer_ptrs_dev), int(hdl.multicast_ptr), slab_bytes,
+                             ctrl + 128 * j, ctas, data_offset=off, send_stream=side.cuda_stream)
+            views = [buf[rep.slot_offset(i):rep.slot_offset(i) + slab_bytes].view(torch.float16).view(K_DIM, w)
+                     for i in range(2)]
+            chans.append((rep, views))
+        res = {"buf": buf, "hdl": hdl, "chans": chans, "side": side}
     except Exception as e:  # noqa: BLE001 - any failure means "take the NCCL broadcast"
         why = f"{type(e).__name__}: {e}"
     ok = torch.tensor([1 if res is not None else 0], device=dev)
@@ -219,12 +227,13 @@ def run_ours(args, rank, world, local_rank):
         g.convert_f16_device(B32.data_ptr(), K_DIM, N_DIM, B16.data_ptr(), N_DIM)
         stream.synchronize()
 
-        # With several ranks B may travel as `slabs` column slabs: the broadcasts are
-        # queued first, and the product of slab j (its own columns of C) starts as
-        # soon as slab j has arrived, so later broadcasts overlap earlier products.
-        # Measured on 8 GPUs: 2 slabs hide ~50 us of broadcast but the NCCL kernels
-        # then share the SMs with the GEMM (0.41 -> 0.455 ms), no net gain: default 1.
-        slabs = max(1, args.slabs) if world > 1 else 1
+        # With several ranks B travels as `slabs` column slabs: the product of slab j (its own
+        # columns of C) starts as soon as slab j has arrived, so later slabs travel while earlier
+        # ones are multiplied.  Default: 2 slabs over the multicast path (each slab still gives the
+        # 74 CTA pairs whole waves of tiles at 8 GPUs; 4 slabs would not), 1 slab over NCCL, whose
+        # broadcast kernels take SMs from the GEMM (measured on 8 GPUs: no net gain).
+        use_mm = world > 1 and args.bcast in ("auto", "multimem")
+        slabs = (args.slabs if args.slabs > 0 else (2 if use_mm else 1)) if world > 1 else 1
         if args.gemm_ctas:
             assert L.gonngpu_set_gemm_tuning(0, args.gemm_ctas) == 0
         assert N_DIM % (slabs * 256) == 0, "--slabs must leave whole 256-column tiles"
@@ -248,21 +257,29 @@ def run_ours(args, rank, world, local_rank):
         # that the next B can be written while products still read the previous one.
         mm = None
         transport = args.bcast if world > 1 else "none"
-        if world > 1 and slabs == 1 and args.bcast in ("auto", "multimem"):
-            mm = setup_multimem(torch, dist, dev, rank, world, args.bcast == "multimem", args.bcast_ctas)
+        if use_mm:
+            mm = setup_multimem(torch, dist, dev, rank, world, args.bcast == "multimem", slabs,
+                                args.bcast_ctas)
             transport = "multimem" if mm is not None else "broadcast"
-        elif transport == "auto":
-            transport = "broadcast"
 
         def step(events=None):
             if mm is not None:
-                slot = mm["rep"].replicate(B16.data_ptr() if rank == 0 else None)
-                if events is not None:
-                    events[0][0].record(stream)
-                g.gemm_f16_device(A16.data_ptr(), (rows, K_DIM), K_DIM, False, mm["slots"][slot].data_ptr(),
-                                  (K_DIM, N_DIM), N_DIM, False, C.data_ptr(), N_DIM)
-                if events is not None:
-                    events[0][1].record(stream)
+                if rank == 0:
+                    # the pushes of this step start when the stream has reached this step (B of a
+                    # step is not sent ahead of the step), then run beside the products
+                    go = torch.cuda.Event()
+                    go.record(stream)
+                    mm["side"].wait_event(go)
+                for j, (rep, _) in enumerate(mm["chans"]):
+                    rep.send(Bs[j].data_ptr() if rank == 0 else None)
+                for j, (rep, views) in enumerate(mm["chans"]):
+                    slot = rep.wait()
+                    if events is not None:
+                        events[j][0].record(stream)
+                    g.gemm_f16_device(A16.data_ptr(), (rows, K_DIM), K_DIM, False, views[slot].data_ptr(),
+                                      (K_DIM, w), w, False, C.data_ptr() + 4 * j * w, N_DIM)
+                    if events is not None:
+                        events[j][1].record(stream)
                 return
             if two_step:
                 dist.scatter(piece, pieces, src=0)
@@ -280,7 +297,9 @@ def run_ours(args, rank, world, local_rank):
                     events[j][1].record(stream)
 
         def current_b():
-            return mm["slots"][mm["rep"].slot] if mm is not None else torch.cat(Bs, dim=1)
+            if mm is not None:
+                return torch.cat([views[rep.slot] for rep, views in mm["chans"]], dim=1)
+            return torch.cat(Bs, dim=1)
 
         for _ in range(max(args.warmup, 3)):
             step()
@@ -337,7 +356,7 @@ def run_ours(args, rank, world, local_rank):
 
     if rank == 0:
         report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, clocks, launches, check, e2e,
-               transport, replica_ok)
+               transport, replica_ok, slabs)
     if world > 1:
         dist.destroy_process_group()
 
@@ -410,7 +429,7 @@ def traffic_estimate(rows):
 
 
 def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, clocks, launches, check, e2e,
-           transport="none", replica_ok=None):
+           transport="none", replica_ok=None, slabs=1):
     if True:
         peaks = load_peaks()
         timed_s = total_ms * 1e-3
@@ -422,7 +441,7 @@ def report(args, g, world, rows, total_ms, kernel_ms_max, ms_per_step, value, cl
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows_per_gpu": rows, "parallelism": f"row-shard x{world}",
                        "l2": "operands and result (>=384 MiB per GPU) exceed the 126 MB L2",
-                       "b_broadcast_in_step": world > 1, "b_slabs": args.slabs if world > 1 else 1,
+                       "b_broadcast_in_step": world > 1, "b_slabs": slabs,
                        "b_transport": transport, "b_replica_bit_exact": replica_ok},
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
@@ -457,15 +476,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
-    ap.add_argument("--slabs", type=int, default=1,
-                    help="column slabs B is broadcast in when there are several ranks (1, 2, 4 ...)")
+    ap.add_argument("--slabs", type=int, default=0,
+                    help="column slabs B travels in when there are several ranks (1, 2, 4 ...); "
+                         "0 = 2 over the multicast path, 1 over NCCL")
     ap.add_argument("--bcast", default="auto",
                     choices=["auto", "multimem", "broadcast", "scatter_allgather"],
                     help="how B reaches the other ranks inside a step: multimem = this library's "
                          "multicast-store kernel over NVSwitch, broadcast = NCCL; auto takes multimem "
                          "when the GPUs offer a multicast address, else broadcast")
-    ap.add_argument("--bcast-ctas", type=int, default=0,
-                    help="thread blocks of the multimem push (0 = one per SM)")
+    ap.add_argument("--bcast-ctas", type=int, default=32,
+                    help="thread blocks of the multimem push (0 = one per SM; 16 already reach the "
+                         "link rate, and the push shares the GPU with a product)")
     ap.add_argument("--gemm-ctas", type=int, default=0,
                     help="CTAs the GEMM may use (0 = one per SM); fewer leaves SMs to the broadcast kernels")
     ap.add_argument("--m-total", type=int, default=M_TOTAL,

@@ -948,7 +948,7 @@ int gonngpu_convert_f16_device(const float* src, long rows, long cols, void* dst
 // ---- replication of B for the row-sharded product ----------------------------------
 int gonngpu_replicate_send(const void* src, void* dst_multicast, long bytes, void* const* bases_dev,
                            int world, int rank, long ctrl_offset, int slot, unsigned epoch,
-                           unsigned ack_needed, int ctas, CError* err) {
+                           unsigned ack_needed, int ctas, void* stream, CError* err) {
   std::lock_guard<std::recursive_mutex> lk(g_mu);
   if (!src || !dst_multicast || !bases_dev) {
     set_error(err, "replicate_send: NULL pointer.");
@@ -964,15 +964,20 @@ int gonngpu_replicate_send(const void* src, void* dst_multicast, long bytes, voi
   }
   if (ensure_device(g_current, err)) return -1;
   Device& d = g_dev[g_current];
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : d.stream;
   cudaError_t e = gonn::launch_replicate_send(src, dst_multicast, uint64_t(bytes), bases_dev, world, rank,
                                               uint64_t(ctrl_offset), slot, epoch, ack_needed,
-                                              d.status_dev, ctas ? ctas : d.sm_count, d.stream);
+                                              d.status_dev, ctas ? ctas : d.sm_count, s);
   if (e != cudaSuccess) {
     cudaGetLastError();
     set_error(err, "replicate_send: launch failed: %s", cudaGetErrorString(e));
     return -4;
   }
   ++g_stats[3];
+  if (stream && g_blocking && cudaStreamSynchronize(s) != cudaSuccess) {
+    set_error(err, "replicate_send: CUDA error: %s", cudaGetErrorString(cudaGetLastError()));
+    return -6;
+  }
   return finish(d, err, -6, "replicate_send");
 }
 

@@ -138,7 +138,11 @@ replicate_send_kernel(const uint4* __restrict__ src, uint4* mc_dst, uint64_t n16
 __global__ void __launch_bounds__(32)
 replicate_wait_kernel(void* const* __restrict__ bases, int owner, int my_rank, uint64_t ctrl_offset,
                       int slot, uint32_t epoch, uint32_t ack_value, GemmStatus* status) {
-  ptx::grid_dependency_release();
+  // No early release of the next kernel here: the product behind this wait is a persistent
+  // grid that fills every SM, and the one behind that cannot be placed at all.  Scheduled
+  // ahead of time, such a grid waits at the head of the block scheduler's queue and keeps the
+  // owner's push (another stream) from getting SMs while this kernel waits for that push.
+  // The next kernel is therefore released only when this one exits.
   ptx::grid_dependency_wait();  // everything earlier on this stream is complete from here on
   if (threadIdx.x != 0) return;
   ReplicaControl* owners = reinterpret_cast<ReplicaControl*>(static_cast<char*>(bases[owner]) +

@@ -90,7 +90,7 @@ SIGNATURES = {
         _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _vp, _errp]),
     "gonngpu_replicate_send": (
         _c_int, [_vp, _vp, _c_long, _vp, _c_int, _c_int, _c_long, _c_int, ctypes.c_uint, ctypes.c_uint,
-                 _c_int, _errp]),
+                 _c_int, _vp, _errp]),
     "gonngpu_replicate_wait": (
         _c_int, [_vp, _c_int, _c_int, _c_int, _c_long, _c_int, ctypes.c_uint, ctypes.c_uint, _errp]),
     "gonngpu_linear_backward": (
@@ -293,13 +293,14 @@ def convert_f16_device(src_ptr, rows, cols, dst_ptr, dst_pitch, mode=FP16_RN):
 
 
 def replicate_send(src_ptr, dst_multicast_ptr, nbytes, bases_dev_ptr, world, rank, ctrl_offset, slot,
-                   epoch, ack_needed, ctas=0):
+                   epoch, ack_needed, ctas=0, stream=None):
     """Owner of B: pushes `nbytes` from src to the multicast address of the slot (one copy per
-    GPU of the group through NVSwitch) and publishes `epoch` on every rank."""
+    GPU of the group through NVSwitch) and publishes `epoch` on every rank.  `stream`: a
+    cudaStream_t as an int, None = the library's stream."""
     err = CError()
     _check(lib().gonngpu_replicate_send(_vp(src_ptr), _vp(dst_multicast_ptr), nbytes, _vp(bases_dev_ptr),
                                         world, rank, ctrl_offset, slot, epoch, ack_needed, ctas,
-                                        ctypes.byref(err)), err)
+                                        _vp(stream) if stream else None, ctypes.byref(err)), err)
 
 
 def replicate_wait(bases_dev_ptr, world, owner, rank, ctrl_offset, slot, epoch, ack_value):

@@ -23,13 +23,23 @@ to `Replicator` directly.
 
 class Replicator:
     def __init__(self, binding, world, rank, owner, bases_dev, multicast_ptr, slot_bytes, ctrl_offset,
-                 ctas=0):
-        if slot_bytes % 16 or ctrl_offset % 16 or ctrl_offset < 2 * slot_bytes:
-            raise ValueError("slots are multiples of 16 bytes and the control words lie behind them")
+                 ctas=0, data_offset=0, send_stream=None):
+        """`data_offset`: where this channel's two slots begin inside the symmetric buffer (several
+        channels, one per column slab of B, share one buffer; each has its own 128 bytes of
+        control words at `ctrl_offset`).  `send_stream`: cudaStream_t (int) the owner's pushes are
+        enqueued on, None = the library's stream."""
+        if slot_bytes % 16 or ctrl_offset % 16 or data_offset % 16 or \
+                data_offset <= ctrl_offset < data_offset + 2 * slot_bytes:
+            raise ValueError("slots are multiples of 16 bytes and the control words lie outside them")
         self.g, self.world, self.rank, self.owner = binding, world, rank, owner
         self.bases, self.mc = bases_dev, multicast_ptr
         self.slot_bytes, self.ctrl, self.ctas = slot_bytes, ctrl_offset, ctas
+        self.data_offset, self.send_stream = data_offset, send_stream
         self.epoch = 0
+
+    def slot_offset(self, slot):
+        """Byte offset of `slot` inside every rank's symmetric buffer."""
+        return self.data_offset + slot * self.slot_bytes
 
     @property
     def slot(self):
@@ -37,17 +47,30 @@ class Replicator:
         return self.epoch % 2
 
     def replicate(self, src_ptr=None):
-        """One replication, enqueued on the library's stream: the owner pushes the bytes at
-        `src_ptr`; every rank (the owner too) then holds its stream until they have arrived.
-        Returns the slot the following product reads."""
+        """One replication: the owner pushes the bytes at `src_ptr`; every rank (the owner too)
+        then holds the library's stream until they have arrived.  Returns the slot the following
+        product reads."""
+        slot = self.send(src_ptr)
+        self.wait()
+        return slot
+
+    def wait(self):
+        """Second half of `replicate`: acknowledge the previous epoch, wait for the current one."""
+        e = self.epoch
+        self.g.replicate_wait(self.bases, self.world, self.owner, self.rank, self.ctrl, e % 2, e, e - 1)
+        return e % 2
+
+    def send(self, src_ptr=None):
+        """First half of `replicate`: opens the next epoch; on the owner, enqueues the push."""
         self.epoch += 1
         e, slot = self.epoch, self.epoch % 2
         if self.rank == self.owner:
             if src_ptr is None:
+                self.epoch -= 1
                 raise ValueError("the owner passes the source address")
-            self.g.replicate_send(src_ptr, self.mc + slot * self.slot_bytes, self.slot_bytes, self.bases,
-                                  self.world, self.rank, self.ctrl, slot, e, max(e - 2, 0), self.ctas)
-        self.g.replicate_wait(self.bases, self.world, self.owner, self.rank, self.ctrl, slot, e, e - 1)
+            self.g.replicate_send(src_ptr, self.mc + self.slot_offset(slot), self.slot_bytes, self.bases,
+                                  self.world, self.rank, self.ctrl, slot, e, max(e - 2, 0), self.ctas,
+                                  self.send_stream)
         return slot
 
 

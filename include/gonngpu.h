@@ -260,7 +260,14 @@ GONNGPU_API int gonngpu_convert_f16_device(const float *src, long rows, long col
  * receives a copy while the owner's NVLink carries B once; then marks the slot
  * as holding `epoch` on every rank.  Before writing it waits until every rank
  * has acknowledged epoch `ack_needed` (pass the last epoch that used this slot,
- * 0 if none).  `ctas`: thread blocks to use, 0 = one per SM.
+ * 0 if none).  `ctas`: thread blocks to use, 0 = one per SM (16 already reach the
+ * link rate).  `stream`: cudaStream_t to enqueue on, NULL = the library's
+ * stream; on a stream of its own the push runs beside the products of the
+ * library's stream (B in column slabs: slab j+1 travels while slab j is being
+ * multiplied) and needs no ordering against them, because the
+ * acknowledgements already keep it from overwriting a slot that is still read.
+ * Two sends of one GPU must not run at the same time (they share a counter):
+ * keep them on one stream.
  * gonngpu_replicate_wait (every rank, the owner included, before the product
  * that reads the slot): tells the owner that all work queued earlier on this
  * library's stream is complete up to epoch `ack_value` (pass epoch - 1), then
@@ -275,7 +282,7 @@ GONNGPU_API int gonngpu_convert_f16_device(const float *src, long rows, long col
  * -4 launch, -6 execution. */
 GONNGPU_API int gonngpu_replicate_send(const void *src, void *dst_multicast, long bytes,
                            void *const *bases_dev, int world, int rank, long ctrl_offset, int slot,
-                           unsigned epoch, unsigned ack_needed, int ctas, CError *err);
+                           unsigned epoch, unsigned ack_needed, int ctas, void *stream, CError *err);
 GONNGPU_API int gonngpu_replicate_wait(void *const *bases_dev, int world, int owner, int rank,
                            long ctrl_offset, int slot, unsigned epoch, unsigned ack_value,
                            CError *err);

@@ -51,7 +51,11 @@ def main():
     if rank == 0:
         np.savez(os.path.join(out, "inputs.npz"), A=A, epochs=EPOCHS, **{f"B{e}": b for e, b in enumerate(Bs)})
     lo, hi = shard_rows(M, world, rank)
-    rep = Replicator(g, world, rank, 0, int(hdl.buffer_ptrs_dev), int(hdl.multicast_ptr), slot_bytes, ctrl)
+    # the owner's pushes run on a stream of their own, unordered against the products: only the
+    # acknowledgements keep a slot from being overwritten while it is read
+    side = torch.cuda.Stream(device=dev, priority=-1)
+    rep = Replicator(g, world, rank, 0, int(hdl.buffer_ptrs_dev), int(hdl.multicast_ptr), slot_bytes, ctrl,
+                     ctas=16, send_stream=side.cuda_stream)
     slots = [buf[i * slot_bytes:(i + 1) * slot_bytes].view(torch.float16).view(K, N) for i in range(2)]
     bit_exact = True
     with torch.cuda.stream(stream):
@@ -68,6 +72,7 @@ def main():
                               False, Cs[e].data_ptr(), N)
             got[e].copy_(slots[slot])
         stream.synchronize()
+        side.synchronize()
         g.synchronize()          # raises if a bounded wait ran out
         L.gonngpu_set_blocking(1)
         for e in range(EPOCHS):

@@ -23,7 +23,8 @@ class FakeBinding:
     def __init__(self, log):
         self.log = log
 
-    def replicate_send(self, src, dst, nbytes, bases, world, rank, ctrl, slot, epoch, ack_needed, ctas=0):
+    def replicate_send(self, src, dst, nbytes, bases, world, rank, ctrl, slot, epoch, ack_needed, ctas=0,
+                       stream=None):
         self.log.append(("send", rank, slot, epoch, ack_needed, dst, nbytes))
 
     def replicate_wait(self, bases, world, owner, rank, ctrl, slot, epoch, ack_value):
@@ -53,6 +54,21 @@ def test_replicator_sequence_and_slot_safety():
     # slot s at epoch e only when every ack >= e - 2; products of e - 1 read the OTHER slot.
     for e in range(3, 7):
         assert (e - 1) % 2 != e % 2 and (e - 2) % 2 == e % 2
+
+
+def test_replicator_channels_share_a_buffer():
+    """Two column slabs of B: each channel has its own slots and control words."""
+    slab, log = 1 << 16, []
+    chans = [Replicator(FakeBinding(log), 2, 0, 0, 0x1000, 0x9000_0000, slab, 4 * slab + 128 * j,
+                        data_offset=2 * slab * j, send_stream=0x55) for j in range(2)]
+    for rep in chans:
+        rep.send(0xAB00)
+    for rep in chans:
+        rep.wait()
+    sends = [x for x in log if x[0] == "send"]
+    assert [s[5] for s in sends] == [0x9000_0000 + slab, 0x9000_0000 + 3 * slab]   # epoch 1 -> slot 1
+    assert [x[0] for x in log] == ["send", "send", "wait", "wait"]
+    assert chans[1].slot_offset(0) == 2 * slab and chans[1].slot_offset(1) == 3 * slab
 
 
 def test_replicator_rejects_bad_layout():
