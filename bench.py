@@ -7,8 +7,9 @@
 Workload: the row-sharded tall GEMM of the benchmark configurations, fp16
 inputs / fp32 accumulate / fp32 C, M=131072, K=4096, N=4096, A split by rows
 across the N ranks (one process per GPU), B replicated from rank 0 over
-NVLink (NCCL broadcast) inside every step when N > 1.  Inputs are seeded
-synthetic normal(0, 1/sqrt(K)) values.  One "step" is one full product.
+NVLink inside every step when N > 1 (this library's multicast-store kernel
+through NVSwitch, or NCCL's broadcast: --bcast).  Inputs are seeded synthetic
+normal(0, 1/sqrt(K)) values.  One "step" is one full product.
 
 `value` is device-timed with the operands already resident in HBM as fp16;
 `e2e` is the same product through the handle-based C ABI from page-locked host

@@ -24,6 +24,7 @@
 // st.release.sys through plain peer pointers.  A reader takes the flag with
 // ld.acquire.sys.  No multicast LOAD of any kind is issued anywhere in this file.
 #include <cstdint>
+#include <cstdlib>
 
 #include "kernels.h"
 #include "launch.cuh"
@@ -45,10 +46,19 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// WEAK: a plain (weak) multicast store; else relaxed at system scope.  Either way the data
+// stores carry no ordering of their own: the fences before the flag stores order them.
+template <bool WEAK>
 __device__ __forceinline__ void multimem_st_16(void* mc, const uint4& v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc),
-               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
+  if constexpr (WEAK) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x),
+                 "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+  } else {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+  }
 }
 __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
   uint4 v;
@@ -76,6 +86,7 @@ __device__ bool bounded_wait(const uint32_t* word, uint32_t wanted) {
   return false;
 }
 
+template <bool WEAK>
 __global__ void __launch_bounds__(512)
 replicate_send_kernel(const uint4* __restrict__ src, uint4* mc_dst, uint64_t n16,
                       void* const* __restrict__ bases, int world, int my_rank, uint64_t ctrl_offset,
@@ -109,12 +120,12 @@ replicate_send_kernel(const uint4* __restrict__ src, uint4* mc_dst, uint64_t n16
       const uint4 v1 = ld_stream_16(src + i + stride);
       const uint4 v2 = ld_stream_16(src + i + 2 * stride);
       const uint4 v3 = ld_stream_16(src + i + 3 * stride);
-      multimem_st_16(mc_dst + i, v0);
-      multimem_st_16(mc_dst + i + stride, v1);
-      multimem_st_16(mc_dst + i + 2 * stride, v2);
-      multimem_st_16(mc_dst + i + 3 * stride, v3);
+      multimem_st_16<WEAK>(mc_dst + i, v0);
+      multimem_st_16<WEAK>(mc_dst + i + stride, v1);
+      multimem_st_16<WEAK>(mc_dst + i + 2 * stride, v2);
+      multimem_st_16<WEAK>(mc_dst + i + 3 * stride, v3);
     }
-    for (; i < n16; i += stride) multimem_st_16(mc_dst + i, ld_stream_16(src + i));
+    for (; i < n16; i += stride) multimem_st_16<WEAK>(mc_dst + i, ld_stream_16(src + i));
   }
   __syncthreads();
   __shared__ int s_last;
@@ -164,7 +175,13 @@ cudaError_t launch_replicate_send(const void* src, void* mc_dst, uint64_t bytes,
                                   int world, int my_rank, uint64_t ctrl_offset, int slot,
                                   uint32_t epoch, uint32_t ack_needed, GemmStatus* status, int ctas,
                                   cudaStream_t stream) {
-  return launch_kernel(replicate_send_kernel, dim3(unsigned(ctas)), dim3(512), 0, stream,
+  // GONNGPU_REPLICATE_WEAK=1 (read once): weak instead of relaxed.sys multicast stores
+  static const bool weak = [] {
+    const char* e = std::getenv("GONNGPU_REPLICATE_WEAK");
+    return e && e[0] == '1';
+  }();
+  auto kern = weak ? replicate_send_kernel<true> : replicate_send_kernel<false>;
+  return launch_kernel(kern, dim3(unsigned(ctas)), dim3(512), 0, stream,
                        static_cast<const uint4*>(src), static_cast<uint4*>(mc_dst), bytes / 16, bases,
                        world, my_rank, ctrl_offset, slot, epoch, ack_needed, status);
 }
