@@ -151,7 +151,7 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def setup_multimem(torch, dist, dev, rank, world, required, slabs, ctas=0):
+def setup_multimem(torch, dist, dev, rank, world, required, slabs, ctas=0, side_stream=True):
     """Symmetric buffer for B with an NVSwitch multicast address: one channel per column slab
     (two slots and 128 bytes of control words each).  torch's symmetric-memory allocator does
     the allocation, the exchange of handles between the processes and the multicast binding;
@@ -166,12 +166,14 @@ def setup_multimem(torch, dist, dev, rank, world, required, slabs, ctas=0):
     res, why = None, ""
     try:
         buf, hdl, ctrl = open_symmetric(torch, dist, dev, total)
-        side = torch.cuda.Stream(device=dev, priority=-1)   # placed ahead of queued product grids
+        # a stream of its own for the pushes (high priority: placed ahead of queued product grids)
+        side = torch.cuda.Stream(device=dev, priority=-1) if side_stream else None
         chans = []
         for j in range(slabs):
             off = j * 2 * slab_bytes
             rep = Replicator(g, world, rank, 0, int(hdl.buffer_ptrs_dev), int(hdl.multicast_ptr), slab_bytes,
-                             ctrl + 128 * j, ctas, data_offset=off, send_stream=side.cuda_stream)
+                             ctrl + 128 * j, ctas, data_offset=off,
+                             send_stream=side.cuda_stream if side is not None else None)
             views = [buf[rep.slot_offset(i):rep.slot_offset(i) + slab_bytes].view(torch.float16).view(K_DIM, w)
                      for i in range(2)]
             chans.append((rep, views))
@@ -228,13 +230,14 @@ def run_ours(args, rank, world, local_rank):
         g.convert_f16_device(B32.data_ptr(), K_DIM, N_DIM, B16.data_ptr(), N_DIM)
         stream.synchronize()
 
-        # With several ranks B travels as `slabs` column slabs: the product of slab j (its own
+        # With several ranks B may travel as `slabs` column slabs: the product of slab j (its own
         # columns of C) starts as soon as slab j has arrived, so later slabs travel while earlier
-        # ones are multiplied.  Default: 2 slabs over the multicast path (each slab still gives the
-        # 74 CTA pairs whole waves of tiles at 8 GPUs; 4 slabs would not), 1 slab over NCCL, whose
-        # broadcast kernels take SMs from the GEMM (measured on 8 GPUs: no net gain).
+        # ones are multiplied.  Measured on 8 GPUs it loses both ways: NCCL's broadcast kernels
+        # take SMs from the GEMM, and the multicast push of slab j+1, sharing the owner's SMs with
+        # the product of slab j, slows to less than its stand-alone rate (2 slabs 0.553 ms per
+        # step against 0.506 ms with 1).  Default: 1 slab.
         use_mm = world > 1 and args.bcast in ("auto", "multimem")
-        slabs = (args.slabs if args.slabs > 0 else (2 if use_mm else 1)) if world > 1 else 1
+        slabs = max(1, args.slabs) if world > 1 else 1
         if args.gemm_ctas:
             assert L.gonngpu_set_gemm_tuning(0, args.gemm_ctas) == 0
         assert N_DIM % (slabs * 256) == 0, "--slabs must leave whole 256-column tiles"
@@ -260,12 +263,12 @@ def run_ours(args, rank, world, local_rank):
         transport = args.bcast if world > 1 else "none"
         if use_mm:
             mm = setup_multimem(torch, dist, dev, rank, world, args.bcast == "multimem", slabs,
-                                args.bcast_ctas)
+                                args.bcast_ctas, args.push_stream == "side")
             transport = "multimem" if mm is not None else "broadcast"
 
         def step(events=None):
             if mm is not None:
-                if rank == 0:
+                if rank == 0 and mm["side"] is not None:
                     # the pushes of this step start when the stream has reached this step (B of a
                     # step is not sent ahead of the step), then run beside the products
                     go = torch.cuda.Event()
@@ -477,14 +480,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
-    ap.add_argument("--slabs", type=int, default=0,
-                    help="column slabs B travels in when there are several ranks (1, 2, 4 ...); "
-                         "0 = 2 over the multicast path, 1 over NCCL")
+    ap.add_argument("--slabs", type=int, default=1,
+                    help="column slabs B travels in when there are several ranks (1, 2, 4 ...)")
     ap.add_argument("--bcast", default="auto",
                     choices=["auto", "multimem", "broadcast", "scatter_allgather"],
                     help="how B reaches the other ranks inside a step: multimem = this library's "
                          "multicast-store kernel over NVSwitch, broadcast = NCCL; auto takes multimem "
                          "when the GPUs offer a multicast address, else broadcast")
+    ap.add_argument("--push-stream", default="main", choices=["side", "main"],
+                    help="stream of the multicast pushes: the library's, or one of their own (they can "
+                         "then run beside a product; costs an event wait per step, measured 8 us)")
     ap.add_argument("--bcast-ctas", type=int, default=32,
                     help="thread blocks of the multimem push (0 = one per SM; 16 already reach the "
                          "link rate, and the push shares the GPU with a product)")

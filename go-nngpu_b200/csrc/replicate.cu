@@ -175,10 +175,10 @@ cudaError_t launch_replicate_send(const void* src, void* mc_dst, uint64_t bytes,
                                   int world, int my_rank, uint64_t ctrl_offset, int slot,
                                   uint32_t epoch, uint32_t ack_needed, GemmStatus* status, int ctas,
                                   cudaStream_t stream) {
-  // GONNGPU_REPLICATE_WEAK=1 (read once): weak instead of relaxed.sys multicast stores
+  // weak multicast stores; GONNGPU_REPLICATE_WEAK=0 (read once) makes them relaxed.sys
   static const bool weak = [] {
     const char* e = std::getenv("GONNGPU_REPLICATE_WEAK");
-    return e && e[0] == '1';
+    return !(e && e[0] == '0');
   }();
   auto kern = weak ? replicate_send_kernel<true> : replicate_send_kernel<false>;
   return launch_kernel(kern, dim3(unsigned(ctas)), dim3(512), 0, stream,
