@@ -82,6 +82,57 @@ def test_replicator_rejects_bad_layout():
 
 
 @pytest.mark.gpu
+def test_wait_that_nothing_answers_runs_out_and_reports(gpu):
+    """Failure detection without a fault: one GPU, a group of one, an arrival flag that nobody
+    sets.  The wait kernel gives up after its limit (1.5 s), the call returns -6 with the slot,
+    the epoch and the last value seen, the acknowledgement has been written, and the library
+    goes on working.  Then the flag is set and the same wait returns at once."""
+    import time
+    g = gpu
+    L = g.lib()
+    L.gonngpu_set_blocking(1)
+    words = np.zeros(64, np.uint32)                      # control words (first 128 bytes) + spare
+    ctrl = g.Buffer.from_host(words.view(np.float32))
+    ctrl_addr = L.gonngpu_device_address(ctrl.handle)
+    assert ctrl_addr
+    bases = g.Buffer.from_host(np.array([ctrl_addr, 0], np.uint64).view(np.float32))
+    bases_addr = L.gonngpu_device_address(bases.handle)
+    assert bases_addr
+    t0 = time.time()
+    with pytest.raises(g.GonnError) as ei:
+        g.replicate_wait(bases_addr, 1, 0, 0, 0, 1, 7, 6)     # slot 1, epoch 7, acknowledge 6
+    dt = time.time() - t0
+    assert ei.value.code == -6 and "role 5" in ei.value.message
+    assert 1.0 < dt < 20.0
+    assert g.last_kernel_status() == [5, 1, 7, 0]
+    seen = ctrl.retrieve((64,)).view(np.uint32)
+    assert seen[16] == 6 and seen[0] == 0 and seen[1] == 0    # ack[0] written, flags untouched
+    words[1] = 9                                              # a later epoch satisfies the wait too
+    ctrl.upload(words.view(np.float32))
+    t0 = time.time()
+    g.replicate_wait(bases_addr, 1, 0, 0, 0, 1, 7, 6)
+    assert time.time() - t0 < 1.0
+    # the context is intact: a product still matches the oracle
+    from oracle import oracle
+    rng = np.random.default_rng(5)
+    A = rng.standard_normal((96, 40)).astype(np.float32)
+    B = rng.standard_normal((40, 24)).astype(np.float32)
+    a, b = g.Buffer.from_host(A), g.Buffer.from_host(B)
+    c = g.Buffer.from_host(np.zeros((96, 24), np.float32))
+    g.matmul(a, A.shape, b, B.shape, c, (96, 24))
+    assert oracle.rel_frobenius(c.retrieve((96, 24)), oracle.gemm_f64(A, B)) <= 1e-5
+    for x in (a, b, c, ctrl, bases):
+        x.release()
+    # argument checks answer without touching the GPU
+    for bad in [dict(world=0), dict(rank=1), dict(owner=3), dict(slot=2), dict(ctrl=8)]:
+        kw = dict(world=1, owner=0, rank=0, ctrl=0, slot=0)
+        kw.update(bad)
+        with pytest.raises(g.GonnError) as ei:
+            g.replicate_wait(1 << 20, kw["world"], kw["owner"], kw["rank"], kw["ctrl"], kw["slot"], 1, 0)
+        assert ei.value.code == -3
+
+
+@pytest.mark.gpu
 def test_two_gpu_replication_and_sharded_product(tmp_path, gpu):
     if gpu.lib().gonngpu_device_count() < 2:
         pytest.skip("needs two GPUs")
