@@ -1007,6 +1007,59 @@ int gonngpu_replicate_wait(void* const* bases_dev, int world, int owner, int ran
   return finish(d, err, -6, "replicate_wait");
 }
 
+int gonngpu_gemm_f16_sharded(const void* a, long aRows, long aCols, long aPitch, const void* b_src,
+                             long bCols, void* local_base, void* const* bases_dev,
+                             void* multicast_base, int world, int owner, int rank,
+                             long slots_offset, long ctrl_offset, unsigned epoch, float* c, long ldc,
+                             int first_group, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!a || !c || !local_base || !bases_dev || (rank == owner && !b_src)) {
+    set_error(err, "gemm_f16_sharded: NULL pointer (the owner of B passes its source).");
+    return -2;
+  }
+  if (aRows <= 0 || aCols <= 0 || bCols <= 0 || aPitch < aCols || aPitch % 8 || bCols % 8 ||
+      ldc < bCols || aRows >= (1l << 31) || aCols >= (1l << 31) || bCols >= (1l << 31) ||
+      world < 1 || world > gonn::kShardMaxRanks || rank < 0 || rank >= world || owner < 0 ||
+      owner >= world || slots_offset < 0 || slots_offset % 16 || ctrl_offset < 0 || ctrl_offset % 16 ||
+      epoch == 0 || first_group < 0) {
+    set_error(err, "gemm_f16_sharded: bad dimensions (B needs a multiple of 8 columns), pitches, "
+                   "offsets (multiples of 16 bytes), group (1..%d ranks) or epoch (starts at 1).",
+              gonn::kShardMaxRanks);
+    return -3;
+  }
+  const uint64_t slot_bytes = uint64_t(aCols) * uint64_t(bCols) * 2;
+  const uint64_t lo = uint64_t(slots_offset), hi = lo + 2 * slot_bytes;
+  if (uint64_t(ctrl_offset) + sizeof(gonn::ShardControl) > lo && uint64_t(ctrl_offset) < hi) {
+    set_error(err, "gemm_f16_sharded: the control words lie inside the slots.");
+    return -3;
+  }
+  if (ensure_device(g_current, err)) return -1;
+  Device& d = g_dev[g_current];
+  gonn::ShardLink link;
+  link.slot = int(epoch & 1u);
+  link.slot_offset = lo + uint64_t(link.slot) * slot_bytes;
+  link.b_src = b_src;
+  link.slot_multicast = multicast_base ? static_cast<char*>(multicast_base) + link.slot_offset : nullptr;
+  link.bases = bases_dev;
+  link.ctrl_offset = uint64_t(ctrl_offset);
+  link.world = world;
+  link.owner = owner;
+  link.rank = rank;
+  link.epoch = epoch;
+  link.first_group = uint32_t(first_group);
+  const char* msg = gonn::launch_gemm_sharded(uint32_t(aRows), uint32_t(bCols), uint32_t(aCols), a,
+                                              uint64_t(aPitch), static_cast<char*>(local_base) + link.slot_offset,
+                                              c, uint64_t(ldc), link, d.status_dev, d.sm_count, d.stream);
+  if (msg) {
+    cudaGetLastError();
+    set_error(err, "gemm_f16_sharded: %s", msg);
+    return (std::strstr(msg, "pitch") || std::strstr(msg, "aligned") || std::strstr(msg, "bad ")) ? -3 : -4;
+  }
+  ++g_stats[3];
+  ++g_stats[4];
+  return finish(d, err, -6, "gemm_f16_sharded");
+}
+
 // ---- element-wise family (internal/cgo/metal_bridge_matrix.m:172-543) -------------
 namespace {
 // Equal-shaped binary op.  Order of checks and codes as in the reference:

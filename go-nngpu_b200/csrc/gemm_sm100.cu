@@ -36,6 +36,8 @@ constexpr uint32_t SLAB_ROW_BYTES = 128;             // one swizzle row
 constexpr uint32_t A_TILE_BYTES = BLOCK_M * SLAB_ROW_BYTES;  // 16 KiB per plane per k block
 constexpr uint32_t KSTEPS = 4;                       // MMAs (per product) per k block
 constexpr uint32_t NUM_THREADS = 192;
+constexpr uint32_t GATED_THREADS = 256;  // + 2 sender warps (row-sharded product)
+constexpr uint32_t SENDER_WARPS = 2;
 constexpr uint32_t SMEM_LIMIT = 227 * 1024;
 
 // How one operand's k-block tile is fetched by TMA and described to the MMA.
@@ -58,10 +60,27 @@ struct OperandPlan {
   uint32_t kgroup;
 };
 
+// Device-side view of a ShardLink (row-sharded product that replicates B itself).
+struct ShardParams {
+  const uint4* src;      // owner: B in this GPU's memory, `row_chunks` 16-byte chunks per row
+  uint4* mc_dst;         // multicast address of the slot, or null (plain peer stores)
+  void* const* bases;    // every rank's symmetric buffer as this GPU maps it
+  uint64_t slot_offset, ctrl_offset;
+  uint32_t world, owner, rank, slot, epoch, ack_needed;
+  uint32_t slab_tiles;   // column tiles per arrival flag
+  uint32_t num_slabs;
+  uint32_t rows;         // K
+  uint32_t row_chunks;   // 16-byte chunks per row of B
+  uint32_t slab_chunks;  // 16-byte chunks per row of one slab
+};
+
 struct KernelParams {
   OperandPlan a, b;
   uint32_t M, N;
   uint32_t tiles_m, tiles_n, num_tiles, num_kblocks, group_m;
+  // The first `group_m0` row tiles form one group of their own (0 = none): the gated product
+  // sweeps them column slab by column slab while B is still arriving.
+  uint32_t group_m0;
   uint32_t idesc;
   float* C;
   const float* c_in;
@@ -82,15 +101,27 @@ struct KernelParams {
   float* sk_ws;
   uint32_t* sk_count;
   GemmStatus* status;
+  ShardParams sh;
 };
 
 __device__ __forceinline__ void tile_coords(const KernelParams& p, uint32_t t, uint32_t& tm,
                                             uint32_t& tn) {
   // Groups of `group_m` row tiles sweep the columns together so that a wave of
   // CTAs shares A rows and B columns in L2.
+  uint32_t base_m = 0;
+  if (p.group_m0) {
+    const uint32_t first = p.group_m0 * p.tiles_n;
+    if (t < first) {
+      tm = t % p.group_m0;
+      tn = t / p.group_m0;
+      return;
+    }
+    t -= first;
+    base_m = p.group_m0;
+  }
   const uint32_t per_group = p.group_m * p.tiles_n;
   const uint32_t g = t / per_group;
-  const uint32_t first_m = g * p.group_m;
+  const uint32_t first_m = base_m + g * p.group_m;
   const uint32_t gm = min(p.group_m, p.tiles_m - first_m);
   const uint32_t r = t - g * per_group;
   tm = first_m + r % gm;
@@ -412,6 +443,86 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
 }
 
 // ---------------------------------------------------------------------------
+// Row-sharded product: the pieces that move B (see ShardLink in kernels.h).
+__device__ __forceinline__ ShardControl* shard_ctrl(const ShardParams& s, uint32_t rank) {
+  return reinterpret_cast<ShardControl*>(static_cast<char*>(s.bases[rank]) + s.ctrl_offset);
+}
+
+// Sender warps of the owner (warp `wid` of `nwarps`, all CTAs together): B goes out column
+// slab by column slab, each warp taking whole rows of a slab (consecutive lanes, consecutive
+// 16-byte chunks).  After a slab every lane fences at system scope and the warp counts
+// itself in; the warp that completes the count fences again and writes the slab's arrival
+// flag on every rank with st.release.sys.  A reader that took the flag with ld.acquire.sys
+// therefore sees the slab.  No multicast load is issued: only stores use the multicast address.
+__device__ void push_b_slabs(const ShardParams& s, uint32_t wid, uint32_t nwarps, uint32_t lane,
+                             GemmStatus* status) {
+  ShardControl* mine = shard_ctrl(s, s.rank);
+  // the slot may be overwritten only when every rank has finished with the epoch that last used it
+  bool ok = true;
+  if (lane < s.world) ok = ptx::flag_wait(&mine->ack[lane], s.ack_needed, nullptr);
+  if (!__all_sync(0xffffffffu, ok)) {
+    // nothing is written and nothing published: the products' own waits run out and report
+    if (!ok && (atomicOr(&mine->gave_up, 2u) & 2u) == 0u) report(status, 4, lane, s.epoch, s.ack_needed);
+    return;
+  }
+  for (uint32_t slab = 0; slab < s.num_slabs; ++slab) {
+    const uint32_t c0 = slab * s.slab_chunks;
+    const uint32_t width = min(s.slab_chunks, s.row_chunks - c0);
+    for (uint32_t ch = lane; ch < width; ch += 32u) {
+      const uint64_t col = uint64_t(c0) + ch;
+      for (uint32_t row = wid; row < s.rows; row += 4u * nwarps) {
+        uint4 v[4];
+        uint64_t off[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+          const uint32_t r = row + j * nwarps;
+          off[j] = uint64_t(r) * s.row_chunks + col;
+          if (r < s.rows) v[j] = ptx::ld_stream_16(s.src + off[j]);
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+          if (row + j * nwarps >= s.rows) continue;
+          if (s.mc_dst) {
+            ptx::multimem_st_16(s.mc_dst + off[j], v[j]);
+          } else {
+            for (uint32_t r = 0; r < s.world; ++r)
+              reinterpret_cast<uint4*>(static_cast<char*>(s.bases[r]) + s.slot_offset)[off[j]] = v[j];
+          }
+        }
+      }
+    }
+    __threadfence_system();
+    __syncwarp();
+    uint32_t last = 0;
+    if (lane == 0) last = (atomicAdd(&mine->sent[slab], 1u) == nwarps - 1u) ? 1u : 0u;
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      if (lane == 0) mine->sent[slab] = 0;  // zero again for the next launch
+      if (lane < s.world) {
+        __threadfence_system();
+        ptx::st_release_sys(&shard_ctrl(s, lane)->arrived[s.slot][slab], s.epoch);
+      }
+    }
+  }
+}
+
+// Last step of a CTA of the gated product: the CTA that leaves last tells the owner that this
+// rank has finished reading the slot (unless some CTA gave up), and zeroes the scratch words.
+__device__ __forceinline__ void shard_exit(const ShardParams& s, bool gave_up) {
+  ShardControl* mine = shard_ctrl(s, s.rank);
+  if (gave_up) atomicOr(&mine->gave_up, 1u);
+  __threadfence();
+  if (atomicAdd(&mine->exited, 1u) == gridDim.x - 1u) {
+    mine->exited = 0;
+    const uint32_t gave = atomicExch(&mine->gave_up, 0u);
+    if (!gave) {
+      __threadfence_system();
+      ptx::st_release_sys(&shard_ctrl(s, s.owner)->ack[s.rank], s.epoch);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // fp16 kernel for large problems: CTA pairs (cta_group::2).
 //
 // A cluster of two CTAs computes a 256 x BLOCK_N tile.  CTA r of the pair
@@ -431,8 +542,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
 //
 // A stage holds SUB k blocks (each laid out as A tile then B half tile); one
 // barrier round (full wait, commit) therefore covers 4*SUB MMAs.
-template <int BLOCK_N, int STAGES, int SUB>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+//
+// GATED: the row-sharded product that replicates B itself.  Two more warps per CTA (6, 7)
+// push B on the owner; every producer waits for the arrival flag of a tile's column slab
+// before the tile's first load; the last CTA to leave acknowledges the epoch.
+template <int BLOCK_N, int STAGES, int SUB, bool GATED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATED ? GATED_THREADS : NUM_THREADS, 1)
 gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                      const __grid_constant__ CUtensorMap tm_b,
                      const __grid_constant__ KernelParams p) {
@@ -499,11 +614,34 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     // ------------------------------------------------------------ producer
     uint32_t stage = 0, phase = 0;
     bool alive = true;
+    uint32_t slabs_seen = 0;  // GATED: column slabs of B known to have arrived (bit per slab)
     for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs) {
       uint32_t tm, tn;
       tile_coords(p, t, tm, tn);
       const int32_t a_tile = int32_t(tm * 2 + cta_rank);  // in units of 128 rows
       const int32_t b_tile = int32_t(tn * 2 + cta_rank);  // in units of BLOCK_N/2 columns
+      if constexpr (GATED) {
+        const uint32_t slab = tn / p.sh.slab_tiles;
+        if (!((slabs_seen >> slab) & 1u)) {
+          bool here = true;
+          if (lane == 0) {
+            here = ptx::flag_wait(&shard_ctrl(p.sh, p.sh.rank)->arrived[p.sh.slot][slab], p.sh.epoch,
+                                  abort_flag);
+            // the slab was written by another GPU's stores: order the flag's acquire before
+            // this thread's TMA loads of the slab
+            ptx::fence_proxy_async_global();
+          }
+          if (!__all_sync(0xffffffffu, here)) {
+            if (lane == 0) {
+              *abort_flag = 1;
+              report(p.status, 6, slab, t, p.sh.epoch);
+            }
+            alive = false;
+            break;
+          }
+          slabs_seen |= 1u << slab;
+        }
+      }
       for (uint32_t rd = 0; rd < rounds; ++rd) {
         bool ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -598,6 +736,10 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
       }
     }
+  } else if (GATED && warp >= 6) {
+    // ------------------------------------------- sender warps (owner of B only)
+    if (p.sh.rank == p.sh.owner)
+      push_b_slabs(p.sh, blockIdx.x * SENDER_WARPS + (warp - 6u), gridDim.x * SENDER_WARPS, lane, p.status);
   } else {
     // ------------------------------------------------------------ epilogue
     const uint32_t quarter = warp & 3u;
@@ -699,6 +841,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     ptx::tc_fence_after();
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
+  // every load of B this CTA issued has landed and been consumed
+  if (GATED && threadIdx.x == 0) shard_exit(p.sh, *abort_flag != 0u);
 }
 
 // One thread's 32 consecutive accumulator columns of one output row:
@@ -2011,7 +2155,7 @@ TileChoice choose_tiles(Kind kind, uint32_t M, uint32_t N, uint32_t K, int sms, 
   return best;
 }
 
-template <int BLOCK_N, int SUB>
+template <int BLOCK_N, int SUB, bool GATED = false>
 const char* launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, const KernelParams& kp,
                                 uint32_t pairs, cudaStream_t stream) {
   constexpr uint32_t stage = SUB * (A_TILE_BYTES + (BLOCK_N / 2) * SLAB_ROW_BYTES);
@@ -2019,7 +2163,7 @@ const char* launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, co
   constexpr int STAGES = (avail / stage) > 8 ? 8 : int(avail / stage);
   constexpr uint32_t smem = STAGES * stage + 1024 + 256;
   static_assert(STAGES >= 1 && smem <= SMEM_LIMIT, "pair kernel shared memory");
-  auto kern = gemm_f16_pair_kernel<BLOCK_N, STAGES, SUB>;
+  auto kern = gemm_f16_pair_kernel<BLOCK_N, STAGES, SUB, GATED>;
   static bool attr_done_dev[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -2030,7 +2174,8 @@ const char* launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, co
     attr_done_dev[dev & 63] = true;
   }
   // (cluster size 2 is compiled in)
-  if (launch_kernel(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ma, mb, kp) != cudaSuccess) {
+  if (launch_kernel(kern, dim3(2 * pairs), dim3(GATED ? GATED_THREADS : NUM_THREADS), smem, stream, ma,
+                    mb, kp) != cudaSuccess) {
     cudaGetLastError();
     return "GEMM pair kernel launch failed";
   }
@@ -2064,7 +2209,7 @@ const char* launch_pair512(const CUtensorMap& ma, const CUtensorMap& mb, const C
 // fp16 GEMM on CTA pairs: (256 or 512) x bn tiles, one cluster of two CTAs per tile.
 const char* launch_gemm_pair(uint32_t M, uint32_t N, uint32_t K, int bn, bool tall,
                              const GemmOperand& A, const GemmOperand& B, KernelParams kp,
-                             int sm_count, int max_ctas, cudaStream_t stream) {
+                             int sm_count, int max_ctas, cudaStream_t stream, bool gated = false) {
   const uint32_t block_k = 64;
   const uint32_t tile_m = tall ? 4 * BLOCK_M : 2 * BLOCK_M;
   kp.a = plan_operand(false, A.mn_major, BLOCK_M, block_k);
@@ -2074,17 +2219,14 @@ const char* launch_gemm_pair(uint32_t M, uint32_t N, uint32_t K, int bn, bool ta
   kp.num_tiles = kp.tiles_m * kp.tiles_n;
   kp.num_kblocks = (K + block_k - 1) / block_k;
   kp.group_m = tall ? 4 : 8;
+  kp.group_m0 = gated ? std::min(kp.group_m0, kp.tiles_m) : 0u;
   kp.idesc = ptx::make_idesc(0u, A.mn_major, B.mn_major, 2 * BLOCK_M, uint32_t(bn));
   CUtensorMap ma, mb;
   std::memset(&ma, 0, sizeof(ma));
   std::memset(&mb, 0, sizeof(mb));
   const uint32_t a_box_rows = A.mn_major ? block_k : BLOCK_M;
   const uint32_t b_box_rows = B.mn_major ? block_k : uint32_t(bn / 2);
-  static const int sub = [] {
-    const char* e = std::getenv("GONNGPU_PAIR_SUB");  // experiment switch: k blocks per stage
-    return e ? std::atoi(e) : 2;
-  }();
-  const uint32_t kgroup = (!tall && sub != 1) ? 2u : 0u;
+  const uint32_t kgroup = tall ? 0u : 2u;  // the 256-row kernel's stage holds two k blocks
   if (!make_operand_maps(false, A, A.mn_major ? M : K, A.mn_major ? K : M, a_box_rows, kp.a, &ma, nullptr, kgroup) ||
       !make_operand_maps(false, B, B.mn_major ? N : K, B.mn_major ? K : N, b_box_rows, kp.b, &mb, nullptr, kgroup))
     return "cuTensorMapEncodeTiled failed";
@@ -2112,11 +2254,9 @@ const char* launch_gemm_pair(uint32_t M, uint32_t N, uint32_t K, int bn, bool ta
     }
     return launch_pair512(ma, mb, mc, kp, pairs, stream);
   }
-  if (bn == 256)
-    return sub == 1 ? launch_pair_variant<256, 1>(ma, mb, kp, pairs, stream)
-                    : launch_pair_variant<256, 2>(ma, mb, kp, pairs, stream);
-  return sub == 1 ? launch_pair_variant<128, 1>(ma, mb, kp, pairs, stream)
-                  : launch_pair_variant<128, 2>(ma, mb, kp, pairs, stream);
+  if (gated) return launch_pair_variant<256, 2, true>(ma, mb, kp, pairs, stream);
+  if (bn == 256) return launch_pair_variant<256, 2>(ma, mb, kp, pairs, stream);
+  return launch_pair_variant<128, 2>(ma, mb, kp, pairs, stream);
 }
 
 // fp32-accurate GEMM on CTA pairs (256 x 256 tiles).
@@ -2306,6 +2446,64 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
       default: return launch_variant<1, 32>(maps, kp, grid, stream);
     }
   }
+}
+
+// Row-sharded product with the replication of B inside the kernel (see kernels.h).
+const char* launch_gemm_sharded(uint32_t M, uint32_t N, uint32_t K, const void* a, uint64_t a_pitch,
+                                const void* b_slot, float* C, uint64_t ldc, const ShardLink& link,
+                                GemmStatus* status, int sm_count, cudaStream_t stream) {
+  if (M == 0 || N == 0 || K == 0) return "GEMM dimensions must be positive";
+  if (N % 8 || a_pitch % 8) return "operand pitch must be a multiple of 16 bytes";
+  if (reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(b_slot) % 16 ||
+      reinterpret_cast<uintptr_t>(link.b_src) % 16 || reinterpret_cast<uintptr_t>(link.slot_multicast) % 16 ||
+      link.slot_offset % 16)
+    return "operand planes must be 16-byte aligned";
+  if (link.world < 1 || link.world > kShardMaxRanks || link.rank < 0 || link.rank >= link.world ||
+      link.owner < 0 || link.owner >= link.world || (link.slot != 0 && link.slot != 1) || !link.bases)
+    return "bad rank, owner, slot or group size";
+  if (link.rank == link.owner && !link.b_src) return "the owner passes the source of B";
+  constexpr uint32_t bn = 256;
+  GemmOperand A, B;
+  A.plane0 = a;
+  A.pitch = a_pitch;
+  A.mn_major = false;
+  B.plane0 = b_slot;
+  B.pitch = N;
+  B.mn_major = true;
+  KernelParams kp{};
+  kp.M = M;
+  kp.N = N;
+  kp.C = C;
+  kp.ldc = ldc;
+  kp.alpha = 1.f;
+  kp.act = ACT_NONE;
+  kp.vec_store = (ldc % 4 == 0) && (reinterpret_cast<uintptr_t>(C) % 16 == 0);
+  kp.status = status;
+  kp.splits = 1;
+  const uint32_t tiles_n = (N + bn - 1) / bn;
+  ShardParams& sh = kp.sh;
+  sh.src = static_cast<const uint4*>(link.b_src);
+  sh.mc_dst = static_cast<uint4*>(link.slot_multicast);
+  sh.bases = link.bases;
+  sh.slot_offset = link.slot_offset;
+  sh.ctrl_offset = link.ctrl_offset;
+  sh.world = uint32_t(link.world);
+  sh.owner = uint32_t(link.owner);
+  sh.rank = uint32_t(link.rank);
+  sh.slot = uint32_t(link.slot);
+  sh.epoch = link.epoch;
+  sh.ack_needed = link.epoch > 2u ? link.epoch - 2u : 0u;
+  sh.slab_tiles = (tiles_n + kShardMaxSlabs - 1) / kShardMaxSlabs;
+  sh.num_slabs = (tiles_n + sh.slab_tiles - 1) / sh.slab_tiles;
+  sh.rows = K;
+  sh.row_chunks = N / 8;
+  sh.slab_chunks = sh.slab_tiles * bn / 8;
+  // Row tiles swept slab by slab while B arrives.  A slab must be consumed no faster than the
+  // next one arrives: the group's tiles of one slab have to last as long as a slab's transfer.
+  // Measured on B200s: a 2 MiB slab takes about 4.5 us to reach 2 GPUs and 7 to 11 us to reach
+  // 8, a wave of 74 tiles with K = 4096 about 28 us; larger groups only cost L2 reuse of A.
+  kp.group_m0 = link.first_group ? link.first_group : (link.world <= 2 ? 16u : link.world <= 4 ? 24u : 32u);
+  return launch_gemm_pair(M, N, K, int(bn), false, A, B, kp, sm_count, 0, stream, true);
 }
 
 }  // namespace gonn

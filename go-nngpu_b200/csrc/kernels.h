@@ -146,4 +146,49 @@ cudaError_t launch_replicate_wait(void* const* bases, int owner, int my_rank, ui
                                   int slot, uint32_t epoch, uint32_t ack_value, GemmStatus* status,
                                   cudaStream_t stream);
 
+// ---- row-sharded product with the replication of B inside the kernel ---------------
+// Every rank multiplies its rows of A by the whole of B, which only the owner holds.  The
+// product kernel itself moves B: on the owner, two extra warps per CTA push B, column slab by
+// column slab, into the current slot of every rank's symmetric buffer (multimem.st through
+// NVSwitch, or plain peer stores when the group has no multicast address) and publish one
+// arrival flag per slab; on every rank the TMA producer of a tile waits for the flag of the
+// tile's slab before its first load, and the last CTA to leave acknowledges the epoch to the
+// owner, which may then overwrite the slot two epochs later.  Tiles are visited slab by slab
+// while B is arriving, so the product runs beside the transfer instead of behind it.
+constexpr int kShardMaxSlabs = 32;
+constexpr int kShardMaxRanks = 16;
+// Control words at the same offset of every rank's symmetric buffer, zero before the first
+// epoch.  `sent`, `exited` and `gave_up` are scratch of the local kernel and zero between
+// launches.
+struct ShardControl {
+  uint32_t arrived[2][kShardMaxSlabs];  // [slot][slab]: last epoch complete on this GPU
+  uint32_t ack[kShardMaxRanks];         // on the owner: last epoch rank r has finished reading
+  uint32_t sent[kShardMaxSlabs];        // owner: sender warps done with the slab
+  uint32_t exited;                      // CTAs of the running product that have left
+  uint32_t gave_up;                     // a CTA of the running product gave up
+  uint32_t pad[14];
+};
+static_assert(sizeof(ShardControl) == 512, "ShardControl layout");
+
+struct ShardLink {
+  const void* b_src = nullptr;   // owner only: B [K, N] fp16, dense, in this GPU's memory
+  void* slot_multicast = nullptr;  // multicast address of the slot, or null: plain peer stores
+  void* const* bases = nullptr;  // device array: rank r's symmetric buffer as this GPU maps it
+  uint64_t slot_offset = 0;      // byte offset of the slot inside every rank's buffer
+  uint64_t ctrl_offset = 0;      // byte offset of the ShardControl inside every rank's buffer
+  int world = 1, owner = 0, rank = 0;
+  int slot = 0;
+  uint32_t epoch = 1;
+  uint32_t first_group = 0;      // row tiles (256 rows) visited slab by slab; 0 = choose
+};
+
+// C[M,N] = A[M,K] . B[K,N] for this rank's rows, fp16 operands, fp32 accumulate; `b_slot` is
+// this rank's own copy of the slot (what the tensor map reads).  N must be a multiple of 8.
+// Status codes beyond the GEMM's: 4 the owner ran out waiting for acknowledgements, 6 a
+// producer ran out waiting for a slab of B.
+const char* launch_gemm_sharded(uint32_t M, uint32_t N, uint32_t K, const void* a, uint64_t a_pitch,
+                                const void* b_slot, float* C, uint64_t ldc, const ShardLink& link,
+                                GemmStatus* status, int sm_count, cudaStream_t stream);
+
+
 }  // namespace gonn

@@ -359,6 +359,56 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t cta_mask)
       ::"r"(bar), "h"(cta_mask) : "memory");
 }
 
+// ------------------------------------------------- system-scope flags, multicast stores
+// Flags that another GPU writes or reads (arrival of replicated data, acknowledgements).
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Orders this thread's earlier generic-proxy accesses to global memory (the acquire load of a
+// flag) before its later asynchronous-proxy accesses (TMA loads of the data the flag covers).
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+// 16 bytes to a multicast address: NVSwitch delivers a copy to every GPU bound to it.  A weak
+// store carries no ordering of its own; a system-scope fence before the flag store orders it.
+__device__ __forceinline__ void multimem_st_16(void* mc, const uint4& v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// 16 bytes that are read once: no L1 allocation.
+__device__ __forceinline__ uint4 ld_stream_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// Epochs only grow; the comparison tolerates wrap-around of the 32-bit counter.
+__device__ __forceinline__ bool epoch_reached(uint32_t seen, uint32_t wanted) {
+  return int32_t(seen - wanted) >= 0;
+}
+// Polls `word` until it has reached `wanted`; false when the limit (1.5 s and an iteration
+// cap) ran out or `abort_flag` (may be null) was raised.
+__device__ __forceinline__ bool flag_wait(const uint32_t* word, uint32_t wanted,
+                                          volatile uint32_t* abort_flag) {
+  for (uint32_t i = 0; i < 1024; ++i)
+    if (epoch_reached(ld_acquire_sys(word), wanted)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 0; i < (1u << 24); ++i) {
+    if (epoch_reached(ld_acquire_sys(word), wanted)) return true;
+    if (abort_flag && *abort_flag) return false;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    __nanosleep(100);
+  }
+  return false;
+}
+
 // ------------------------------------------------- descriptors (host+device)
 // Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle:
 //   [0,14) start address >> 4, [16,30) leading byte offset >> 4,

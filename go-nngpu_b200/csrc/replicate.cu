@@ -18,7 +18,7 @@
 // that runs out writes a status word and the kernel returns; there is no trap
 // and no endless spin.
 //
-// Memory order.  Data stores are relaxed multimem stores.  Each block then runs
+// Memory order.  Data stores are weak multimem stores.  Each block then runs
 // __syncthreads, one thread fences at system scope and counts the block in; the
 // thread that sees the count complete fences again and writes the flags with
 // st.release.sys through plain peer pointers.  A reader takes the flag with
@@ -33,60 +33,15 @@
 namespace gonn {
 namespace {
 
-constexpr uint64_t kReplicaWaitNs = 1500ull * 1000 * 1000;
-
-// Blocks that have finished their share of the current send (zero between launches).
+// Blocks that have finished their share of the current send, and whether one of them gave
+// up waiting for the acknowledgements (both zero between launches).  One send at a time per
+// GPU: two sends of one GPU must be ordered on one stream.
 __device__ unsigned int g_send_blocks_done;
+__device__ unsigned int g_send_gave_up;
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// WEAK: a plain (weak) multicast store; else relaxed at system scope.  Either way the data
-// stores carry no ordering of their own: the fences before the flag stores order them.
-template <bool WEAK>
-__device__ __forceinline__ void multimem_st_16(void* mc, const uint4& v) {
-  if constexpr (WEAK) {
-    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x),
-                 "r"(v.y), "r"(v.z), "r"(v.w)
-                 : "memory");
-  } else {
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc),
-                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                 : "memory");
-  }
-}
-__device__ __forceinline__ uint4 ld_stream_16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
+using ptx::ld_acquire_sys;
+using ptx::st_release_sys;
 
-// Epochs only grow; the comparison tolerates wrap-around of the 32-bit counter.
-__device__ __forceinline__ bool reached(uint32_t seen, uint32_t wanted) {
-  return int32_t(seen - wanted) >= 0;
-}
-
-// Polls `word` until it has reached `wanted`; false when the limit ran out.
-__device__ bool bounded_wait(const uint32_t* word, uint32_t wanted) {
-  for (uint32_t i = 0; i < 4096; ++i)
-    if (reached(ld_acquire_sys(word), wanted)) return true;
-  const uint64_t t0 = ptx::globaltimer_ns();
-  for (uint32_t i = 0; i < (1u << 24); ++i) {
-    if (reached(ld_acquire_sys(word), wanted)) return true;
-    if (ptx::globaltimer_ns() - t0 > kReplicaWaitNs) return false;
-    __nanosleep(128);
-  }
-  return false;
-}
-
-template <bool WEAK>
 __global__ void __launch_bounds__(512)
 replicate_send_kernel(const uint4* __restrict__ src, uint4* mc_dst, uint64_t n16,
                       void* const* __restrict__ bases, int world, int my_rank, uint64_t ctrl_offset,
@@ -101,13 +56,15 @@ replicate_send_kernel(const uint4* __restrict__ src, uint4* mc_dst, uint64_t n16
   if (threadIdx.x < world) {
     const ReplicaControl* mine = reinterpret_cast<const ReplicaControl*>(
         static_cast<const char*>(bases[my_rank]) + ctrl_offset);
-    if (!bounded_wait(&mine->ack[threadIdx.x], ack_needed)) {
+    if (!ptx::flag_wait(&mine->ack[threadIdx.x], ack_needed, nullptr)) {
       s_ok = 0;
-      if (blockIdx.x == 0) {
-        status->code = 4;
+      // whichever block runs out first reports; any block that ran out keeps the epoch
+      // from being published, so that no receiver multiplies a partly written slot
+      if (atomicOr(&g_send_gave_up, 1u) == 0u) {
         status->where = threadIdx.x;
         status->tile = epoch;
         status->kblock = ack_needed;
+        status->code = 4;
       }
     }
   }
@@ -116,16 +73,16 @@ replicate_send_kernel(const uint4* __restrict__ src, uint4* mc_dst, uint64_t n16
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
     uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     for (; i + 3 * stride < n16; i += 4 * stride) {
-      const uint4 v0 = ld_stream_16(src + i);
-      const uint4 v1 = ld_stream_16(src + i + stride);
-      const uint4 v2 = ld_stream_16(src + i + 2 * stride);
-      const uint4 v3 = ld_stream_16(src + i + 3 * stride);
-      multimem_st_16<WEAK>(mc_dst + i, v0);
-      multimem_st_16<WEAK>(mc_dst + i + stride, v1);
-      multimem_st_16<WEAK>(mc_dst + i + 2 * stride, v2);
-      multimem_st_16<WEAK>(mc_dst + i + 3 * stride, v3);
+      const uint4 v0 = ptx::ld_stream_16(src + i);
+      const uint4 v1 = ptx::ld_stream_16(src + i + stride);
+      const uint4 v2 = ptx::ld_stream_16(src + i + 2 * stride);
+      const uint4 v3 = ptx::ld_stream_16(src + i + 3 * stride);
+      ptx::multimem_st_16(mc_dst + i, v0);
+      ptx::multimem_st_16(mc_dst + i + stride, v1);
+      ptx::multimem_st_16(mc_dst + i + 2 * stride, v2);
+      ptx::multimem_st_16(mc_dst + i + 3 * stride, v3);
     }
-    for (; i < n16; i += stride) multimem_st_16<WEAK>(mc_dst + i, ld_stream_16(src + i));
+    for (; i < n16; i += stride) ptx::multimem_st_16(mc_dst + i, ptx::ld_stream_16(src + i));
   }
   __syncthreads();
   __shared__ int s_last;
@@ -135,9 +92,14 @@ replicate_send_kernel(const uint4* __restrict__ src, uint4* mc_dst, uint64_t n16
   }
   __syncthreads();
   if (s_last) {
-    if (threadIdx.x == 0) g_send_blocks_done = 0;
+    __shared__ unsigned int s_gave_up;
+    if (threadIdx.x == 0) {
+      g_send_blocks_done = 0;
+      s_gave_up = atomicExch(&g_send_gave_up, 0u);
+    }
+    __syncthreads();
     // a send that gave up publishes nothing: the receivers' waits run out and report too
-    if (s_ok && threadIdx.x < world) {
+    if (!s_gave_up && threadIdx.x < world) {
       __threadfence_system();
       ReplicaControl* theirs = reinterpret_cast<ReplicaControl*>(
           static_cast<char*>(bases[threadIdx.x]) + ctrl_offset);
@@ -161,7 +123,7 @@ replicate_wait_kernel(void* const* __restrict__ bases, int owner, int my_rank, u
   st_release_sys(&owners->ack[my_rank], ack_value);
   const ReplicaControl* mine = reinterpret_cast<const ReplicaControl*>(
       static_cast<const char*>(bases[my_rank]) + ctrl_offset);
-  if (!bounded_wait(&mine->arrived[slot], epoch)) {
+  if (!ptx::flag_wait(&mine->arrived[slot], epoch, nullptr)) {
     status->code = 5;
     status->where = uint32_t(slot);
     status->tile = epoch;
@@ -175,13 +137,7 @@ cudaError_t launch_replicate_send(const void* src, void* mc_dst, uint64_t bytes,
                                   int world, int my_rank, uint64_t ctrl_offset, int slot,
                                   uint32_t epoch, uint32_t ack_needed, GemmStatus* status, int ctas,
                                   cudaStream_t stream) {
-  // weak multicast stores; GONNGPU_REPLICATE_WEAK=0 (read once) makes them relaxed.sys
-  static const bool weak = [] {
-    const char* e = std::getenv("GONNGPU_REPLICATE_WEAK");
-    return !(e && e[0] == '0');
-  }();
-  auto kern = weak ? replicate_send_kernel<true> : replicate_send_kernel<false>;
-  return launch_kernel(kern, dim3(unsigned(ctas)), dim3(512), 0, stream,
+  return launch_kernel(replicate_send_kernel, dim3(unsigned(ctas)), dim3(512), 0, stream,
                        static_cast<const uint4*>(src), static_cast<uint4*>(mc_dst), bytes / 16, bases,
                        world, my_rank, ctrl_offset, slot, epoch, ack_needed, status);
 }

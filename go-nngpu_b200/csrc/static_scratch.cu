@@ -17,8 +17,12 @@
 // Set-up: `g_scratch` as named in host code is only a host-side stand-in for
 // the symbol, not a device address.  The first call on each device (with that
 // device current) asks the runtime for the real address with
-// cudaGetSymbolAddress and caches it; make that first call before any stream
-// capture is begun.
+// cudaGetSymbolAddress and caches it.  With CUDA's lazy module loading that
+// first call is also when the driver loads this library's kernels and the
+// array, taking device memory of its own for them.  A caller that reserves the
+// rest of HBM for itself therefore makes one small warm-up call per device
+// first (or sets CUDA_MODULE_LOADING=EAGER), and makes it before any stream
+// capture is begun.  Every call ends with cudaStreamSynchronize on its stream.
 //
 // Sharing: all calls use the same array and it keeps the previous call's
 // contents.  Nothing in it has to start at zero except the kernel's status

@@ -93,6 +93,9 @@ SIGNATURES = {
                  _c_int, _vp, _errp]),
     "gonngpu_replicate_wait": (
         _c_int, [_vp, _c_int, _c_int, _c_int, _c_long, _c_int, ctypes.c_uint, ctypes.c_uint, _errp]),
+    "gonngpu_gemm_f16_sharded": (
+        _c_int, [_vp, _c_long, _c_long, _c_long, _vp, _c_long, _vp, _vp, _vp, _c_int, _c_int, _c_int,
+                 _c_long, _c_long, ctypes.c_uint, _vp, _c_long, _c_int, _errp]),
     "gonngpu_linear_backward": (
         _c_int, [_vp, _vp, _vp, _vp, _c_long, _c_long, _c_long, _vp, _vp, _vp, _errp]),
     "gonngpu_column_sum": (_c_int, [_vp, _c_long, _c_long, _vp, _errp]),
@@ -309,6 +312,16 @@ def replicate_wait(bases_dev_ptr, world, owner, rank, ctrl_offset, slot, epoch, 
     err = CError()
     _check(lib().gonngpu_replicate_wait(_vp(bases_dev_ptr), world, owner, rank, ctrl_offset, slot, epoch,
                                         ack_value, ctypes.byref(err)), err)
+
+
+def gemm_f16_sharded(a_ptr, a_shape, a_pitch, b_src_ptr, b_cols, local_base, bases_dev_ptr, multicast_base,
+                     world, owner, rank, slots_offset, ctrl_offset, epoch, c_ptr, ldc, first_group=0):
+    """One rank's share of the row-sharded product; B travels inside the kernel."""
+    err = CError()
+    _check(lib().gonngpu_gemm_f16_sharded(
+        _vp(a_ptr), a_shape[0], a_shape[1], a_pitch, _vp(b_src_ptr) if b_src_ptr else None, b_cols,
+        _vp(local_base), _vp(bases_dev_ptr), _vp(multicast_base) if multicast_base else None, world, owner,
+        rank, slots_offset, ctrl_offset, epoch, _vp(c_ptr), ldc, first_group, ctypes.byref(err)), err)
 
 
 def matmul_f16_static_scratch(a_ptr, a_shape, b_ptr, b_shape, c_ptr, stream=None):

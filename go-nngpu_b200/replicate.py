@@ -74,14 +74,50 @@ class Replicator:
         return slot
 
 
-def open_symmetric(torch, dist, dev, slot_bytes):
+class ShardedProduct:
+    """The row-sharded product whose kernel replicates B itself (`gonngpu_gemm_f16_sharded`):
+    keeps the epoch, which every rank advances by one per step, and the addresses of the
+    symmetric buffer (two slots of B at offset 0, the control words behind them)."""
+
+    def __init__(self, binding, world, rank, owner, local_base, bases_dev, multicast_base, k, n,
+                 first_group=0):
+        if n % 8:
+            raise ValueError("B needs a multiple of 8 columns")
+        self.g, self.world, self.rank, self.owner = binding, world, rank, owner
+        self.local_base, self.bases, self.mc = local_base, bases_dev, multicast_base
+        self.k, self.n, self.first_group = k, n, first_group
+        self.slot_bytes = 2 * k * n
+        self.ctrl = 2 * self.slot_bytes
+        self.epoch = 0
+
+    @property
+    def slot(self):
+        """Slot that holds the most recent epoch's B."""
+        return self.epoch % 2
+
+    def slot_offset(self, slot):
+        return slot * self.slot_bytes
+
+    def step(self, a_ptr, rows, a_pitch, c_ptr, ldc, b_src_ptr=None):
+        """Enqueues this rank's product of the next epoch; the owner passes where B lies."""
+        if self.rank == self.owner and not b_src_ptr:
+            raise ValueError("the owner passes the source address")
+        self.epoch += 1
+        self.g.gemm_f16_sharded(a_ptr, (rows, self.k), a_pitch, b_src_ptr if self.rank == self.owner else None,
+                                self.n, self.local_base, self.bases, self.mc, self.world, self.owner,
+                                self.rank, 0, self.ctrl, self.epoch, c_ptr, ldc, self.first_group)
+        return self.epoch % 2
+
+
+def open_symmetric(torch, dist, dev, slot_bytes, require_multicast=True):
     """Allocates the symmetric buffer (two slots + one 4 KiB page of control words, zeroed) with
     torch's symmetric-memory allocator and returns (buffer, handle, ctrl_offset).  Raises when the
-    group has no multicast address (no NVSwitch, or the driver refuses the binding)."""
+    group has no multicast address (no NVSwitch, or the driver refuses the binding), unless
+    `require_multicast` is False (the handle's multicast_ptr is then 0)."""
     import torch.distributed._symmetric_memory as symm
     buf = symm.empty(2 * slot_bytes + 4096, dtype=torch.uint8, device=dev)
     hdl = symm.rendezvous(buf, dist.group.WORLD)
-    if not int(hdl.multicast_ptr):
+    if require_multicast and not int(hdl.multicast_ptr):
         raise RuntimeError("no multicast address for the group")
     buf.zero_()
     return buf, hdl, 2 * slot_bytes

@@ -287,6 +287,42 @@ GONNGPU_API int gonngpu_replicate_wait(void *const *bases_dev, int world, int ow
                            long ctrl_offset, int slot, unsigned epoch, unsigned ack_value,
                            CError *err);
 
+/* The row-sharded MatMul with the replication of B INSIDE the product kernel: one
+ * launch per rank and step, nothing else on the stream.  No counterpart in the
+ * reference (one device); it is the multi-GPU form of matrix.MatMul
+ * (gpu/matrix/matrix.go:53-105) for a tall A split by rows.
+ *
+ * Rank `rank` computes C[aRows, bCols] = A . B for its own rows of A (fp16,
+ * [aRows, aCols], pitch aPitch elements) with B [aCols, bCols] (fp16, dense, bCols
+ * a multiple of 8) that only rank `owner` holds, at `b_src` in its own memory
+ * (NULL on the other ranks).  The ranks share a symmetric buffer as for
+ * gonngpu_replicate_send: `local_base` is this rank's own mapping of it,
+ * `bases_dev` the device array of every rank's mapping, `multicast_base` its
+ * NVSwitch multicast address (NULL: the owner writes every rank's copy with plain
+ * peer stores instead).  At `slots_offset` it holds two slots of aCols*bCols*2
+ * bytes, at `ctrl_offset` 512 bytes of control words, zero before epoch 1.
+ *
+ * On the owner two extra warps of every CTA push B into slot epoch % 2 of every
+ * rank, 256-column slab by slab, and raise one arrival flag per slab; on every
+ * rank a tile's loads wait for the flag of its slab, and the first `first_group`
+ * 256-row tiles (0 = chosen from the group size) are visited slab by slab, so the
+ * product runs while B is still arriving.  The last CTA to leave acknowledges the
+ * epoch to the owner, which overwrites a slot only when every rank has
+ * acknowledged the epoch that used it before (epoch - 2).  Every rank calls this
+ * once per step with the same epoch: 1, 2, 3 ...  The kernels read B from their
+ * own GPU's memory only.
+ *
+ * Enqueued on the library's stream.  Every wait is bounded (1.5 s); one that ran
+ * out is reported as -6 (blocking mode) or by gonngpu_synchronize, with status
+ * code 4 (owner: acknowledgements missing) or 6 (a slab of B did not arrive;
+ * where = slab, tile, k block = epoch); no acknowledgement is then sent.
+ * Errors: -1 device, -2 NULL pointer, -3 arguments, -4 kernel set-up, -6 execution. */
+GONNGPU_API int gonngpu_gemm_f16_sharded(const void *a, long aRows, long aCols, long aPitch,
+                             const void *b_src, long bCols, void *local_base,
+                             void *const *bases_dev, void *multicast_base, int world, int owner,
+                             int rank, long slots_offset, long ctrl_offset, unsigned epoch, float *c,
+                             long ldc, int first_group, CError *err);
+
 /* No counterpart in the reference.  C[M,N] = A[M,K] . B[K,N] on the fp16 path
  * (inputs rounded to fp16, fp32 accumulate, as GONNGPU_FP16_RN) for callers
  * that must not allocate: programs that gave all of HBM to their own arena at
@@ -296,10 +332,14 @@ GONNGPU_API int gonngpu_replicate_wait(void *const *bases_dev, int world, int ow
  * live in a fixed array inside the library, GONNGPU_STATIC_SCRATCH_BYTES of HBM
  * on every GPU that loads it.  Operands whose planes (rows x columns padded to
  * 64, 2 bytes each, A and B together) exceed that are refused with -3.
- * `stream` is the cudaStream_t to run on (NULL: the default stream); the call
- * returns after the work finished.  The first call on a device looks up the
- * array's address: make it before any stream capture.  All calls share the
- * array, so calls that overlap on the GPU race; serialise them.
+ * `stream` is the cudaStream_t to run on (NULL: the default stream); every call
+ * waits for its work with cudaStreamSynchronize before it returns.  The first
+ * call on a device does the set-up: it looks up the array's address and makes
+ * CUDA load the kernels, for which the driver itself takes device memory.  Make
+ * one small warm-up call per device first: before the arena takes the rest of
+ * HBM and before any stream capture is begun (or start the process with
+ * CUDA_MODULE_LOADING=EAGER).  All calls share the array, so calls that overlap
+ * on the GPU race; serialise them.
  * Errors: -1 device, -2 NULL pointer, -3 dimensions or size, -4 kernel set-up,
  * -6 execution. */
 #define GONNGPU_STATIC_SCRATCH_BYTES (32l << 20)

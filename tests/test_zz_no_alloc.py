@@ -5,13 +5,27 @@ that reserved all of HBM for its own arena, or a latency-critical loop - by
 keeping the fp16 operand planes in a fixed array inside the library.  The test
 drives it through the C ABI twice in a row (the second call reuses the array
 with other shapes, so stale contents would show) and compares each result with
-the ordinary allocating entry point on the same inputs.  This file sorts last
-so that a failure here cannot hide the other tests' results.
+the ordinary allocating entry point on the same inputs and with the float64
+oracle; the device's free memory, as the driver reports it, must not shrink
+across the two calls (after one warm-up call, which is when CUDA loads the
+kernels).  This file sorts last so that a failure here cannot hide the other
+tests' results.
 """
 import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
+
+
+def _free_bytes():
+    """Free device memory as the driver reports it (cudaMemGetInfo)."""
+    try:
+        from cuda.bindings import runtime as rt
+    except ImportError:
+        from cuda import cudart as rt
+    err, free, _total = rt.cudaMemGetInfo()
+    assert int(err) == 0, err
+    return int(free)
 
 
 def _ordinary(gpu, A, B):
@@ -25,6 +39,7 @@ def _ordinary(gpu, A, B):
 
 
 def test_static_scratch_matmul_matches_allocating_entry_twice(gpu):
+    from oracle import oracle
     rng = np.random.default_rng(99)
     # inputs and outputs are allocated up front, outside the calls under test
     shapes = [((700, 520), (520, 900)), ((129, 65), (65, 257))]
@@ -35,16 +50,24 @@ def test_static_scratch_matmul_matches_allocating_entry_twice(gpu):
         a, b = gpu.Buffer.from_host(A), gpu.Buffer.from_host(B)
         c = gpu.Buffer.empty(sa[0] * sb[1] * 4)
         bufs.append((A, B, a, b, c, a.device_address(), b.device_address(), c.device_address()))
+    # the warm-up a caller makes once per device (set-up; CUDA loads each kernel at its first use)
+    for (A, B, a, b, c, pa, pb, pc) in bufs:
+        gpu.matmul_f16_static_scratch(pa, A.shape, pb, B.shape, pc)
+        c.upload(np.zeros((A.shape[0], B.shape[1]), np.float32))   # the checked results come from the calls below
     hbm_before = gpu.stats()["hbm_bytes"]
-    got = []
+    free_before = _free_bytes()
     for (A, B, a, b, c, pa, pb, pc) in bufs:           # two calls in a row
         gpu.matmul_f16_static_scratch(pa, A.shape, pb, B.shape, pc)
-        got.append(c.retrieve((A.shape[0], B.shape[1])))
-    assert gpu.stats()["hbm_bytes"] == hbm_before      # the library's allocator was not used
-    for (A, B, *_), C in zip(bufs, got):
+    assert _free_bytes() >= free_before                # nothing was taken from the device
+    assert gpu.stats()["hbm_bytes"] == hbm_before      # nor through the library's own allocator
+    for (A, B, a, b, c, *_) in bufs:
+        C = c.retrieve((A.shape[0], B.shape[1]))
         ref = _ordinary(gpu, A, B)
         err = np.linalg.norm(C.astype(np.float64) - ref) / np.linalg.norm(ref.astype(np.float64))
-        assert err <= 2e-5, err                         # same tolerance as the fp16-path tests
+        assert err <= 2e-5, err                         # against the existing entry point
+        exact = oracle.gemm_f64(A.astype(np.float16).astype(np.float32), B.astype(np.float16).astype(np.float32))
+        assert oracle.rel_frobenius(C, exact) <= 1e-2   # fp16-path tolerance against the oracle
+        assert oracle.rel_frobenius(C, exact) <= 1e-5   # (fp32 accumulation of exact fp16 products)
     for (_, _, a, b, c, *_) in bufs:
         for x in (a, b, c):
             x.release()
