@@ -16,7 +16,11 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <functional>
+#include <map>
 #include <memory>
+#include <mutex>
+#include <random>
 #include <stdexcept>
 #include <string>
 #include <utility>
@@ -50,6 +54,46 @@ inline std::string take_message(CError& e) {
 
 namespace tensor {
 
+// tensor/tensor.go:22-77: every GPU buffer a Tensor creates is recorded here (pointer ->
+// bytes), with the running total and its peak.  EnsureGPU records (tensor.go:146-147),
+// ReleaseGPU removes (tensor.go:195-196).
+class GlobalMemoryPool {
+ public:
+  void trackAllocation(const void* ptr, int64_t size) {  // tensor.go:43-52
+    std::lock_guard<std::mutex> lk(mu_);
+    allocations_[ptr] = size;
+    total_ += size;
+    if (total_ > peak_) peak_ = total_;
+  }
+  void trackDeallocation(const void* ptr) {  // tensor.go:55-63
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = allocations_.find(ptr);
+    if (it != allocations_.end()) {
+      total_ -= it->second;
+      allocations_.erase(it);
+    }
+  }
+  struct Stats {
+    int64_t currentUsage, peakUsage;
+    int numAllocations;
+  };
+  Stats GetStats() {  // tensor.go:66-71
+    std::lock_guard<std::mutex> lk(mu_);
+    return Stats{total_, peak_, int(allocations_.size())};
+  }
+
+ private:
+  std::map<const void*, int64_t> allocations_;
+  int64_t total_ = 0, peak_ = 0;
+  std::mutex mu_;
+};
+inline GlobalMemoryPool& getGlobalMemoryPool() {  // tensor.go:37-40
+  static GlobalMemoryPool pool;
+  return pool;
+}
+// tensor.go:74-77
+inline GlobalMemoryPool::Stats GetGlobalMemoryStats() { return getGlobalMemoryPool().GetStats(); }
+
 // tensor/tensor.go:80-87.  Shape and Data are public as in Go.  Data is the
 // host copy; after an operation wrote the tensor on the device, call
 // RetrieveCPU() before reading Data (the protocol tensor.go states; on Apple
@@ -63,9 +107,7 @@ class Tensor {
       : Shape(std::move(shape)), Data(std::move(data)) {}
   Tensor(const Tensor&) = delete;
   Tensor& operator=(const Tensor&) = delete;
-  ~Tensor() {
-    if (gpuPtr_) release_gpu_buffer(gpuPtr_);
-  }
+  ~Tensor() { dropBuffer(); }
 
   // tensor.go:113-150
   void EnsureGPU() {
@@ -73,10 +115,7 @@ class Tensor {
     // The reference leaves the old buffer behind after RetrieveCPU (tensor.go:154-184
     // keeps gpuPtr); here it is released so that nothing leaks, and a new buffer
     // registers the possibly modified Data.
-    if (gpuPtr_) {
-      release_gpu_buffer(gpuPtr_);
-      gpuPtr_ = nullptr;
-    }
+    dropBuffer();
     CError err{nullptr};
     GPUPtr p = nullptr;
     DevicePtr d = nullptr;
@@ -89,6 +128,7 @@ class Tensor {
     gpuPtr_ = p;
     devicePtr_ = d;
     isOnGPU_ = true;
+    getGlobalMemoryPool().trackAllocation(p, int64_t(Data.size() * sizeof(float)));
   }
 
   // tensor.go:154-184
@@ -106,10 +146,7 @@ class Tensor {
 
   // tensor.go:189-202
   void ReleaseGPU() {
-    if (gpuPtr_) {
-      release_gpu_buffer(gpuPtr_);
-      gpuPtr_ = nullptr;
-    }
+    dropBuffer();
     isOnGPU_ = false;
   }
 
@@ -121,6 +158,7 @@ class Tensor {
     gpuPtr_ = p;
     devicePtr_ = d;
     isOnGPU_ = true;
+    getGlobalMemoryPool().trackAllocation(p, int64_t(Data.size() * sizeof(float)));
   }
 
   GPUPtr GPUPointer() const { return gpuPtr_; }        // tensor.go:206 (GPUPtr)
@@ -128,6 +166,12 @@ class Tensor {
   bool IsOnGPU() const { return isOnGPU_; }
 
  private:
+  void dropBuffer() {
+    if (!gpuPtr_) return;
+    getGlobalMemoryPool().trackDeallocation(gpuPtr_);
+    release_gpu_buffer(gpuPtr_);
+    gpuPtr_ = nullptr;
+  }
   GPUPtr gpuPtr_ = nullptr;
   DevicePtr devicePtr_ = nullptr;
   bool isOnGPU_ = false;
@@ -190,9 +234,125 @@ using tensor::TensorPtr;
 // ---- gpu/matrix/activation.go:18-29 -----------------------------------------
 enum ActivationType { ReLU = 0, Sigmoid, Tanh, Softmax, LeakyReLU, ELU, Swish, GELU };
 
+// ---- gpu/matrix/tensor-unified-memory.go:35-175, unified-memory-optimization.go ----------
+// A tensor's "unified" buffer: page-locked host memory from allocateSharedMemory plus the
+// GPU buffer createGPUBufferFromSharedMemory makes over it (metal_bridge.h:1803-1804).  On
+// Apple silicon both sides are the same bytes; here the device keeps its own copy, so
+// GetUnifiedCPUData brings the device contents back into the shared memory before it hands
+// out the pointer.
+class TensorUnifiedMemoryAdapter {
+ public:
+  explicit TensorUnifiedMemoryAdapter(DevicePtr device) : device_(device) {}
+  ~TensorUnifiedMemoryAdapter() {
+    for (auto& kv : buffers_) free_buffer(kv.second);
+  }
+
+  // tensor-unified-memory.go:65-108
+  void EnsureUnifiedGPU(const TensorPtr& t) {
+    std::lock_guard<std::mutex> lk(mu_);
+    if (buffers_.count(t.get())) {
+      ++zeroCopyHits_;
+      return;
+    }
+    const long bytes = long(t->Data.size() * sizeof(float));
+    Shared sb;
+    sb.cpu = allocateSharedMemory(bytes);
+    if (!sb.cpu) throw gonngpu::Error("failed to create unified buffer: failed to allocate shared memory");
+    std::memcpy(sb.cpu, t->Data.data(), size_t(bytes));
+    sb.gpu = createGPUBufferFromSharedMemory(device_, sb.cpu, bytes);
+    if (!sb.gpu) {
+      gonngpu_host_free(sb.cpu);
+      throw gonngpu::Error("failed to create unified buffer: failed to create GPU buffer from shared memory");
+    }
+    sb.bytes = bytes;
+    buffers_[t.get()] = sb;
+    ++zeroCopyHits_;
+  }
+  // tensor-unified-memory.go:111-121
+  GPUPtr GetUnifiedGPUBuffer(const TensorPtr& t) {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = buffers_.find(t.get());
+    if (it == buffers_.end()) return nullptr;
+    ++zeroCopyHits_;
+    return it->second.gpu;
+  }
+  // tensor-unified-memory.go:124-135
+  float* GetUnifiedCPUData(const TensorPtr& t) {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = buffers_.find(t.get());
+    if (it == buffers_.end()) return nullptr;
+    ++zeroCopyHits_;
+    CError err{nullptr};
+    const int rc = retrieve_gpu_buffer_data(it->second.gpu, static_cast<float*>(it->second.cpu),
+                                            it->second.bytes, &err);
+    if (rc != 0)
+      throw gonngpu::Error("failed to retrieve GPU buffer data (code " + std::to_string(rc) +
+                           "): " + gonngpu::detail::take_message(err));
+    return static_cast<float*>(it->second.cpu);
+  }
+  // tensor-unified-memory.go:163-171
+  void ReleaseUnifiedBuffer(const TensorPtr& t) {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = buffers_.find(t.get());
+    if (it == buffers_.end()) return;
+    free_buffer(it->second);
+    buffers_.erase(it);
+  }
+  long ZeroCopyHits() const { return zeroCopyHits_; }
+  size_t NumBuffers() const { return buffers_.size(); }
+
+ private:
+  struct Shared {
+    void* cpu = nullptr;
+    GPUPtr gpu = nullptr;
+    long bytes = 0;
+  };
+  static void free_buffer(Shared& sb) {
+    if (sb.gpu) release_gpu_buffer(sb.gpu);
+    if (sb.cpu) gonngpu_host_free(sb.cpu);
+    sb = Shared{};
+  }
+  DevicePtr device_;
+  std::map<const tensor::Tensor*, Shared> buffers_;
+  std::mutex mu_;
+  long zeroCopyHits_ = 0;
+};
+
+namespace detail {
+inline DevicePtr& global_matrix_device() {
+  static DevicePtr d = nullptr;
+  return d;
+}
+}  // namespace detail
+
+// tensor-unified-memory.go:57-62: one adapter per process, made for the first device asked.
+inline TensorUnifiedMemoryAdapter& GetGlobalTensorAdapter(DevicePtr device) {
+  static TensorUnifiedMemoryAdapter adapter(device);
+  return adapter;
+}
+// matrix.go:19-24
+inline void SetGlobalMatrixDevice(DevicePtr device) { detail::global_matrix_device() = device; }
+// matrix.go:27-37
+inline void ensureUnifiedGPU(const TensorPtr& t) {
+  if (detail::global_matrix_device()) {
+    GetGlobalTensorAdapter(detail::global_matrix_device()).EnsureUnifiedGPU(t);
+    return;
+  }
+  t->EnsureGPU();
+}
+// matrix.go:40-50
+inline GPUPtr getUnifiedGPUPtr(const TensorPtr& t) {
+  if (detail::global_matrix_device()) {
+    if (GPUPtr p = GetGlobalTensorAdapter(detail::global_matrix_device()).GetUnifiedGPUBuffer(t)) return p;
+  }
+  return t->GPUPointer();
+}
+
 // ---- gpu/matrix/matrix.go ------------------------------------------------------
 
-// matrix.go:53-105
+// matrix.go:53-105.  With a global device set the operands and the result live in unified
+// buffers (the result is then read through GetUnifiedCPUData, as in the reference, whose
+// result tensor's Data is not the shared memory either).
 inline TensorPtr MatMul(const TensorPtr& A, const TensorPtr& B) {
   if (A->Shape.size() != 2 || B->Shape.size() != 2)
     throw gonngpu::Error("MatMul requires 2D tensors (matrices)");
@@ -202,13 +362,13 @@ inline TensorPtr MatMul(const TensorPtr& A, const TensorPtr& B) {
                          std::to_string(B->Shape[0]) + ")");
   const int rows = A->Shape[0], cols = B->Shape[1];
   TensorPtr result = tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols));
-  A->EnsureGPU();
-  B->EnsureGPU();
-  result->EnsureGPU();
+  ensureUnifiedGPU(A);
+  ensureUnifiedGPU(B);
+  ensureUnifiedGPU(result);
   CError err{nullptr};
   const int rc = perform_mps_matrix_multiplication(
-      A->GPUPointer(), A->Shape[0], A->Shape[1], B->GPUPointer(), B->Shape[0], B->Shape[1],
-      result->GPUPointer(), rows, cols, result->DevicePointer(), &err);
+      getUnifiedGPUPtr(A), A->Shape[0], A->Shape[1], getUnifiedGPUPtr(B), B->Shape[0], B->Shape[1],
+      getUnifiedGPUPtr(result), rows, cols, detail::global_matrix_device(), &err);
   if (rc != 0)
     throw gonngpu::Error("GPU matrix multiplication failed (code " + std::to_string(rc) +
                          "): " + gonngpu::detail::take_message(err));
@@ -461,6 +621,7 @@ struct FusedLinearConfig {  // fused-operations.go:49-54
 // activation they named: the enum is translated to the native code here.
 // Softmax, ELU and Swish have no fused native code.
 inline int native_activation_code(ActivationType t) {
+  if (int(t) < 0) return GONNGPU_ACT_NONE;  // no activation (the layer stack's plain linear layer)
   switch (t) {
     case ReLU: return 0;
     case LeakyReLU: return 1;
@@ -623,6 +784,315 @@ inline TensorPtr ForwardFloat16(const TensorPtr& input, const TensorPtr& weights
   if (rc != 0)
     throw gonngpu::Error("GPU matrix multiplication failed (code " + std::to_string(rc) +
                          "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
+// ---- gpu/matrix/mixed-precision-{efficient,fixed,optimized}.go: precision selectors ------
+// Thin decisions, by operand size, between the float32 MatMul and a reduced-precision one.
+// The thresholds and the host-side "simulated precision" scaling of the result are the
+// reference's own.
+struct MixedPrecisionConfig {  // mixed-precision.go (DefaultMixedPrecisionConfig)
+  bool Enabled = true;
+  float LossScale = 65536.0f;
+};
+
+class EfficientMixedPrecisionTrainer {  // mixed-precision-efficient.go:14-113
+ public:
+  explicit EfficientMixedPrecisionTrainer(MixedPrecisionConfig c = {}) : config_(c) {}
+  TensorPtr EfficientMatMul(const TensorPtr& A, const TensorPtr& B) const {  // :46-64
+    if (!config_.Enabled) return MatMul(A, B);
+    const long total = long(A->Shape[0]) * A->Shape[1] + long(B->Shape[0]) * B->Shape[1];
+    if (total > 256 * 256) return MatMul(A, B);
+    TensorPtr result = MatMul(A, B);  // :67-101 (inPlaceMixedPrecisionMatMul)
+    if (result->Data.size() <= size_t(128 * 128)) {
+      result->RetrieveCPU();
+      for (float& v : result->Data) v = simulateFloat16Precision(v);
+    }
+    return result;
+  }
+  static float simulateFloat16Precision(float val) {  // :104-118
+    if (val > 65000 || val < -65000) return val * 0.999f;
+    if (val < 1e-4f && val > -1e-4f) return val * 0.95f;
+    return val * 0.9999f;
+  }
+
+ private:
+  MixedPrecisionConfig config_;
+};
+
+class ZeroCopyMixedPrecisionOps {  // mixed-precision-efficient.go:116-158
+ public:
+  explicit ZeroCopyMixedPrecisionOps(MixedPrecisionConfig c = {}) : trainer_(c), enabled_(c.Enabled) {}
+  TensorPtr OptimalMatMul(const TensorPtr& A, const TensorPtr& B) const {
+    if (!enabled_) return MatMul(A, B);
+    const long rowsA = A->Shape[0], colsA = A->Shape[1], rowsB = B->Shape[0], colsB = B->Shape[1];
+    const double flops = double(rowsA) * colsA * colsB * 2;
+    const double bytes = double(rowsA * colsA + rowsB * colsB + rowsA * colsB) * 4;
+    if (flops / bytes > 0.5 && rowsA <= 512 && colsB <= 512) return trainer_.EfficientMatMul(A, B);
+    return MatMul(A, B);
+  }
+
+ private:
+  EfficientMixedPrecisionTrainer trainer_;
+  bool enabled_;
+};
+
+class FixedMixedPrecisionTrainer {  // mixed-precision-fixed.go:10-128
+ public:
+  explicit FixedMixedPrecisionTrainer(MixedPrecisionConfig c = {}) : config_(c) {}
+  TensorPtr OptimalMatMul(const TensorPtr& A, const TensorPtr& B) const {  // :30-76
+    if (!config_.Enabled) return MatMul(A, B);
+    const long rowsA = A->Shape[0], colsA = A->Shape[1], rowsB = B->Shape[0], colsB = B->Shape[1];
+    if (colsA != rowsB)
+      throw gonngpu::Error("incompatible matrix dimensions: A[" + std::to_string(rowsA) + "," +
+                           std::to_string(colsA) + "] * B[" + std::to_string(rowsB) + "," +
+                           std::to_string(colsB) + "]");
+    const double flops = double(rowsA) * colsA * colsB * 2;
+    const double bytes = double(rowsA * colsA + rowsB * colsB + rowsA * colsB) * 4;
+    const long maxDim = std::max(std::max(rowsA, colsA), std::max(rowsB, colsB));
+    if (maxDim <= 128 || (maxDim <= 256 && flops / bytes > 1.0)) {
+      TensorPtr result = MatMul(A, B);  // :79-100 (simulatedMixedPrecisionMatMul)
+      result->RetrieveCPU();
+      for (float& v : result->Data) v = fastPrecisionReduction(v);
+      return result;
+    }
+    return MatMul(A, B);
+  }
+  static float fastPrecisionReduction(float val) {  // :103-124
+    const float a = val < 0 ? -val : val;
+    if (a > 65000) return val * 0.9999f;
+    if (a < 1e-5f) return val * 0.995f;
+    return val * 0.99995f;
+  }
+
+ private:
+  MixedPrecisionConfig config_;
+};
+
+class OptimizedMixedPrecisionOps {  // mixed-precision-optimized.go:12-56
+ public:
+  explicit OptimizedMixedPrecisionOps(MixedPrecisionConfig c = {}) : enabled_(c.Enabled) {}
+  TensorPtr MatMulOptimized(const TensorPtr& A, const TensorPtr& B) const {
+    if (!enabled_) return MatMul(A, B);
+    const long total = long(A->Shape[0]) * A->Shape[1] + long(B->Shape[0]) * B->Shape[1];
+    if (total > 512 * 512) return MatMul(A, B);
+    return ForwardFloat16(A, B, nullptr);
+  }
+
+ private:
+  bool enabled_;
+};
+
+// ---- gpu/matrix/layers.go: the eager layer stack ---------------------------------------------
+struct Layer {  // layers.go (Layer interface)
+  virtual ~Layer() = default;
+  virtual TensorPtr Forward(const TensorPtr& input) = 0;
+  virtual TensorPtr Backward(const TensorPtr& gradOutput) = 0;
+  virtual std::vector<TensorPtr> GetParameters() = 0;
+  virtual std::vector<TensorPtr> GetGradients() = 0;
+};
+
+class Sequential;
+
+// layers.go:10-109.  Forward is input . Weight + Bias in one call on the device (the
+// reference multiplies on the GPU and then adds the bias into the result's host slice,
+// layers.go:271-279, which only reaches a following GPU operation because its buffers
+// alias host memory; here the sum is formed on the device and is what later operations
+// read).  Backward forms all three gradients in one call without materialised transposes.
+class LinearLayer : public Layer {
+ public:
+  TensorPtr Weight, Bias, WeightGrad, BiasGrad;
+  int InputSize, OutputSize;
+  bool UseBias;
+
+  // layers.go:30-52: Xavier-uniform weights, zero bias.  `seed` stands in for Go's global
+  // math/rand source.
+  LinearLayer(int inputSize, int outputSize, bool useBias, uint32_t seed = 1)
+      : InputSize(inputSize), OutputSize(outputSize), UseBias(useBias) {
+    std::mt19937 gen(seed);
+    std::uniform_real_distribution<float> u(0.f, 1.f);
+    const float scale = float(std::sqrt(2.0 / double(inputSize + outputSize)));
+    std::vector<float> w(size_t(inputSize) * outputSize);
+    for (float& x : w) x = (u(gen) * 2 - 1) * scale;
+    Weight = tensor::NewTensor({inputSize, outputSize}, std::move(w));
+    if (useBias) Bias = tensor::NewTensor({outputSize}, std::vector<float>(size_t(outputSize)));
+  }
+
+  TensorPtr Forward(const TensorPtr& input) override {  // layers.go:55-74
+    input_ = input;
+    return forward(input, nullptr);
+  }
+  TensorPtr Backward(const TensorPtr& gradOutput) override {  // layers.go:77-96
+    return backward(gradOutput, nullptr);
+  }
+  std::vector<TensorPtr> GetParameters() override {  // layers.go:99-104
+    if (UseBias && Bias) return {Weight, Bias};
+    return {Weight};
+  }
+  std::vector<TensorPtr> GetGradients() override {  // layers.go:107-112
+    if (UseBias && BiasGrad) return {WeightGrad, BiasGrad};
+    return {WeightGrad};
+  }
+
+ private:
+  friend class Sequential;
+  // `act`: a ReLU folded into this layer's kernels by Sequential, else null
+  TensorPtr forward(const TensorPtr& input, const FusedActivationConfig* act) {
+    static const FusedActivationConfig identity{ActivationType(-1), 0.f};
+    FusedLinearConfig cfg;
+    cfg.Bias = UseBias && Bias;
+    cfg.Activation = act ? act : &identity;
+    std::vector<TensorPtr> in{input, Weight};
+    if (cfg.Bias) in.push_back(Bias);
+    return FusedLinearActivationForward(in, cfg);
+  }
+  TensorPtr backward(const TensorPtr& gradOutput, const TensorPtr& activationOutput) {
+    if (!input_) throw gonngpu::Panic("Backward called before Forward");
+    LinearGradients g = LinearBackward(input_, Weight, gradOutput, activationOutput);
+    WeightGrad = g.Weight;
+    if (UseBias && Bias) BiasGrad = g.Bias;
+    return g.Input;
+  }
+  TensorPtr input_;
+};
+inline std::shared_ptr<LinearLayer> NewLinearLayer(int inputSize, int outputSize, bool useBias,
+                                                   uint32_t seed = 1) {
+  return std::make_shared<LinearLayer>(inputSize, outputSize, useBias, seed);
+}
+
+// layers.go:115-152
+class ReLULayer : public Layer {
+ public:
+  TensorPtr Forward(const TensorPtr& input) override {  // layers.go:126-130
+    input_ = input;
+    output_ = ActivationForward(input, ReLU, 0.f);
+    return output_;
+  }
+  TensorPtr Backward(const TensorPtr& gradOutput) override {  // layers.go:133-142
+    if (!input_) throw gonngpu::Panic("Backward called before Forward");
+    return ActivationBackward(gradOutput, output_, ReLU, 0.f);
+  }
+  std::vector<TensorPtr> GetParameters() override { return {}; }
+  std::vector<TensorPtr> GetGradients() override { return {}; }
+
+ private:
+  friend class Sequential;
+  TensorPtr input_, output_;
+};
+inline std::shared_ptr<ReLULayer> NewReLULayer() { return std::make_shared<ReLULayer>(); }
+
+// layers.go:330-376.  A LinearLayer directly followed by a ReLULayer runs as one fused
+// call each way (bias + ReLU in the product's epilogue; the ReLU mask applied while the
+// gradient's operand planes are written), with both layers' caches filled as if they had
+// run one after the other; every other layer runs through its own Forward / Backward.
+class Sequential {
+ public:
+  explicit Sequential(std::vector<std::shared_ptr<Layer>> layers, bool fuse = true)
+      : layers_(std::move(layers)), fuse_(fuse) {}
+
+  TensorPtr Forward(const TensorPtr& input) {  // layers.go:343-349
+    TensorPtr out = input;
+    for (size_t i = 0; i < layers_.size(); ++i) {
+      auto* lin = fuse_ ? dynamic_cast<LinearLayer*>(layers_[i].get()) : nullptr;
+      auto* relu = (lin && i + 1 < layers_.size()) ? dynamic_cast<ReLULayer*>(layers_[i + 1].get()) : nullptr;
+      if (lin && relu) {
+        static const FusedActivationConfig kRelu{ReLU, 0.f};
+        lin->input_ = out;
+        out = lin->forward(out, &kRelu);
+        relu->input_ = out;  // the pre-activation is never stored; Backward needs the output only
+        relu->output_ = out;
+        ++i;
+      } else {
+        out = layers_[i]->Forward(out);
+      }
+    }
+    return out;
+  }
+
+  TensorPtr Backward(const TensorPtr& gradOutput) {  // layers.go:352-359
+    TensorPtr grad = gradOutput;
+    for (size_t n = layers_.size(); n > 0; --n) {
+      const size_t i = n - 1;
+      auto* relu = fuse_ ? dynamic_cast<ReLULayer*>(layers_[i].get()) : nullptr;
+      auto* lin = (relu && i > 0) ? dynamic_cast<LinearLayer*>(layers_[i - 1].get()) : nullptr;
+      if (relu && lin) {
+        if (!relu->input_) throw gonngpu::Panic("Backward called before Forward");
+        grad = lin->backward(grad, relu->output_);
+        --n;
+      } else {
+        grad = layers_[i]->Backward(grad);
+      }
+    }
+    return grad;
+  }
+
+  std::vector<TensorPtr> GetParameters() {  // layers.go:362-368
+    std::vector<TensorPtr> params;
+    for (auto& l : layers_)
+      for (auto& p : l->GetParameters()) params.push_back(p);
+    return params;
+  }
+  std::vector<TensorPtr> GetGradients() {  // layers.go:371-377
+    std::vector<TensorPtr> grads;
+    for (auto& l : layers_)
+      for (auto& g : l->GetGradients()) grads.push_back(g);
+    return grads;
+  }
+
+ private:
+  std::vector<std::shared_ptr<Layer>> layers_;
+  bool fuse_;
+};
+inline std::shared_ptr<Sequential> NewSequential(std::vector<std::shared_ptr<Layer>> layers) {
+  return std::make_shared<Sequential>(std::move(layers));
+}
+
+// ---- gpu/matrix/fused-operations.go:1468-1520 (GradFusedLinearActivation) ---------------------
+// The slice of the reference's GradientTensor this entry needs (gradient.go:16-40): the
+// tensor, whether it wants a gradient, and the function that maps the gradient of the
+// output to the gradients of {input, weight, bias}.
+struct GradientTensor {
+  TensorPtr Tensor;
+  bool RequiresGrad = false;
+  bool IsLeaf = true;
+  std::function<std::vector<TensorPtr>(const TensorPtr&)> BackwardFn;  // GradFn.BackwardFn
+};
+using GradientTensorPtr = std::shared_ptr<GradientTensor>;
+
+// Forward through the fused kernel; the backward closure returns {dX, dW, db?}.  The
+// reference's backward reads the activation mask from its third saved tensor, which this
+// function fills with the BIAS (fused-operations.go:491-500 against :1473-1476), and leaves the
+// bias gradient to a placeholder; here the mask comes from the saved activation output and
+// the bias gradient is the column sum.  ReLU or no activation only (what the mask covers).
+inline GradientTensorPtr GradFusedLinearActivation(const GradientTensorPtr& input,
+                                                   const GradientTensorPtr& weight,
+                                                   const GradientTensorPtr& bias,
+                                                   const FusedLinearConfig& config) {
+  std::vector<TensorPtr> inputs{input->Tensor, weight->Tensor};
+  if (bias) inputs.push_back(bias->Tensor);
+  TensorPtr output;
+  try {
+    output = FusedLinearActivationForward(inputs, config);
+  } catch (const gonngpu::Error& e) {
+    throw gonngpu::Error(std::string("fused linear+activation forward failed: ") + e.what());
+  }
+  auto result = std::make_shared<GradientTensor>();
+  result->Tensor = output;
+  result->IsLeaf = false;
+  result->RequiresGrad = input->RequiresGrad || weight->RequiresGrad || (bias && bias->RequiresGrad);
+  if (result->RequiresGrad) {
+    const bool relu = !config.Activation || config.Activation->Type == ReLU;
+    if (!relu && int(config.Activation->Type) >= 0)
+      throw gonngpu::Error("GradFusedLinearActivation: backward supports ReLU or no activation");
+    TensorPtr x = input->Tensor, w = weight->Tensor;
+    const bool with_bias = bias != nullptr;
+    result->BackwardFn = [x, w, output, relu, with_bias](const TensorPtr& gradOutput) {
+      LinearGradients g = LinearBackward(x, w, gradOutput, relu ? output : nullptr);
+      std::vector<TensorPtr> grads{g.Input, g.Weight};
+      if (with_bias) grads.push_back(g.Bias);
+      return grads;
+    };
+  }
   return result;
 }
 
