@@ -64,6 +64,9 @@ struct Device {
   uint32_t* splitk_counters = nullptr;           // per-tile arrival counters (zero between launches)
   void* stage[2] = {nullptr, nullptr};
   cudaEvent_t stage_ev[2] = {nullptr, nullptr};
+  // events of the streamed product (re-recorded block after block: a stream's wait keeps the
+  // record that was current when the wait was enqueued)
+  cudaEvent_t ev_start = nullptr, ev_up = nullptr, ev_done = nullptr;
 };
 
 Device g_dev[kMaxDevices];
@@ -174,7 +177,10 @@ int ensure_device(int ordinal, CError* err) {
             cudaMalloc(reinterpret_cast<void**>(&d.first_zero_dev), 8) == cudaSuccess &&
             cudaMalloc(reinterpret_cast<void**>(&d.splitk_ws), kSplitKBytes) == cudaSuccess &&
             cudaMalloc(reinterpret_cast<void**>(&d.splitk_counters), kSplitKSlots * 4) == cudaSuccess &&
-            cudaMemset(d.splitk_counters, 0, kSplitKSlots * 4) == cudaSuccess;
+            cudaMemset(d.splitk_counters, 0, kSplitKSlots * 4) == cudaSuccess &&
+            cudaEventCreateWithFlags(&d.ev_start, cudaEventDisableTiming) == cudaSuccess &&
+            cudaEventCreateWithFlags(&d.ev_up, cudaEventDisableTiming) == cudaSuccess &&
+            cudaEventCreateWithFlags(&d.ev_done, cudaEventDisableTiming) == cudaSuccess;
   for (int i = 0; ok && i < 2; ++i) {
     ok = cudaHostAlloc(&d.stage[i], kStageBytes, cudaHostAllocDefault) == cudaSuccess &&
          cudaEventCreateWithFlags(&d.stage_ev[i], cudaEventDisableTiming) == cudaSuccess;
@@ -394,6 +400,79 @@ long stream_rows() {
   }();
   return rows;
 }
+// One device's share of a streamed product: `rows` rows of A in page-locked host memory, the
+// fp32 and fp16 device copies they pass through, the B plane on that device, and where the
+// rows of C go (device and page-locked host).
+struct StreamedShard {
+  const float* host_a = nullptr;
+  float* host_c = nullptr;
+  float* dev_a = nullptr;
+  float* dev_c = nullptr;
+  void* plane_a = nullptr;
+  uint64_t pitch = 0;
+  long rows = 0, N = 0, K = 0;
+  gonn::GemmOperand b;
+  int pkind = 0;
+  float alpha = 1.f;
+  const float* bias = nullptr;
+  int act = gonn::ACT_NONE;
+  float act_param = 0.f;
+  // the uploads of A wait for what is already queued on the compute stream (false: only the
+  // products do, so the rows travel while B is still on its way)
+  bool uploads_wait = true;
+};
+
+// Enqueues the shard's blocks on the device's three streams (the device must be current)
+// without waiting for anything.  Returns false on a CUDA or launch error (*msg set for the latter).
+bool streamed_issue(Device& d, const StreamedShard& s, const char** msg) {
+  const long block = stream_rows();
+  // the side streams start after everything already queued on the compute stream (B, bias)
+  bool ok = cudaEventRecord(d.ev_start, d.stream) == cudaSuccess &&
+            (!s.uploads_wait || cudaStreamWaitEvent(d.copy_stream, d.ev_start, 0) == cudaSuccess) &&
+            cudaStreamWaitEvent(d.d2h_stream, d.ev_start, 0) == cudaSuccess;
+  for (long r0 = 0; r0 < s.rows && ok; r0 += block) {
+    const long rows = std::min(block, s.rows - r0);
+    float* a_dev = s.dev_a + size_t(r0) * s.K;
+    float* c_dev = s.dev_c + size_t(r0) * s.N;
+    ok = cudaMemcpyAsync(a_dev, s.host_a + size_t(r0) * s.K, size_t(rows) * s.K * 4,
+                         cudaMemcpyHostToDevice, d.copy_stream) == cudaSuccess &&
+         cudaEventRecord(d.ev_up, d.copy_stream) == cudaSuccess &&
+         cudaStreamWaitEvent(d.stream, d.ev_up, 0) == cudaSuccess;
+    if (!ok) break;
+    g_stats[1] += long(rows) * s.K * 4;
+    char* plane_rows = static_cast<char*>(s.plane_a) + size_t(r0) * s.pitch * 2;
+    gonn::launch_cvt_f16(a_dev, uint64_t(rows), uint64_t(s.K), plane_rows, s.pitch, s.pkind, d.stream);
+    gonn::GemmOperand oa;
+    oa.plane0 = plane_rows;
+    oa.pitch = s.pitch;
+    oa.mn_major = false;
+    gonn::GemmEpilogue epi;
+    epi.alpha = s.alpha;
+    epi.bias = s.bias;
+    epi.act = s.act;
+    epi.act_param = s.act_param;
+    *msg = gonn::launch_gemm(gonn::Kind::F16, uint32_t(rows), uint32_t(s.N), uint32_t(s.K), oa, s.b, c_dev,
+                             uint64_t(s.N), epi, d.status_dev, d.sm_count, g_tune, d.stream);
+    if (*msg) return false;
+    g_stats[3] += 2;
+    ++g_stats[4];
+    ok = cudaEventRecord(d.ev_done, d.stream) == cudaSuccess &&
+         cudaStreamWaitEvent(d.d2h_stream, d.ev_done, 0) == cudaSuccess &&
+         cudaMemcpyAsync(s.host_c + size_t(r0) * s.N, c_dev, size_t(rows) * s.N * 4, cudaMemcpyDeviceToHost,
+                         d.d2h_stream) == cudaSuccess;
+    g_stats[2] += long(rows) * s.N * 4;
+  }
+  return ok;
+}
+
+// Everything a streamed_issue enqueued is complete on return.
+bool streamed_wait(Device& d) {
+  const bool a = cudaStreamSynchronize(d.copy_stream) == cudaSuccess;
+  const bool b = cudaStreamSynchronize(d.stream) == cudaSuccess;
+  const bool c = cudaStreamSynchronize(d.d2h_stream) == cudaSuccess;
+  return a && b && c;
+}
+
 int matmul_streamed(Device& d, Buffer* A, Buffer* B, Buffer* C, Buffer* bias, long M, long N, long K,
                     bool transB, int pkind, float alpha, int act, float act_param, const char** msg) {
   const long kStreamRows = stream_rows();
@@ -417,66 +496,27 @@ int matmul_streamed(Device& d, Buffer* A, Buffer* B, Buffer* C, Buffer* bias, lo
     g_stats[0] += long(pa_bytes);
     g_stats[6] += long(pa_bytes);
   }
-  const long blocks = (M + kStreamRows - 1) / kStreamRows;
-  std::vector<cudaEvent_t> up(blocks), done(blocks);
-  bool ok = true;
-  for (long i = 0; i < blocks && ok; ++i)
-    ok = cudaEventCreateWithFlags(&up[i], cudaEventDisableTiming) == cudaSuccess &&
-         cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming) == cudaSuccess;
-  cudaEvent_t start;
-  ok = ok && cudaEventCreateWithFlags(&start, cudaEventDisableTiming) == cudaSuccess;
-  // the side streams start after everything already queued on the compute stream (B, bias)
-  ok = ok && cudaEventRecord(start, d.stream) == cudaSuccess &&
-       cudaStreamWaitEvent(d.copy_stream, start, 0) == cudaSuccess &&
-       cudaStreamWaitEvent(d.d2h_stream, start, 0) == cudaSuccess;
-  gonn::GemmOperand ob;
-  ob.plane0 = pb->p0;
-  ob.pitch = pb->pitch;
-  ob.mn_major = !transB;
-  for (long i = 0; i < blocks && ok; ++i) {
-    const long r0 = i * kStreamRows, rows = std::min(kStreamRows, M - r0);
-    float* a_dev = A->dptr + size_t(r0) * K;
-    float* c_dev = C->dptr + size_t(r0) * N;
-    ok = cudaMemcpyAsync(a_dev, A->host + size_t(r0) * K, size_t(rows) * K * 4, cudaMemcpyHostToDevice,
-                         d.copy_stream) == cudaSuccess &&
-         cudaEventRecord(up[i], d.copy_stream) == cudaSuccess &&
-         cudaStreamWaitEvent(d.stream, up[i], 0) == cudaSuccess;
-    if (!ok) break;
-    g_stats[1] += long(rows) * K * 4;
-    char* plane_rows = static_cast<char*>(pa.p0) + size_t(r0) * pitch * 2;
-    gonn::launch_cvt_f16(a_dev, uint64_t(rows), uint64_t(K), plane_rows, pitch, pkind, d.stream);
-    gonn::GemmOperand oa;
-    oa.plane0 = plane_rows;
-    oa.pitch = pitch;
-    oa.mn_major = false;
-    gonn::GemmEpilogue epi;
-    epi.alpha = alpha;
-    epi.bias = bias ? bias->dptr : nullptr;
-    epi.act = act;
-    epi.act_param = act_param;
-    *msg = gonn::launch_gemm(gonn::Kind::F16, uint32_t(rows), uint32_t(N), uint32_t(K), oa, ob, c_dev,
-                             uint64_t(N), epi, d.status_dev, d.sm_count, g_tune, d.stream);
-    if (*msg) {
-      ok = false;
-      break;
-    }
-    g_stats[3] += 2;
-    ++g_stats[4];
-    ok = cudaEventRecord(done[i], d.stream) == cudaSuccess &&
-         cudaStreamWaitEvent(d.d2h_stream, done[i], 0) == cudaSuccess &&
-         cudaMemcpyAsync(C->host + size_t(r0) * N, c_dev, size_t(rows) * N * 4, cudaMemcpyDeviceToHost,
-                         d.d2h_stream) == cudaSuccess;
-    g_stats[2] += long(rows) * N * 4;
-  }
+  StreamedShard s;
+  s.host_a = A->host;
+  s.host_c = C->host;
+  s.dev_a = A->dptr;
+  s.dev_c = C->dptr;
+  s.plane_a = pa.p0;
+  s.pitch = pitch;
+  s.rows = M;
+  s.N = N;
+  s.K = K;
+  s.b.plane0 = pb->p0;
+  s.b.pitch = pb->pitch;
+  s.b.mn_major = !transB;
+  s.pkind = pkind;
+  s.alpha = alpha;
+  s.bias = bias ? bias->dptr : nullptr;
+  s.act = act;
+  s.act_param = act_param;
+  const bool ok = streamed_issue(d, s, msg);
   // everything is complete on return (the ABI is blocking)
-  const bool synced = cudaStreamSynchronize(d.copy_stream) == cudaSuccess &&
-                      cudaStreamSynchronize(d.stream) == cudaSuccess &&
-                      cudaStreamSynchronize(d.d2h_stream) == cudaSuccess;
-  for (long i = 0; i < blocks; ++i) {
-    if (up[i]) cudaEventDestroy(up[i]);
-    if (done[i]) cudaEventDestroy(done[i]);
-  }
-  if (start) cudaEventDestroy(start);
+  const bool synced = streamed_wait(d);
   if (!ok || !synced) return -1;
   A->host_pending = false;
   ++A->version;
@@ -1058,6 +1098,188 @@ int gonngpu_gemm_f16_sharded(const void* a, long aRows, long aCols, long aPitch,
   ++g_stats[3];
   ++g_stats[4];
   return finish(d, err, -6, "gemm_f16_sharded");
+}
+
+// ---- row-sharded MatMul over the GPUs of one process ----------------------------------
+namespace {
+// Rows [lo, hi) of device `i` of `n`: contiguous blocks of ceil(M / n) rows rounded up to the
+// 256-row tile of the pair kernel; the last blocks may be short or empty.
+void shard_rows(long M, int n, int i, long* lo, long* hi) {
+  long per = (M + n - 1) / n;
+  per = (per + 255) / 256 * 256;
+  *lo = std::min(long(i) * per, M);
+  *hi = std::min(*lo + per, M);
+}
+
+struct ShardScratch {
+  int dev = -1;
+  long lo = 0, hi = 0;
+  void* dev_a = nullptr;
+  void* dev_c = nullptr;
+  void* plane_a = nullptr;
+  void* plane_b = nullptr;
+  size_t a_bytes = 0, c_bytes = 0, pa_bytes = 0, pb_bytes = 0;
+};
+}  // namespace
+
+int gonngpu_shard_plan(long rows, int n_devices, int device, long* first_row, long* end_row) {
+  if (rows < 0 || n_devices < 1 || device < 0 || device >= n_devices || !first_row || !end_row) return -3;
+  shard_rows(rows, n_devices, device, first_row, end_row);
+  return 0;
+}
+
+int gonngpu_matmul_sharded(const float* a, long aRows, long aCols, const float* b, long bRows,
+                           long bCols, float* c, int precision, int n_devices, CError* err) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!a || !b || !c) {
+    set_error(err, "matmul_sharded: NULL matrix pointer.");
+    return -2;
+  }
+  if (aRows <= 0 || aCols <= 0 || bRows <= 0 || bCols <= 0 || aCols != bRows || aRows >= (1l << 31) ||
+      aCols >= (1l << 31) || bCols >= (1l << 31)) {
+    set_error(err, "matmul_sharded: incompatible dimensions: A %ldx%ld, B %ldx%ld.", aRows, aCols, bRows,
+              bCols);
+    return -3;
+  }
+  if (precision != GONNGPU_FP16_RN && precision != GONNGPU_FP16_TRUNC) {
+    set_error(err, "matmul_sharded: precision must be GONNGPU_FP16_RN or GONNGPU_FP16_TRUNC.");
+    return -3;
+  }
+  const int visible = gonngpu_device_count();
+  if (n_devices == 0) n_devices = visible;
+  if (n_devices < 1 || n_devices > visible || n_devices > kMaxDevices) {
+    set_error(err, "matmul_sharded: %d devices asked for, %d visible.", n_devices, visible);
+    return -1;
+  }
+  const long M = aRows, K = aCols, N = bCols;
+  const int pkind = precision == GONNGPU_FP16_RN ? 0 : 1;
+  // The rows travel by asynchronous copies: the host matrices must be page-locked.  Memory that
+  // is not (a Go slice, a malloc) is locked for the duration of the call, which costs far more
+  // than the product; callers that care allocate with gonngpu_host_alloc.
+  void* locked[3] = {nullptr, nullptr, nullptr};
+  const void* host[3] = {a, c, b};
+  const size_t host_bytes[3] = {size_t(M) * K * 4, size_t(M) * N * 4, size_t(K) * N * 4};
+  bool lock_ok = true;
+  for (int i = 0; i < 3 && lock_ok; ++i) {
+    if (host_is_pinned(host[i])) continue;
+    if (cudaHostRegister(const_cast<void*>(host[i]), host_bytes[i], cudaHostRegisterPortable) == cudaSuccess) {
+      locked[i] = const_cast<void*>(host[i]);
+    } else {
+      cudaGetLastError();
+      lock_ok = false;
+    }
+  }
+  std::vector<ShardScratch> sh;
+  const uint64_t pitch = round_up(uint64_t(K), 64), pitch_b = round_up(uint64_t(N), 64);
+  int rc = 0;
+  const char* msg = nullptr;
+  void* b32 = nullptr;
+  auto fail = [&](int code, const char* what) {
+    if (rc == 0) {
+      rc = code;
+      cudaError_t e = cudaGetLastError();
+      set_error(err, "matmul_sharded: %s%s%s", what, e != cudaSuccess ? ": " : "",
+                e != cudaSuccess ? cudaGetErrorString(e) : "");
+    }
+  };
+  if (!lock_ok) fail(-5, "could not page-lock a host matrix");
+  // ---- plan and scratch
+  for (int i = 0; i < n_devices && rc == 0; ++i) {
+    ShardScratch x;
+    x.dev = i;
+    shard_rows(M, n_devices, i, &x.lo, &x.hi);
+    if (x.hi <= x.lo) continue;
+    if (ensure_device(i, nullptr)) {
+      fail(-1, "a device of the group is not a usable sm_100 GPU");
+      break;
+    }
+    const size_t rows = size_t(x.hi - x.lo);
+    x.a_bytes = rows * K * 4;
+    x.c_bytes = rows * N * 4;
+    x.pa_bytes = rows * pitch * 2;
+    x.pb_bytes = size_t(K) * pitch_b * 2;
+    if (pool_alloc(i, &x.dev_a, x.a_bytes) != cudaSuccess || pool_alloc(i, &x.dev_c, x.c_bytes) != cudaSuccess ||
+        pool_alloc(i, &x.plane_a, x.pa_bytes) != cudaSuccess || pool_alloc(i, &x.plane_b, x.pb_bytes) != cudaSuccess)
+      fail(-5, "could not allocate device memory for a shard");
+    sh.push_back(x);
+  }
+  // ---- B: to the first device over PCIe, converted there, then to every other device over NVLink
+  if (rc == 0 && !sh.empty()) {
+    ShardScratch& s0 = sh[0];
+    Device& d0 = g_dev[s0.dev];
+    cudaSetDevice(s0.dev);
+    if (pool_alloc(s0.dev, &b32, host_bytes[2]) != cudaSuccess) fail(-5, "could not allocate device memory for B");
+    if (rc == 0) {
+      if (cudaMemcpyAsync(b32, b, host_bytes[2], cudaMemcpyHostToDevice, d0.stream) != cudaSuccess)
+        fail(-6, "host to device copy of B failed");
+      g_stats[1] += long(host_bytes[2]);
+      gonn::launch_cvt_f16(static_cast<const float*>(b32), uint64_t(K), uint64_t(N), s0.plane_b, pitch_b, pkind,
+                           d0.stream);
+      ++g_stats[3];
+      if (cudaEventRecord(d0.ev_done, d0.stream) != cudaSuccess) fail(-6, "event record failed");
+    }
+    for (size_t i = 1; i < sh.size() && rc == 0; ++i) {
+      Device& di = g_dev[sh[i].dev];
+      cudaSetDevice(sh[i].dev);
+      int can = 0;
+      if (cudaDeviceCanAccessPeer(&can, sh[i].dev, s0.dev) == cudaSuccess && can) {
+        if (cudaDeviceEnablePeerAccess(s0.dev, 0) != cudaSuccess) cudaGetLastError();  // already enabled is fine
+      }
+      if (cudaStreamWaitEvent(di.stream, d0.ev_done, 0) != cudaSuccess ||
+          cudaMemcpyPeerAsync(sh[i].plane_b, sh[i].dev, s0.plane_b, s0.dev, s0.pb_bytes, di.stream) != cudaSuccess)
+        fail(-6, "peer copy of B failed");
+    }
+  }
+  // ---- every device's rows: upload, convert, multiply, write back, block by block
+  for (size_t i = 0; i < sh.size() && rc == 0; ++i) {
+    ShardScratch& x = sh[i];
+    Device& d = g_dev[x.dev];
+    cudaSetDevice(x.dev);
+    StreamedShard s;
+    s.host_a = a + size_t(x.lo) * K;
+    s.host_c = c + size_t(x.lo) * N;
+    s.dev_a = static_cast<float*>(x.dev_a);
+    s.dev_c = static_cast<float*>(x.dev_c);
+    s.plane_a = x.plane_a;
+    s.pitch = pitch;
+    s.rows = x.hi - x.lo;
+    s.N = N;
+    s.K = K;
+    s.b.plane0 = x.plane_b;
+    s.b.pitch = pitch_b;
+    s.b.mn_major = true;
+    s.pkind = pkind;
+    s.uploads_wait = false;  // the scratch is this call's own; only the products need B
+    if (!streamed_issue(d, s, &msg)) fail(msg ? -4 : -6, msg ? msg : "a copy or launch of a shard failed");
+  }
+  // ---- wait for every device, collect kernel status, hand the scratch back to the cache
+  for (auto& x : sh) {
+    Device& d = g_dev[x.dev];
+    cudaSetDevice(x.dev);
+    if (!streamed_wait(d)) fail(-6, "execution failed");
+    if (d.status_host->code != 0) {
+      d.last_status = *d.status_host;
+      std::memset(d.status_host, 0, sizeof(GemmStatus));
+      if (rc == 0) {
+        rc = -6;
+        set_error(err, "matmul_sharded: GEMM kernel on device %d gave up waiting (role %u, tile %u, k block %u).",
+                  x.dev, d.last_status.code, d.last_status.tile, d.last_status.kblock);
+      }
+    }
+    pool_free(x.dev, x.dev_a, x.a_bytes);
+    pool_free(x.dev, x.dev_c, x.c_bytes);
+    pool_free(x.dev, x.plane_a, x.pa_bytes);
+    pool_free(x.dev, x.plane_b, x.pb_bytes);
+  }
+  if (b32 && !sh.empty()) {
+    cudaSetDevice(sh[0].dev);
+    pool_free(sh[0].dev, b32, host_bytes[2]);
+  }
+  for (void* p : locked)
+    if (p) cudaHostUnregister(p);
+  cudaSetDevice(g_current);
+  cudaGetLastError();
+  return rc;
 }
 
 // ---- element-wise family (internal/cgo/metal_bridge_matrix.m:172-543) -------------

@@ -96,6 +96,9 @@ SIGNATURES = {
     "gonngpu_gemm_f16_sharded": (
         _c_int, [_vp, _c_long, _c_long, _c_long, _vp, _c_long, _vp, _vp, _vp, _c_int, _c_int, _c_int,
                  _c_long, _c_long, ctypes.c_uint, _vp, _c_long, _c_int, _errp]),
+    "gonngpu_matmul_sharded": (
+        _c_int, [_vp, _c_long, _c_long, _vp, _c_long, _c_long, _vp, _c_int, _c_int, _errp]),
+    "gonngpu_shard_plan": (_c_int, [_c_long, _c_int, _c_int, ctypes.POINTER(_c_long), ctypes.POINTER(_c_long)]),
     "gonngpu_linear_backward": (
         _c_int, [_vp, _vp, _vp, _vp, _c_long, _c_long, _c_long, _vp, _vp, _vp, _errp]),
     "gonngpu_column_sum": (_c_int, [_vp, _c_long, _c_long, _vp, _errp]),
@@ -322,6 +325,21 @@ def gemm_f16_sharded(a_ptr, a_shape, a_pitch, b_src_ptr, b_cols, local_base, bas
         _vp(a_ptr), a_shape[0], a_shape[1], a_pitch, _vp(b_src_ptr) if b_src_ptr else None, b_cols,
         _vp(local_base), _vp(bases_dev_ptr), _vp(multicast_base) if multicast_base else None, world, owner,
         rank, slots_offset, ctrl_offset, epoch, _vp(c_ptr), ldc, first_group, ctypes.byref(err)), err)
+
+
+def matmul_sharded(A, B, C, precision=FP16_RN, n_devices=0):
+    """Host float32 arrays in and out: A's rows split over the process's GPUs."""
+    err = CError()
+    _check(lib().gonngpu_matmul_sharded(_np_ptr(A), A.shape[0], A.shape[1], _np_ptr(B), B.shape[0], B.shape[1],
+                                        _np_ptr(C), precision, n_devices, ctypes.byref(err)), err)
+
+
+def shard_plan(rows, n_devices, device):
+    lo, hi = _c_long(), _c_long()
+    rc = lib().gonngpu_shard_plan(rows, n_devices, device, ctypes.byref(lo), ctypes.byref(hi))
+    if rc != 0:
+        raise GonnError(rc, "bad shard plan arguments")
+    return lo.value, hi.value
 
 
 def matmul_f16_static_scratch(a_ptr, a_shape, b_ptr, b_shape, c_ptr, stream=None):

@@ -287,6 +287,27 @@ GONNGPU_API int gonngpu_replicate_wait(void *const *bases_dev, int world, int ow
                            long ctrl_offset, int slot, unsigned epoch, unsigned ack_value,
                            CError *err);
 
+/* The row-sharded MatMul as ONE call, for a process that sees several GPUs: the multi-GPU
+ * form of matrix.MatMul (gpu/matrix/matrix.go:53-105; the reference has one device).
+ * C[aRows, bCols] = A . B with all three matrices in HOST memory, float32, row-major, dense.
+ * A is split into contiguous row blocks over devices 0 .. n_devices-1 (gonngpu_shard_plan;
+ * n_devices 0 = every visible device), B crosses PCIe once (to device 0), is converted to
+ * fp16 there and copied to the other devices over NVLink (peer copies), and every device
+ * streams its own rows: upload, fp32 -> fp16, product on the tensor cores, and the rows of
+ * C straight back into the caller's `c` at their row offset, block by block, so that both
+ * PCIe directions of every GPU and the tensor cores overlap.  The kernels read their own
+ * GPU's memory only.  `precision` is GONNGPU_FP16_RN or GONNGPU_FP16_TRUNC.
+ * The host matrices should be page-locked (gonngpu_host_alloc); other memory is locked for
+ * the duration of the call, which is slow.  Blocking: C is complete on return.
+ * Errors: -1 device, -2 NULL pointer, -3 dimensions or precision, -4 kernel set-up,
+ * -5 memory, -6 execution. */
+GONNGPU_API int gonngpu_matmul_sharded(const float *a, long aRows, long aCols, const float *b, long bRows,
+                           long bCols, float *c, int precision, int n_devices, CError *err);
+/* The row block [*first_row, *end_row) of `device` when `rows` rows are split over
+ * `n_devices` (blocks of ceil(rows / n_devices) rounded up to the 256-row tile; trailing
+ * blocks may be short or empty).  Returns -3 on bad arguments. */
+GONNGPU_API int gonngpu_shard_plan(long rows, int n_devices, int device, long *first_row, long *end_row);
+
 /* The row-sharded MatMul with the replication of B INSIDE the product kernel: one
  * launch per rank and step, nothing else on the stream.  No counterpart in the
  * reference (one device); it is the multi-GPU form of matrix.MatMul

@@ -22,7 +22,7 @@ def test_shards_tile_the_rows(m, world):
     for (lo, hi), (lo2, _) in zip(shards, shards[1:]):
         assert hi == lo2 and lo <= hi
     for lo, hi in shards[:-1]:
-        assert (hi - lo) % 128 == 0 or hi == m     # full tiles except where the rows run out
+        assert (hi - lo) % 256 == 0 or hi == m     # full tiles except where the rows run out
     assert sum(hi - lo for lo, hi in shards) == m
     with pytest.raises(ValueError):
         shard_rows(m, world, world)
