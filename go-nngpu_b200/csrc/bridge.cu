@@ -99,7 +99,21 @@ constexpr size_t kPoolCapBytes = size_t(24) << 30;
 std::multimap<size_t, void*> g_pool[kMaxDevices];
 size_t g_pool_bytes[kMaxDevices] = {};
 
+// Host-side fault injection (gonngpu_inject_fault): the n-th next allocation / host-to-device
+// copy / device-to-host copy reports failure BEFORE anything is asked of the device, so that
+// the error paths can be tested without making a GPU fail.  0 = disarmed.
+enum FaultKind { FAULT_ALLOC = 0, FAULT_H2D = 1, FAULT_D2H = 2, FAULT_KINDS = 3 };
+int g_fault_countdown[FAULT_KINDS] = {0, 0, 0};
+bool fault_hit(FaultKind k) {
+  if (g_fault_countdown[k] <= 0) return false;
+  return --g_fault_countdown[k] == 0;
+}
+
 cudaError_t pool_alloc(int dev, void** out, size_t bytes) {
+  if (fault_hit(FAULT_ALLOC)) {
+    *out = nullptr;
+    return cudaErrorMemoryAllocation;
+  }
   auto& pool = g_pool[dev];
   auto it = pool.find(bytes);
   if (it != pool.end()) {
@@ -214,6 +228,7 @@ bool host_is_pinned(const void* p) {
 // copy; pageable sources are pipelined through two pinned staging chunks.
 bool copy_h2d(Device& d, void* dst, const void* src, size_t bytes) {
   if (bytes == 0) return true;
+  if (fault_hit(FAULT_H2D)) return false;
   g_stats[1] += long(bytes);
   if (host_is_pinned(src)) {
     return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, d.stream) == cudaSuccess;
@@ -237,6 +252,7 @@ bool copy_h2d(Device& d, void* dst, const void* src, size_t bytes) {
 // Device -> host, complete on return.
 bool copy_d2h(Device& d, void* dst, const void* src, size_t bytes) {
   if (bytes == 0) return true;
+  if (fault_hit(FAULT_D2H)) return false;
   g_stats[2] += long(bytes);
   if (host_is_pinned(dst)) {
     return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, d.stream) == cudaSuccess &&
@@ -1937,6 +1953,18 @@ void gonngpu_host_free(void* p) {
   if (!p) return;
   cudaFreeHost(p);
   cudaGetLastError();
+}
+
+int gonngpu_inject_fault(const char* kind, int nth) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  if (!kind || nth < 0) return -3;
+  int k = -1;
+  if (std::strcmp(kind, "alloc") == 0) k = FAULT_ALLOC;
+  else if (std::strcmp(kind, "h2d") == 0) k = FAULT_H2D;
+  else if (std::strcmp(kind, "d2h") == 0) k = FAULT_D2H;
+  if (k < 0) return -3;
+  g_fault_countdown[k] = nth;
+  return 0;
 }
 
 int gonngpu_device_count(void) {

@@ -111,6 +111,7 @@ SIGNATURES = {
     "gonngpu_mark_modified": (_c_int, [_vp]),
     "gonngpu_host_alloc": (_vp, [_c_long]),
     "gonngpu_host_free": (None, [_vp]),
+    "gonngpu_inject_fault": (_c_int, [ctypes.c_char_p, _c_int]),
     "gonngpu_device_count": (_c_int, []),
     "gonngpu_set_device": (_c_int, [_c_int]),
     "gonngpu_get_device": (_c_int, []),

@@ -409,6 +409,14 @@ GONNGPU_API int gonngpu_mark_modified(GPUPtr buffer);
 GONNGPU_API void *gonngpu_host_alloc(long bytes);
 GONNGPU_API void gonngpu_host_free(void *p);
 
+/* Host-side fault injection for tests of the error paths: the `nth` next device allocation
+ * (`kind` "alloc"), host-to-device copy ("h2d") or device-to-host copy ("d2h") of this
+ * library reports failure before the device is asked for anything; the entry point that
+ * needed it returns its documented error code and message, and the library's state (handles,
+ * cache, statistics) stays consistent.  nth 0 disarms.  No GPU is made to fail.  Returns -3
+ * for an unknown kind. */
+GONNGPU_API int gonngpu_inject_fault(const char *kind, int nth);
+
 GONNGPU_API int gonngpu_device_count(void);
 GONNGPU_API int gonngpu_set_device(int ordinal); /* device used by later calls of this process */
 GONNGPU_API int gonngpu_get_device(void);
