@@ -354,17 +354,20 @@ def run_ours(args, rank, world, local_rank):
         launches = g.stats()["kernel_launches"] - launches0
         total_ms = ev[0].elapsed_time(ev[-1])
 
-        # the dominant kernel alone, B resident: its launch duration for the roofline
-        res_steps = max(3, min(args.steps, 20))
-        product(current_b().data_ptr())
-        kev = [torch.cuda.Event(enable_timing=True) for _ in range(res_steps + 1)]
-        kev[0].record(stream)
-        for i in range(res_steps):
+        # the dominant kernel alone, B resident: its launch duration for the roofline (with one
+        # rank the timed steps above are exactly that)
+        resident_ms = total_ms / args.steps
+        if world > 1:
+            res_steps = max(3, min(args.steps, 20))
             product(current_b().data_ptr())
-            kev[i + 1].record(stream)
-        stream.synchronize()
-        g.synchronize()
-        resident_ms = kev[0].elapsed_time(kev[-1]) / res_steps
+            kev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            kev[0].record(stream)
+            for i in range(res_steps):
+                product(current_b().data_ptr())
+            kev[1].record(stream)
+            stream.synchronize()
+            g.synchronize()
+            resident_ms = kev[0].elapsed_time(kev[1]) / res_steps
         # at N = 1 the step IS that kernel; with several ranks the step's kernel also moves B
         kernel_ms = total_ms / args.steps if world == 1 else resident_ms
         step()                      # C of a complete step for the parity check below

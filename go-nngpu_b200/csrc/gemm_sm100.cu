@@ -22,6 +22,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 #include "kernels.h"
 #include "launch.cuh"
@@ -36,8 +37,9 @@ constexpr uint32_t SLAB_ROW_BYTES = 128;             // one swizzle row
 constexpr uint32_t A_TILE_BYTES = BLOCK_M * SLAB_ROW_BYTES;  // 16 KiB per plane per k block
 constexpr uint32_t KSTEPS = 4;                       // MMAs (per product) per k block
 constexpr uint32_t NUM_THREADS = 192;
-constexpr uint32_t GATED_THREADS = 256;  // + 2 sender warps (row-sharded product)
-constexpr uint32_t SENDER_WARPS = 2;
+constexpr uint32_t SENDER_WARPS = 4;     // extra warps of the row-sharded product that move B
+constexpr uint32_t GATED_THREADS = NUM_THREADS + 32 * SENDER_WARPS;
+constexpr uint32_t SENDER_DEPTH = 8;     // 16-byte loads a sender lane keeps in flight
 constexpr uint32_t SMEM_LIMIT = 227 * 1024;
 
 // How one operand's k-block tile is fetched by TMA and described to the MMA.
@@ -459,7 +461,7 @@ __device__ void push_b_slabs(const ShardParams& s, uint32_t wid, uint32_t nwarps
   ShardControl* mine = shard_ctrl(s, s.rank);
   // the slot may be overwritten only when every rank has finished with the epoch that last used it
   bool ok = true;
-  if (lane < s.world) ok = ptx::flag_wait(&mine->ack[lane], s.ack_needed, nullptr);
+  if (lane < s.world) ok = ptx::flag_wait(&mine->ack[lane], s.ack_needed, nullptr, ptx::kAckWaitLimitNs);
   if (!__all_sync(0xffffffffu, ok)) {
     // nothing is written and nothing published: the products' own waits run out and report
     if (!ok && (atomicOr(&mine->gave_up, 2u) & 2u) == 0u) report(status, 4, lane, s.epoch, s.ack_needed);
@@ -468,25 +470,27 @@ __device__ void push_b_slabs(const ShardParams& s, uint32_t wid, uint32_t nwarps
   for (uint32_t slab = 0; slab < s.num_slabs; ++slab) {
     const uint32_t c0 = slab * s.slab_chunks;
     const uint32_t width = min(s.slab_chunks, s.row_chunks - c0);
+    // The link only runs at full rate with enough bytes in flight (rate x latency is about
+    // 1.5 MB): every lane issues SENDER_DEPTH loads, one per row, before its first store.
     for (uint32_t ch = lane; ch < width; ch += 32u) {
       const uint64_t col = uint64_t(c0) + ch;
-      for (uint32_t row = wid; row < s.rows; row += 4u * nwarps) {
-        uint4 v[4];
-        uint64_t off[4];
+      for (uint32_t row = wid; row < s.rows; row += SENDER_DEPTH * nwarps) {
+        uint4 v[SENDER_DEPTH];
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
+        for (uint32_t j = 0; j < SENDER_DEPTH; ++j) {
           const uint32_t r = row + j * nwarps;
-          off[j] = uint64_t(r) * s.row_chunks + col;
-          if (r < s.rows) v[j] = ptx::ld_stream_16(s.src + off[j]);
+          if (r < s.rows) v[j] = ptx::ld_stream_16(s.src + uint64_t(r) * s.row_chunks + col);
         }
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
-          if (row + j * nwarps >= s.rows) continue;
+        for (uint32_t j = 0; j < SENDER_DEPTH; ++j) {
+          const uint32_t r = row + j * nwarps;
+          if (r >= s.rows) continue;
+          const uint64_t off = uint64_t(r) * s.row_chunks + col;
           if (s.mc_dst) {
-            ptx::multimem_st_16(s.mc_dst + off[j], v[j]);
+            ptx::multimem_st_16(s.mc_dst + off, v[j]);
           } else {
-            for (uint32_t r = 0; r < s.world; ++r)
-              reinterpret_cast<uint4*>(static_cast<char*>(s.bases[r]) + s.slot_offset)[off[j]] = v[j];
+            for (uint32_t k = 0; k < s.world; ++k)
+              reinterpret_cast<uint4*>(static_cast<char*>(s.bases[k]) + s.slot_offset)[off] = v[j];
           }
         }
       }
@@ -543,8 +547,8 @@ __device__ __forceinline__ void shard_exit(const ShardParams& s, bool gave_up) {
 // A stage holds SUB k blocks (each laid out as A tile then B half tile); one
 // barrier round (full wait, commit) therefore covers 4*SUB MMAs.
 //
-// GATED: the row-sharded product that replicates B itself.  Two more warps per CTA (6, 7)
-// push B on the owner; every producer waits for the arrival flag of a tile's column slab
+// GATED: the row-sharded product that replicates B itself.  SENDER_WARPS more warps per CTA
+// (6 and up) push B on the owner; every producer waits for the arrival flag of a tile's column slab
 // before the tile's first load; the last CTA to leave acknowledges the epoch.
 template <int BLOCK_N, int STAGES, int SUB, bool GATED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATED ? GATED_THREADS : NUM_THREADS, 1)
@@ -626,7 +630,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           bool here = true;
           if (lane == 0) {
             here = ptx::flag_wait(&shard_ctrl(p.sh, p.sh.rank)->arrived[p.sh.slot][slab], p.sh.epoch,
-                                  abort_flag);
+                                  abort_flag, ptx::kDataWaitLimitNs);
             // the slab was written by another GPU's stores: order the flag's acquire before
             // this thread's TMA loads of the slab
             ptx::fence_proxy_async_global();
@@ -1911,7 +1915,7 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn encode_tiled() {
+EncodeTiledFn encode_tiled_driver() {
   static EncodeTiledFn fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {
@@ -1925,6 +1929,60 @@ EncodeTiledFn encode_tiled() {
   });
   return fn;
 }
+
+// A tensor map is a pure function of its arguments (address, extents, strides, box, swizzle),
+// and a layer chain multiplies the same buffers with the same shapes step after step, so the
+// encoded maps are kept: a GEMM call then costs a table look-up per operand instead of a
+// driver call.  Bounded: the table is emptied when it reaches kMapCacheMax entries.
+struct MapKey {
+  uint64_t w[12];
+  bool operator==(const MapKey& o) const { return std::memcmp(w, o.w, sizeof(w)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (uint64_t x : k.w) h = (h ^ x) * 1099511628211ull;
+    return size_t(h);
+  }
+};
+constexpr size_t kMapCacheMax = 1024;
+std::mutex g_map_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+
+CUresult encode_cached(CUtensorMap* map, CUtensorMapDataType dtype, cuuint32_t rank, void* base,
+                       const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
+                       const cuuint32_t* estr, CUtensorMapInterleave il, CUtensorMapSwizzle sw,
+                       CUtensorMapL2promotion promo, CUtensorMapFloatOOBfill oob) {
+  EncodeTiledFn fn = encode_tiled_driver();
+  if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
+  if (rank > 3) return fn(map, dtype, rank, base, dims, strides, box, estr, il, sw, promo, oob);
+  MapKey k{};
+  k.w[0] = uint64_t(dtype) | (uint64_t(rank) << 8) | (uint64_t(il) << 16) | (uint64_t(sw) << 24) |
+           (uint64_t(promo) << 32) | (uint64_t(oob) << 40);
+  k.w[1] = reinterpret_cast<uint64_t>(base);
+  for (cuuint32_t i = 0; i < rank; ++i) {
+    k.w[2 + i] = dims[i];
+    k.w[8 + i] = uint64_t(box[i]) | (uint64_t(estr[i]) << 32);
+  }
+  for (cuuint32_t i = 0; i + 1 < rank; ++i) k.w[5 + i] = strides[i];
+  {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    auto it = g_map_cache.find(k);
+    if (it != g_map_cache.end()) {
+      *map = it->second;
+      return CUDA_SUCCESS;
+    }
+  }
+  const CUresult r = fn(map, dtype, rank, base, dims, strides, box, estr, il, sw, promo, oob);
+  if (r == CUDA_SUCCESS) {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    if (g_map_cache.size() >= kMapCacheMax) g_map_cache.clear();
+    g_map_cache.emplace(k, *map);
+  }
+  return r;
+}
+
+EncodeTiledFn encode_tiled() { return encode_tiled_driver() ? &encode_cached : nullptr; }
 
 // 2-D map over a row-major plane: `inner` contiguous elements per row, `outer`
 // rows, boxes of (128 bytes, box_rows) written with the 128-byte swizzle.

@@ -18,15 +18,24 @@ namespace {
 // internal/cgo/metal_bridge_matrix.m:159-166, tiled through shared memory so
 // that both the read of `in` and the write of `out` are coalesced.
 constexpr int TT = 64;  // tile edge
+constexpr int TG = 8;   // tile rows per band of the block walk
 
 template <bool VEC_IN, bool VEC_OUT>
 __global__ void __launch_bounds__(256) transpose_kernel(const float* __restrict__ in,
                                                         float* __restrict__ out, uint32_t rows,
-                                                        uint32_t cols, uint32_t tiles_c) {
+                                                        uint32_t cols, uint32_t tiles_r,
+                                                        uint32_t tiles_c) {
   ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
   ptx::grid_dependency_wait();
   __shared__ float tile[TT][TT + 1];  // tile[c][r]
-  const uint32_t tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
+  // Blocks walk bands of TG tile rows column by column, so that the blocks in flight
+  // together read TG * 64 input rows and write runs of TG * 256 bytes of every output row
+  // they touch (a plain row-major walk writes 256-byte pieces 4 * rows bytes apart).
+  const uint32_t band = TG * tiles_c;
+  const uint32_t first_r = (blockIdx.x / band) * TG;
+  const uint32_t in_band = blockIdx.x % band;
+  const uint32_t gsz = min(uint32_t(TG), tiles_r - first_r);
+  const uint32_t tr = first_r + in_band % gsz, tc = in_band / gsz;
   const uint32_t r0 = tr * TT, c0 = tc * TT;
   const uint32_t tid = threadIdx.x;
 
@@ -107,29 +116,56 @@ __device__ __forceinline__ uint16_t f32_to_f16(float f, int mode) {
   return mode == F16_TRUNC ? f32_to_f16_trunc(f) : __half_as_ushort(__float2half_rn(f));
 }
 
+// Walks the (row, 4-element group) pairs of a matrix with `q` groups per row in steps of
+// `stride` pairs without a division per step.
+struct RowWalk {
+  uint64_t r, g;      // current row and group within the row
+  uint64_t dr, dg;    // stride / q, stride % q
+  __device__ RowWalk(uint64_t start, uint64_t stride, uint64_t q)
+      : r(start / q), g(start % q), dr(stride / q), dg(stride % q) {}
+  __device__ __forceinline__ void next(uint64_t q) {
+    r += dr;
+    g += dg;
+    if (g >= q) {
+      g -= q;
+      ++r;
+    }
+  }
+};
+
 __global__ void __launch_bounds__(256) cvt_f16_kernel(const float* __restrict__ src, uint64_t rows,
                                                       uint64_t cols, uint16_t* __restrict__ dst,
                                                       uint64_t pitch, int mode, int vec) {
   ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
   ptx::grid_dependency_wait();
+  const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+  const uint64_t start = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
   if (vec) {  // cols % 4 == 0 and both bases 16-byte aligned; pitch % 8 == 0 always
-    const uint64_t q = cols >> 2, total = rows * q;
-    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
-         i += uint64_t(gridDim.x) * blockDim.x) {
-      const uint64_t r = i / q, c = (i - r * q) << 2;
-      const float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * cols + c));
+    const uint64_t q = cols >> 2;
+    RowWalk w2(start + stride, stride * 2, q);
+    // two groups per trip: both loads are in flight before the first store
+    RowWalk a(start, stride * 2, q);
+    for (; w2.r < rows; a.next(q), w2.next(q)) {
+      const float4 v0 = __ldcs(reinterpret_cast<const float4*>(src + a.r * cols + (a.g << 2)));
+      const float4 v1 = __ldcs(reinterpret_cast<const float4*>(src + w2.r * cols + (w2.g << 2)));
+      uint2 o0, o1;
+      o0.x = uint32_t(f32_to_f16(v0.x, mode)) | (uint32_t(f32_to_f16(v0.y, mode)) << 16);
+      o0.y = uint32_t(f32_to_f16(v0.z, mode)) | (uint32_t(f32_to_f16(v0.w, mode)) << 16);
+      o1.x = uint32_t(f32_to_f16(v1.x, mode)) | (uint32_t(f32_to_f16(v1.y, mode)) << 16);
+      o1.y = uint32_t(f32_to_f16(v1.z, mode)) | (uint32_t(f32_to_f16(v1.w, mode)) << 16);
+      *reinterpret_cast<uint2*>(dst + a.r * pitch + (a.g << 2)) = o0;
+      *reinterpret_cast<uint2*>(dst + w2.r * pitch + (w2.g << 2)) = o1;
+    }
+    if (a.r < rows) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(src + a.r * cols + (a.g << 2)));
       uint2 o;
       o.x = uint32_t(f32_to_f16(v.x, mode)) | (uint32_t(f32_to_f16(v.y, mode)) << 16);
       o.y = uint32_t(f32_to_f16(v.z, mode)) | (uint32_t(f32_to_f16(v.w, mode)) << 16);
-      *reinterpret_cast<uint2*>(dst + r * pitch + c) = o;
+      *reinterpret_cast<uint2*>(dst + a.r * pitch + (a.g << 2)) = o;
     }
   } else {
-    const uint64_t total = rows * cols;
-    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
-         i += uint64_t(gridDim.x) * blockDim.x) {
-      const uint64_t r = i / cols, c = i - r * cols;
-      dst[r * pitch + c] = f32_to_f16(src[i], mode);
-    }
+    for (RowWalk w(start, stride, cols); w.r < rows; w.next(cols))
+      dst[w.r * pitch + w.g] = f32_to_f16(src[w.r * cols + w.g], mode);
   }
 }
 
@@ -151,11 +187,12 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
                                                          int vec) {
   ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
   ptx::grid_dependency_wait();
+  const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+  const uint64_t start = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
   if (vec) {
-    const uint64_t q = cols >> 2, total = rows * q;
-    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
-         i += uint64_t(gridDim.x) * blockDim.x) {
-      const uint64_t r = i / q, c = (i - r * q) << 2;
+    const uint64_t q = cols >> 2;
+    for (RowWalk w(start, stride, q); w.r < rows; w.next(q)) {
+      const uint64_t r = w.r, c = w.g << 2;
       float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * cols + c));
       if (mask) {
         const float4 m = __ldcs(reinterpret_cast<const float4*>(mask + r * cols + c));
@@ -173,15 +210,13 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
       *reinterpret_cast<float4*>(lo + r * pitch + c) = l;
     }
   } else {
-    const uint64_t total = rows * cols;
-    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total;
-         i += uint64_t(gridDim.x) * blockDim.x) {
-      const uint64_t r = i / cols, c = i - r * cols;
+    for (RowWalk w(start, stride, cols); w.r < rows; w.next(cols)) {
+      const uint64_t i = w.r * cols + w.g;
       float x = src[i];
       if (mask && !(mask[i] > 0.0f)) x = 0.0f;
       const float h = rna_tf32(x);
-      hi[r * pitch + c] = h;
-      lo[r * pitch + c] = rna_tf32(x - h);
+      hi[w.r * pitch + w.g] = h;
+      lo[w.r * pitch + w.g] = rna_tf32(x - h);
     }
   }
 }
@@ -344,13 +379,17 @@ void launch_transpose(const float* in, uint64_t rows, uint64_t cols, float* out,
   const bool vin = (cols % 4 == 0) && aligned16(in);
   const bool vout = (rows % 4 == 0) && aligned16(out);
   if (vin && vout)
-    launch_kernel(transpose_kernel<true, true>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+    launch_kernel(transpose_kernel<true, true>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_r,
+                  tiles_c);
   else if (vin)
-    launch_kernel(transpose_kernel<true, false>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+    launch_kernel(transpose_kernel<true, false>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_r,
+                  tiles_c);
   else if (vout)
-    launch_kernel(transpose_kernel<false, true>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+    launch_kernel(transpose_kernel<false, true>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_r,
+                  tiles_c);
   else
-    launch_kernel(transpose_kernel<false, false>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_c);
+    launch_kernel(transpose_kernel<false, false>, dim3(grid), dim3(256), 0, stream, in, out, uint32_t(rows), uint32_t(cols), tiles_r,
+                  tiles_c);
 }
 
 void launch_cvt_f16(const float* src, uint64_t rows, uint64_t cols, void* dst, uint64_t pitch,

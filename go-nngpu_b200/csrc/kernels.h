@@ -148,7 +148,7 @@ cudaError_t launch_replicate_wait(void* const* bases, int owner, int my_rank, ui
 
 // ---- row-sharded product with the replication of B inside the kernel ---------------
 // Every rank multiplies its rows of A by the whole of B, which only the owner holds.  The
-// product kernel itself moves B: on the owner, two extra warps per CTA push B, column slab by
+// product kernel itself moves B: on the owner, extra warps of every CTA push B, column slab by
 // column slab, into the current slot of every rank's symmetric buffer (multimem.st through
 // NVSwitch, or plain peer stores when the group has no multicast address) and publish one
 // arrival flag per slab; on every rank the TMA producer of a tile waits for the flag of the

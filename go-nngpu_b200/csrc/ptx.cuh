@@ -393,17 +393,22 @@ __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
 __device__ __forceinline__ bool epoch_reached(uint32_t seen, uint32_t wanted) {
   return int32_t(seen - wanted) >= 0;
 }
-// Polls `word` until it has reached `wanted`; false when the limit (1.5 s and an iteration
-// cap) ran out or `abort_flag` (may be null) was raised.
+// Polls `word` until it has reached `wanted`; false when the limit (`limit_ns` and an
+// iteration cap) ran out or `abort_flag` (may be null) was raised.  Waits that feed one
+// another get staggered limits, the innermost the shortest, so that the wait that names the
+// cause runs out (and reports) before the waits that merely depend on it.
+constexpr uint64_t kAckWaitLimitNs = 1000ull * 1000 * 1000;   // owner: acknowledgements of a slot
+constexpr uint64_t kDataWaitLimitNs = 1250ull * 1000 * 1000;  // a rank: arrival of replicated data
 __device__ __forceinline__ bool flag_wait(const uint32_t* word, uint32_t wanted,
-                                          volatile uint32_t* abort_flag) {
+                                          volatile uint32_t* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   for (uint32_t i = 0; i < 1024; ++i)
     if (epoch_reached(ld_acquire_sys(word), wanted)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t i = 0; i < (1u << 24); ++i) {
     if (epoch_reached(ld_acquire_sys(word), wanted)) return true;
     if (abort_flag && *abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    if (globaltimer_ns() - t0 > limit_ns) return false;
     __nanosleep(100);
   }
   return false;

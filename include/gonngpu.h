@@ -323,7 +323,7 @@ GONNGPU_API int gonngpu_shard_plan(long rows, int n_devices, int device, long *f
  * peer stores instead).  At `slots_offset` it holds two slots of aCols*bCols*2
  * bytes, at `ctrl_offset` 512 bytes of control words, zero before epoch 1.
  *
- * On the owner two extra warps of every CTA push B into slot epoch % 2 of every
+ * On the owner extra warps of every CTA push B into slot epoch % 2 of every
  * rank, 256-column slab by slab, and raise one arrival flag per slab; on every
  * rank a tile's loads wait for the flag of its slab, and the first `first_group`
  * 256-row tiles (0 = chosen from the group size) are visited slab by slab, so the
@@ -333,7 +333,7 @@ GONNGPU_API int gonngpu_shard_plan(long rows, int n_devices, int device, long *f
  * once per step with the same epoch: 1, 2, 3 ...  The kernels read B from their
  * own GPU's memory only.
  *
- * Enqueued on the library's stream.  Every wait is bounded (1.5 s); one that ran
+ * Enqueued on the library's stream.  Every wait is bounded (1 to 1.5 s); one that ran
  * out is reported as -6 (blocking mode) or by gonngpu_synchronize, with status
  * code 4 (owner: acknowledgements missing) or 6 (a slab of B did not arrive;
  * where = slab, tile, k block = epoch); no acknowledgement is then sent.

@@ -144,7 +144,7 @@ def test_group_of_one_sends_to_itself_and_multiplies(gpu, m, k, n, first_group):
 @pytest.mark.gpu
 def test_rank_whose_b_never_arrives_gives_up_and_reports(gpu):
     """Failure detection without a fault: rank 0 of a group of two whose owner (rank 1) does not
-    exist.  The producers' wait for the first slab runs out (1.5 s), the call returns -6 with the
+    exist.  The producers' wait for the first slab runs out (1.25 s), the call returns -6 with the
     slab, tile and epoch, no acknowledgement is written, and the library goes on working.  With
     the flags set by hand (the data is then whatever lies in the slot) the same call succeeds."""
     from oracle import oracle
