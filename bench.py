@@ -277,9 +277,12 @@ def run_ours(args, rank, world, local_rank):
     rows = hi - lo
 
     # ---- inputs: this rank's rows of A and all of B, in page-locked memory (the e2e leg reads them there)
-    hA, pA = g.pinned_array((rows, K_DIM))
+    # (with several ranks, rank 0 keeps all of A: it also drives gonngpu_matmul_sharded over every GPU)
+    whole = world > 1 and rank == 0 and not args.no_e2e
+    hA_all, pA = g.pinned_array((M_TOTAL if whole else rows, K_DIM))
     hB, pB = g.pinned_array((K_DIM, N_DIM))
-    hB[...] = draw_inputs(lo, hi, a_out=hA)[1]
+    hB[...] = draw_inputs(0 if whole else lo, M_TOTAL if whole else hi, a_out=hA_all)[1]
+    hA = hA_all[lo:hi] if whole else hA_all
 
     with torch.cuda.stream(stream):
         L.gonngpu_set_blocking(0)
@@ -409,6 +412,10 @@ def run_ours(args, rank, world, local_rank):
         if not args.no_e2e:
             del A16, C
             e2e = run_e2e(args, g, L, torch, dist, dev, rank, world, rows, hA, hB)
+            if world > 1:
+                one_call = run_e2e_one_call(args, g, L, torch, dist, dev, rank, world, hA_all, hB)
+                if rank == 0:
+                    e2e = merge_e2e(e2e, one_call)
             if numa is not None:
                 e2e["host_numa_node_rank0"] = numa
 
@@ -556,6 +563,55 @@ def run_e2e(args, g, L, torch, dist, dev, rank, world, rows, hA, hB):
     return {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
             "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
             "rank0_rows_rel_frobenius": err}
+
+
+def run_e2e_one_call(args, g, L, torch, dist, dev, rank, world, hA_all, hB):
+    """The same product as ONE library call of ONE process: rank 0 hands the whole host
+    matrices to gonngpu_matmul_sharded, which splits the rows over all `world` GPUs, while the
+    other ranks wait on the host (a gloo barrier: nothing of theirs runs on the GPUs meanwhile)."""
+    cpu = dist.new_group(backend="gloo")
+    torch.cuda.synchronize()
+    dist.barrier(group=cpu)
+    res = None
+    if rank == 0:
+        from oracle import oracle
+        hC, pC = g.pinned_array((M_TOTAL, N_DIM))
+        steps = max(1, min(args.steps, 4))
+        g.matmul_sharded(hA_all, hB, hC, precision=g.FP16_RN, n_devices=world)   # warm-up: contexts, scratch
+        s0 = g.stats()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            g.matmul_sharded(hA_all, hB, hC, precision=g.FP16_RN, n_devices=world)
+        dt = (time.perf_counter() - t0) / steps
+        s1 = g.stats()
+        idx = np.unique(np.concatenate([[r for d in range(world) for r in g.shard_plan(M_TOTAL, world, d)],
+                                        np.random.default_rng(7).choice(M_TOTAL, 64, replace=False)]))
+        idx = idx[idx < M_TOTAL]
+        idx = np.unique(np.concatenate([idx, np.maximum(idx - 1, 0)]))     # first and last row of every shard
+        ref = oracle.gemm_f64(hA_all[idx].astype(np.float16).astype(np.float32),
+                              hB.astype(np.float16).astype(np.float32))
+        res = {"value": 2.0 * M_TOTAL * K_DIM * N_DIM / dt / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int((s1["h2d_bytes"] - s0["h2d_bytes"]) // steps),
+               "d2h_bytes_per_step": int((s1["d2h_bytes"] - s0["d2h_bytes"]) // steps),
+               "ms_per_step": dt * 1e3, "steps": steps, "rows_checked": int(len(idx)),
+               "rel_frobenius": float(oracle.rel_frobenius(hC[idx], ref)),
+               "call": f"gonngpu_matmul_sharded(n_devices={world}) from one process"}
+        L.gonngpu_host_free(pC)
+        L.gonngpu_trim_cache()
+        L.gonngpu_set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dist.barrier(group=cpu)
+    return res
+
+
+def merge_e2e(per_rank, one_call):
+    """`e2e` is the faster of the two public ways to run the job on N GPUs; both are kept."""
+    per_rank = dict(per_rank, call="create_gpu_buffer / gonngpu_matmul_ex / retrieve_gpu_buffer_data in every rank "
+                                   "on its own rows (B over PCIe on rank 0, then NCCL broadcast)")
+    best = one_call if one_call["value"] > per_rank["value"] else per_rank
+    out = dict(best)
+    out["one_process_call"] = one_call
+    out["per_rank_calls"] = per_rank
+    return out
 
 
 # DRAM bytes of one GEMM launch measured with ncu (dram__bytes_read.sum +

@@ -737,8 +737,13 @@ int release_gpu_buffer(GPUPtr gpuPtr) {
   std::lock_guard<std::recursive_mutex> lk(g_mu);
   Buffer* b = as_buffer(gpuPtr);
   if (!b) return -1;
-  if (cudaSetDevice(b->device) == cudaSuccess && g_dev[b->device].ready) {
-    cudaStreamSynchronize(g_dev[b->device].stream);  // nothing in flight may still use it
+  // Memory the caller owns (registered host memory that an upload may still read, wrapped device
+  // memory) must be out of use when this returns.  The library's own device memory goes back to
+  // the cache without a wait: every kernel runs on the device's one compute stream, so whoever
+  // gets the block next is ordered behind its last user, and cudaFree waits by itself.
+  const bool callers_memory = !b->owns || b->host != nullptr;
+  if (cudaSetDevice(b->device) == cudaSuccess && g_dev[b->device].ready && callers_memory) {
+    cudaStreamSynchronize(g_dev[b->device].stream);
   }
   free_plane(b->f16[0]);
   free_plane(b->f16[1]);
@@ -1209,6 +1214,8 @@ int gonngpu_matmul_sharded(const float* a, long aRows, long aCols, const float* 
       fail(-1, "a device of the group is not a usable sm_100 GPU");
       break;
     }
+    // the uploads below do not wait for the compute stream: blocks from the cache must be idle
+    cudaStreamSynchronize(g_dev[i].stream);
     const size_t rows = size_t(x.hi - x.lo);
     x.a_bytes = rows * K * 4;
     x.c_bytes = rows * N * 4;

@@ -91,7 +91,6 @@ struct KernelParams {
   float alpha, beta, act_param;
   int act;
   uint32_t vec_store;  // C base and pitch allow 16-byte stores
-  uint32_t tma_store;  // epilogue may write C with TMA stores (no beta term, aligned C)
   // batched products (stacked matrices): tiles per batch (0 = one product), and the
   // row-coordinate step per batch of the A and B tensor maps; M is then per batch
   uint32_t batch_tiles;
@@ -165,6 +164,14 @@ __device__ __forceinline__ float apply_act(float v, int act, float param) {
   }
 }
 
+// Raises the CTA's abort flag; true for the one role that raised it.  Only that role reports:
+// the roles that leave because they SAW the flag would otherwise overwrite the cause with
+// their own, later, wait (the status words live in mapped host memory, where "write only if
+// still zero" cannot tell a report of a microsecond ago from none).
+__device__ __forceinline__ bool first_to_give_up(volatile uint32_t* abort_flag) {
+  return atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0u;
+}
+
 __device__ __forceinline__ void report(GemmStatus* st, uint32_t code, uint32_t where,
                                        uint32_t tile, uint32_t kb) {
   // `st` may be page-locked host memory mapped into the device: plain stores
@@ -175,6 +182,72 @@ __device__ __forceinline__ void report(GemmStatus* st, uint32_t code, uint32_t w
     v->tile = tile;
     v->kblock = kb;
     v->code = code;
+  }
+}
+
+// alpha * acc + beta * C_in + bias, then the activation, for four neighbouring columns;
+// `cin` / `bias` point at the first of the four (16-byte aligned) or are null.
+__device__ __forceinline__ float4 epilogue_value4(const KernelParams& p, float4 v, const float* cin,
+                                                  const float* bias) {
+  v.x *= p.alpha;
+  v.y *= p.alpha;
+  v.z *= p.alpha;
+  v.w *= p.alpha;
+  if (cin) {
+    const float4 o = *reinterpret_cast<const float4*>(cin);
+    v.x += p.beta * o.x;
+    v.y += p.beta * o.y;
+    v.z += p.beta * o.z;
+    v.w += p.beta * o.w;
+  }
+  if (bias) {
+    const float4 b = *reinterpret_cast<const float4*>(bias);
+    v.x += b.x;
+    v.y += b.y;
+    v.z += b.z;
+    v.w += b.w;
+  }
+  if (p.act >= 0) {
+    v.x = apply_act(v.x, p.act, p.act_param);
+    v.y = apply_act(v.y, p.act, p.act_param);
+    v.z = apply_act(v.z, p.act, p.act_param);
+    v.w = apply_act(v.w, p.act, p.act_param);
+  }
+  return v;
+}
+// The same for one column.
+__device__ __forceinline__ float epilogue_value(const KernelParams& p, float v, const float* cin,
+                                                const float* bias) {
+  v *= p.alpha;
+  if (cin) v += p.beta * *cin;
+  if (bias) v += *bias;
+  if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
+  return v;
+}
+
+// One thread's 32 consecutive accumulator columns of one output row:
+// alpha/beta/bias/activation, then 16-byte stores (scalar at ragged edges).
+__device__ __forceinline__ void epilogue_store32(const KernelParams& p, const uint32_t (&r)[32],
+                                                 uint32_t row, uint32_t col0) {
+  if (row >= p.M || col0 >= p.N) return;
+  float* c_row = p.C + uint64_t(row) * p.ldc;
+  const float* cin_row = p.c_in ? p.c_in + uint64_t(row) * p.ldc : nullptr;
+  if (col0 + 32u <= p.N && p.vec_store) {
+#pragma unroll
+    for (uint32_t j = 0; j < 32; j += 4) {
+      const float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      *reinterpret_cast<float4*>(c_row + col0 + j) =
+          epilogue_value4(p, v, cin_row ? cin_row + col0 + j : nullptr, p.bias ? p.bias + col0 + j : nullptr);
+    }
+  } else {
+#pragma unroll
+    for (uint32_t j = 0; j < 32; ++j) {
+      const uint32_t col = col0 + j;
+      if (col < p.N)
+        c_row[col] = epilogue_value(p, __uint_as_float(r[j]), cin_row ? cin_row + col : nullptr,
+                                    p.bias ? p.bias + col : nullptr);
+    }
   }
 }
 
@@ -257,8 +330,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) {
-            *abort_flag = 1;
-            report(p.status, 1, stage, t, kb);
+            if (first_to_give_up(abort_flag)) report(p.status, 1, stage, t, kb);
           }
           alive = false;
           break;
@@ -301,16 +373,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
         if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-          *abort_flag = 1;
-          report(p.status, 2, 0x100u | acc, t, 0);
+          if (first_to_give_up(abort_flag)) report(p.status, 2, 0x100u | acc, t, 0);
           break;
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
         for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
           if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
-            *abort_flag = 1;
-            report(p.status, 2, stage, t, kb);
+            if (first_to_give_up(abort_flag)) report(p.status, 2, stage, t, kb);
             alive = false;
             break;
           }
@@ -354,8 +424,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) {
-          *abort_flag = 1;
-          report(p.status, 3, acc, t, 0);
+          if (first_to_give_up(abort_flag)) report(p.status, 3, acc, t, 0);
         }
         break;
       }
@@ -363,8 +432,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
       const uint32_t row = tm * BLOCK_M + quarter * 32u + lane;
       const uint32_t col_tile = tn * BLOCK_N;
       const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * BLOCK_N;
-      float* c_row = p.C + uint64_t(row) * p.ldc;
-      const float* cin_row = p.c_in ? p.c_in + uint64_t(row) * p.ldc : nullptr;
 #pragma unroll 1
       for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
         const uint32_t col0 = col_tile + ch * 32u;
@@ -372,52 +439,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0,
         uint32_t r[32];
         ptx::tmem_ld_32x32(taddr + ch * 32u, r);
         ptx::tmem_ld_wait();
-        if (row < p.M) {
-          const bool full_chunk = (col0 + 32u <= p.N);
-          if (full_chunk && p.vec_store) {
-#pragma unroll
-            for (uint32_t j = 0; j < 32; j += 4) {
-              float4 v;
-              v.x = __uint_as_float(r[j + 0]) * p.alpha;
-              v.y = __uint_as_float(r[j + 1]) * p.alpha;
-              v.z = __uint_as_float(r[j + 2]) * p.alpha;
-              v.w = __uint_as_float(r[j + 3]) * p.alpha;
-              if (cin_row) {
-                const float4 o = *reinterpret_cast<const float4*>(cin_row + col0 + j);
-                v.x += p.beta * o.x;
-                v.y += p.beta * o.y;
-                v.z += p.beta * o.z;
-                v.w += p.beta * o.w;
-              }
-              if (p.bias) {
-                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-                v.x += b.x;
-                v.y += b.y;
-                v.z += b.z;
-                v.w += b.w;
-              }
-              if (p.act >= 0) {
-                v.x = apply_act(v.x, p.act, p.act_param);
-                v.y = apply_act(v.y, p.act, p.act_param);
-                v.z = apply_act(v.z, p.act, p.act_param);
-                v.w = apply_act(v.w, p.act, p.act_param);
-              }
-              *reinterpret_cast<float4*>(c_row + col0 + j) = v;
-            }
-          } else {
-#pragma unroll
-            for (uint32_t j = 0; j < 32; ++j) {
-              const uint32_t col = col0 + j;
-              if (col < p.N) {
-                float v = __uint_as_float(r[j]) * p.alpha;
-                if (cin_row) v += p.beta * cin_row[col];
-                if (p.bias) v += p.bias[col];
-                if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
-                c_row[col] = v;
-              }
-            }
-          }
-        }
+        epilogue_store32(p, r, row, col0);
       }
       ptx::tc_fence_before();
       __syncwarp();
@@ -450,14 +472,20 @@ __device__ __forceinline__ ShardControl* shard_ctrl(const ShardParams& s, uint32
   return reinterpret_cast<ShardControl*>(static_cast<char*>(s.bases[rank]) + s.ctrl_offset);
 }
 
-// Sender warps of the owner (warp `wid` of `nwarps`, all CTAs together): B goes out column
-// slab by column slab, each warp taking whole rows of a slab (consecutive lanes, consecutive
-// 16-byte chunks).  After a slab every lane fences at system scope and the warp counts
-// itself in; the warp that completes the count fences again and writes the slab's arrival
-// flag on every rank with st.release.sys.  A reader that took the flag with ld.acquire.sys
-// therefore sees the slab.  No multicast load is issued: only stores use the multicast address.
-__device__ void push_b_slabs(const ShardParams& s, uint32_t wid, uint32_t nwarps, uint32_t lane,
-                             GemmStatus* status) {
+// Sender warps of the owner.  Warp `group` (0 .. SENDER_WARPS-1) of every CTA forms one
+// group with the same warp of all other CTAs (`nwarps` warps, this one is `wid`); group g
+// sends the slabs g, g + SENDER_WARPS, ...  Within a slab each warp takes whole rows
+// (consecutive lanes, consecutive 16-byte chunks).  After a slab every lane fences at system
+// scope and the warp counts itself in; the warp that completes the count fences again and
+// writes the slab's arrival flag on every rank with st.release.sys.  A reader that took the
+// flag with ld.acquire.sys therefore sees the slab.  A fence waits until the switch has
+// acknowledged the warp's stores, ten microseconds and more beside a running product, and a
+// warp that sent every slab would pay that once per slab, one after the other (measured: 32
+// MiB took 300 us that way); with the slabs dealt out to the groups, one group's fence runs
+// beside the other groups' stores.  No multicast load is issued: only stores use the
+// multicast address.
+__device__ void push_b_slabs(const ShardParams& s, uint32_t group, uint32_t wid, uint32_t nwarps,
+                             uint32_t lane, GemmStatus* status) {
   ShardControl* mine = shard_ctrl(s, s.rank);
   // the slot may be overwritten only when every rank has finished with the epoch that last used it
   bool ok = true;
@@ -467,7 +495,7 @@ __device__ void push_b_slabs(const ShardParams& s, uint32_t wid, uint32_t nwarps
     if (!ok && (atomicOr(&mine->gave_up, 2u) & 2u) == 0u) report(status, 4, lane, s.epoch, s.ack_needed);
     return;
   }
-  for (uint32_t slab = 0; slab < s.num_slabs; ++slab) {
+  for (uint32_t slab = group; slab < s.num_slabs; slab += SENDER_WARPS) {
     const uint32_t c0 = slab * s.slab_chunks;
     const uint32_t width = min(s.slab_chunks, s.row_chunks - c0);
     // The link only runs at full rate with enough bytes in flight (rate x latency is about
@@ -637,8 +665,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
           if (!__all_sync(0xffffffffu, here)) {
             if (lane == 0) {
-              *abort_flag = 1;
-              report(p.status, 6, slab, t, p.sh.epoch);
+              if (first_to_give_up(abort_flag)) report(p.status, 6, slab, t, p.sh.epoch);
             }
             alive = false;
             break;
@@ -651,8 +678,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) {
-            *abort_flag = 1;
-            report(p.status, 1, stage, t, rd);
+            if (first_to_give_up(abort_flag)) report(p.status, 1, stage, t, rd);
           }
           alive = false;
           break;
@@ -704,16 +730,14 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
         if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-          *abort_flag = 1;
-          report(p.status, 2, 0x100u | acc, t, 0);
+          if (first_to_give_up(abort_flag)) report(p.status, 2, 0x100u | acc, t, 0);
           break;
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
         for (uint32_t rd = 0; rd < rounds; ++rd) {
           if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
-            *abort_flag = 1;
-            report(p.status, 2, stage, t, rd);
+            if (first_to_give_up(abort_flag)) report(p.status, 2, stage, t, rd);
             alive = false;
             break;
           }
@@ -743,7 +767,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   } else if (GATED && warp >= 6) {
     // ------------------------------------------- sender warps (owner of B only)
     if (p.sh.rank == p.sh.owner)
-      push_b_slabs(p.sh, blockIdx.x * SENDER_WARPS + (warp - 6u), gridDim.x * SENDER_WARPS, lane, p.status);
+      push_b_slabs(p.sh, warp - 6u, blockIdx.x, gridDim.x, lane, p.status);
   } else {
     // ------------------------------------------------------------ epilogue
     const uint32_t quarter = warp & 3u;
@@ -757,8 +781,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) {
-          *abort_flag = 1;
-          report(p.status, 3, acc, t, 0);
+          if (first_to_give_up(abort_flag)) report(p.status, 3, acc, t, 0);
         }
         break;
       }
@@ -766,8 +789,6 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       const uint32_t row = (tm * 2 + cta_rank) * BLOCK_M + quarter * 32u + lane;
       const uint32_t col_tile = tn * BLOCK_N;
       const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * BLOCK_N;
-      float* c_row = p.C + uint64_t(row) * p.ldc;
-      const float* cin_row = p.c_in ? p.c_in + uint64_t(row) * p.ldc : nullptr;
 #pragma unroll 1
       for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
         const uint32_t col0 = col_tile + ch * 32u;
@@ -775,51 +796,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         uint32_t r[32];
         ptx::tmem_ld_32x32(taddr + ch * 32u, r);
         ptx::tmem_ld_wait();
-        if (row < p.M) {
-          if (col0 + 32u <= p.N && p.vec_store) {
-#pragma unroll
-            for (uint32_t j = 0; j < 32; j += 4) {
-              float4 v;
-              v.x = __uint_as_float(r[j + 0]) * p.alpha;
-              v.y = __uint_as_float(r[j + 1]) * p.alpha;
-              v.z = __uint_as_float(r[j + 2]) * p.alpha;
-              v.w = __uint_as_float(r[j + 3]) * p.alpha;
-              if (cin_row) {
-                const float4 o = *reinterpret_cast<const float4*>(cin_row + col0 + j);
-                v.x += p.beta * o.x;
-                v.y += p.beta * o.y;
-                v.z += p.beta * o.z;
-                v.w += p.beta * o.w;
-              }
-              if (p.bias) {
-                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-                v.x += b.x;
-                v.y += b.y;
-                v.z += b.z;
-                v.w += b.w;
-              }
-              if (p.act >= 0) {
-                v.x = apply_act(v.x, p.act, p.act_param);
-                v.y = apply_act(v.y, p.act, p.act_param);
-                v.z = apply_act(v.z, p.act, p.act_param);
-                v.w = apply_act(v.w, p.act, p.act_param);
-              }
-              *reinterpret_cast<float4*>(c_row + col0 + j) = v;
-            }
-          } else {
-#pragma unroll
-            for (uint32_t j = 0; j < 32; ++j) {
-              const uint32_t col = col0 + j;
-              if (col < p.N) {
-                float v = __uint_as_float(r[j]) * p.alpha;
-                if (cin_row) v += p.beta * cin_row[col];
-                if (p.bias) v += p.bias[col];
-                if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
-                c_row[col] = v;
-              }
-            }
-          }
-        }
+        epilogue_store32(p, r, row, col0);
       }
       ptx::tc_fence_before();
       __syncwarp();
@@ -847,58 +824,6 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
   // every load of B this CTA issued has landed and been consumed
   if (GATED && threadIdx.x == 0) shard_exit(p.sh, *abort_flag != 0u);
-}
-
-// One thread's 32 consecutive accumulator columns of one output row:
-// alpha/beta/bias/activation, then 16-byte stores (scalar at ragged edges).
-__device__ __forceinline__ void epilogue_store32(const KernelParams& p, const uint32_t (&r)[32],
-                                                 uint32_t row, uint32_t col0) {
-  if (row >= p.M || col0 >= p.N) return;
-  float* c_row = p.C + uint64_t(row) * p.ldc;
-  const float* cin_row = p.c_in ? p.c_in + uint64_t(row) * p.ldc : nullptr;
-  if (col0 + 32u <= p.N && p.vec_store) {
-#pragma unroll
-    for (uint32_t j = 0; j < 32; j += 4) {
-      float4 v;
-      v.x = __uint_as_float(r[j + 0]) * p.alpha;
-      v.y = __uint_as_float(r[j + 1]) * p.alpha;
-      v.z = __uint_as_float(r[j + 2]) * p.alpha;
-      v.w = __uint_as_float(r[j + 3]) * p.alpha;
-      if (cin_row) {
-        const float4 o = *reinterpret_cast<const float4*>(cin_row + col0 + j);
-        v.x += p.beta * o.x;
-        v.y += p.beta * o.y;
-        v.z += p.beta * o.z;
-        v.w += p.beta * o.w;
-      }
-      if (p.bias) {
-        const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-        v.x += b.x;
-        v.y += b.y;
-        v.z += b.z;
-        v.w += b.w;
-      }
-      if (p.act >= 0) {
-        v.x = apply_act(v.x, p.act, p.act_param);
-        v.y = apply_act(v.y, p.act, p.act_param);
-        v.z = apply_act(v.z, p.act, p.act_param);
-        v.w = apply_act(v.w, p.act, p.act_param);
-      }
-      *reinterpret_cast<float4*>(c_row + col0 + j) = v;
-    }
-  } else {
-#pragma unroll
-    for (uint32_t j = 0; j < 32; ++j) {
-      const uint32_t col = col0 + j;
-      if (col < p.N) {
-        float v = __uint_as_float(r[j]) * p.alpha;
-        if (cin_row) v += p.beta * cin_row[col];
-        if (p.bias) v += p.bias[col];
-        if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
-        c_row[col] = v;
-      }
-    }
-  }
 }
 
 // The same 32 x 32 block of results, written so that a warp's store instruction
@@ -986,28 +911,6 @@ __device__ __forceinline__ void epilogue_store32_coalesced(const KernelParams& p
   __syncwarp();  // the staging tile may be overwritten by the next block
 }
 
-// Same values, but written to a 32-row x 128-byte staging tile in shared memory
-// (rows = this warp's 32 output rows) in the 128-byte-swizzle order a TMA store
-// expects, so that the store to C moves whole 128-byte lines.  No beta term.
-__device__ __forceinline__ void epilogue_stage32(const KernelParams& p, const uint32_t (&r)[32],
-                                                 uint32_t col0, uint32_t staging, uint32_t lane) {
-#pragma unroll
-  for (uint32_t j = 0; j < 8; ++j) {
-    float v[4];
-#pragma unroll
-    for (uint32_t e = 0; e < 4; ++e) {
-      const uint32_t col = col0 + j * 4 + e;
-      float x = __uint_as_float(r[j * 4 + e]) * p.alpha;
-      if (p.bias && col < p.N) x += __ldg(p.bias + col);
-      if (p.act >= 0) x = apply_act(x, p.act, p.act_param);
-      v[e] = x;
-    }
-    const uint32_t addr = staging + lane * 128u + ((j ^ (lane & 7u)) << 4);
-    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[0]), "f"(v[1]),
-                 "f"(v[2]), "f"(v[3]) : "memory");
-  }
-}
-
 // ---------------------------------------------------------------------------
 // fp16 kernel for the largest problems: CTA pairs on 512 x 256 tiles.
 //
@@ -1026,7 +929,6 @@ template <int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
                         const __grid_constant__ CUtensorMap tm_b,
-                        const __grid_constant__ CUtensorMap tm_c,
                         const __grid_constant__ KernelParams p) {
   constexpr uint32_t BN = 256;
   constexpr uint32_t B_TILE_BYTES = (BN / 2) * SLAB_ROW_BYTES;
@@ -1047,9 +949,6 @@ gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
   auto tempty_bar = [&](uint32_t a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 B), 1024-byte aligned
-  const uint32_t staging_base = bar_base + 1024u;
-
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t cta_rank = ptx::cluster_ctarank();
@@ -1101,8 +1000,7 @@ gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) {
-            *abort_flag = 1;
-            report(p.status, 1, stage, t, kb);
+            if (first_to_give_up(abort_flag)) report(p.status, 1, stage, t, kb);
           }
           alive = false;
           break;
@@ -1147,8 +1045,7 @@ gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
         const uint32_t tparity = local & 1u;
         for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
           if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
-            *abort_flag = 1;
-            report(p.status, 2, stage, t, kb);
+            if (first_to_give_up(abort_flag)) report(p.status, 2, stage, t, kb);
             alive = false;
             break;
           }
@@ -1163,8 +1060,7 @@ gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
             if (kb == 0) {
               // accumulator u must have been drained of the previous tile
               if (!ptx::mbar_wait(tempty_bar(u), tparity ^ 1u, abort_flag)) {
-                *abort_flag = 1;
-                report(p.status, 2, 0x100u | u, t, 0);
+                if (first_to_give_up(abort_flag)) report(p.status, 2, 0x100u | u, t, 0);
                 alive = false;
                 break;
               }
@@ -1201,8 +1097,7 @@ gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) {
-            *abort_flag = 1;
-            report(p.status, 3, u, t, 0);
+            if (first_to_give_up(abort_flag)) report(p.status, 3, u, t, 0);
           }
           alive = false;
           break;
@@ -1210,37 +1105,14 @@ gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
         ptx::tc_fence_after();
         const uint32_t row0 = (tm * 4 + u * 2 + cta_rank) * BLOCK_M + quarter * 32u;
         const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + u * BN;
-        if (p.tma_store) {
-          // registers -> swizzled staging tile -> TMA store of whole 128-byte lines
-          // (TMA clips rows >= M and columns >= N)
 #pragma unroll 1
-          for (uint32_t ch = 0; ch < BN / 32; ++ch) {
-            const uint32_t col0 = tn * BN + ch * 32u;
-            if (col0 >= p.N) break;
-            const uint32_t staging = staging_base + ((warp - 2u) * 2u + (ch & 1u)) * 4096u;
-            uint32_t r[32];
-            ptx::tmem_ld_32x32(taddr + ch * 32u, r);
-            if (lane == 0) ptx::tma_store_wait_read<1>();  // the buffer used two chunks ago is free
-            __syncwarp();
-            ptx::tmem_ld_wait();
-            epilogue_stage32(p, r, col0, staging, lane);
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0 && row0 < p.M) {
-              ptx::tma_store_2d(&tm_c, int32_t(col0), int32_t(row0), staging);
-              ptx::tma_store_commit();
-            }
-          }
-        } else {
-#pragma unroll 1
-          for (uint32_t ch = 0; ch < BN / 32; ++ch) {
-            const uint32_t col0 = tn * BN + ch * 32u;
-            if (col0 >= p.N) break;
-            uint32_t r[32];
-            ptx::tmem_ld_32x32(taddr + ch * 32u, r);
-            ptx::tmem_ld_wait();
-            epilogue_store32(p, r, row0 + lane, col0);
-          }
+        for (uint32_t ch = 0; ch < BN / 32; ++ch) {
+          const uint32_t col0 = tn * BN + ch * 32u;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr + ch * 32u, r);
+          ptx::tmem_ld_wait();
+          epilogue_store32(p, r, row0 + lane, col0);
         }
         ptx::tc_fence_before();
         __syncwarp();
@@ -1250,7 +1122,6 @@ gemm_f16_pair512_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
 
   // ---------------------------------------------------------------- teardown
-  if (warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();  // staging tiles fully read and written out
   ptx::tc_fence_before();
   __syncthreads();
   if (*abort_flag) {
@@ -1401,8 +1272,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) {
-            *abort_flag = 1;
-            report(p.status, 1, stage, t, kb);
+            if (first_to_give_up(abort_flag)) report(p.status, 1, stage, t, kb);
           }
           alive = false;
           break;
@@ -1451,8 +1321,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
           const uint32_t acc = chunk & 1u;
           const uint32_t acc_phase = (chunk >> 1) & 1u;
           if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-            *abort_flag = 1;
-            report(p.status, 2, 0x100u | acc, t, kb0);
+            if (first_to_give_up(abort_flag)) report(p.status, 2, 0x100u | acc, t, kb0);
             alive = false;
             break;
           }
@@ -1461,8 +1330,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
           const uint32_t kb_end = min(kb0 + CHUNK_KB, kb_hi);
           for (uint32_t kb = kb0; kb < kb_end; ++kb) {
             if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
-              *abort_flag = 1;
-              report(p.status, 2, stage, t, kb);
+              if (first_to_give_up(abort_flag)) report(p.status, 2, stage, t, kb);
               alive = false;
               break;
             }
@@ -1515,8 +1383,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) {
-            *abort_flag = 1;
-            report(p.status, 3, acc, t, c);
+            if (first_to_give_up(abort_flag)) report(p.status, 3, acc, t, c);
           }
           alive = false;
           break;
@@ -1548,8 +1415,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
               outcome = (before + 1u == p.splits) ? 1u : 0u;
               if (outcome) p.sk_count[t] = 0u;  // nobody else touches this tile again: ready for the next launch
             } else {
-              *abort_flag = 1;
-              report(p.status, 3, 0x200u, t, 0);
+              if (first_to_give_up(abort_flag)) report(p.status, 3, 0x200u, t, 0);
             }
             *sk_flag = outcome;
             ptx::mbar_arrive(sk_lead_bar);
@@ -1561,8 +1427,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
         const uint32_t outcome = *sk_flag;
         if (!ok || outcome == 2u) {
           if (lane == 0 && !ok) {
-            *abort_flag = 1;
-            report(p.status, 3, 0x201u, t, 0);
+            if (first_to_give_up(abort_flag)) report(p.status, 3, 0x201u, t, 0);
           }
           alive = false;
           break;
@@ -1761,8 +1626,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) {
-            *abort_flag = 1;
-            report(p.status, 1, stage, t, kb);
+            if (first_to_give_up(abort_flag)) report(p.status, 1, stage, t, kb);
           }
           alive = false;
           break;
@@ -1804,8 +1668,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
           const uint32_t acc = chunk & 1u;
           const uint32_t acc_phase = (chunk >> 1) & 1u;
           if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-            *abort_flag = 1;
-            report(p.status, 2, 0x100u | acc, t, kb0);
+            if (first_to_give_up(abort_flag)) report(p.status, 2, 0x100u | acc, t, kb0);
             alive = false;
             break;
           }
@@ -1814,8 +1677,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
           const uint32_t kb_end = min(kb0 + CHUNK_KB, p.num_kblocks);
           for (uint32_t kb = kb0; kb < kb_end; ++kb) {
             if (!ready && !ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
-              *abort_flag = 1;
-              report(p.status, 2, stage, t, kb);
+              if (first_to_give_up(abort_flag)) report(p.status, 2, stage, t, kb);
               alive = false;
               break;
             }
@@ -1865,8 +1727,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) {
-            *abort_flag = 1;
-            report(p.status, 3, acc, t, c);
+            if (first_to_give_up(abort_flag)) report(p.status, 3, acc, t, c);
           }
           alive = false;
           break;
@@ -2081,14 +1942,6 @@ bool make_map_kgroup(CUtensorMap* map, const void* base, uint64_t inner, uint64_
   return r == CUDA_SUCCESS;
 }
 
-bool box3d_enabled() {
-  static const bool on = [] {
-    const char* e = std::getenv("GONNGPU_BOX3D");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
-
 // The tensor map(s) of one operand (plane1 only for the fp32 path) and, where the operand is
 // MN-major with a pitch of whole slab rows, the switch of its plan to single 3-D boxes.
 bool make_operand_maps(bool f32, const GemmOperand& op, uint64_t inner, uint64_t outer,
@@ -2096,13 +1949,13 @@ bool make_operand_maps(bool f32, const GemmOperand& op, uint64_t inner, uint64_t
                        uint32_t kgroup = 0) {
   const uint32_t row_elems = SLAB_ROW_BYTES / (f32 ? 4 : 2);
   plan.kgroup = 0;
-  if (!f32 && !op.mn_major && kgroup > 1 && inner % row_elems == 0 && box3d_enabled() &&
+  if (!f32 && !op.mn_major && kgroup > 1 && inner % row_elems == 0 &&
       make_map_kgroup(m0, op.plane0, inner, outer, op.pitch, box_rows, kgroup)) {
     plan.kgroup = kgroup;
     plan.box3d = 0;
     return true;
   }
-  if (op.mn_major && plan.slabs > 1 && op.pitch % row_elems == 0 && box3d_enabled()) {
+  if (op.mn_major && plan.slabs > 1 && op.pitch % row_elems == 0) {
     if (make_map_3d(m0, f32, op.plane0, inner, outer, op.pitch, box_rows, plan.slabs) &&
         (!m1 || make_map_3d(m1, f32, op.plane1, inner, outer, op.pitch, box_rows, plan.slabs))) {
       plan.box3d = 1;
@@ -2240,10 +2093,10 @@ const char* launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, co
   return nullptr;
 }
 
-const char* launch_pair512(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
-                           const KernelParams& kp, uint32_t pairs, cudaStream_t stream) {
+const char* launch_pair512(const CUtensorMap& ma, const CUtensorMap& mb, const KernelParams& kp,
+                           uint32_t pairs, cudaStream_t stream) {
   constexpr uint32_t stage = 2 * A_TILE_BYTES + 128 * SLAB_ROW_BYTES;
-  constexpr uint32_t extra = 1024 /*align*/ + 1024 /*barriers*/ + 4 * 2 * 4096 /*epilogue staging*/;
+  constexpr uint32_t extra = 1024 /*align*/ + 1024 /*barriers*/;
   constexpr int STAGES = int((SMEM_LIMIT - extra) / stage);
   constexpr uint32_t smem = STAGES * stage + extra;
   static_assert(STAGES >= 3 && smem <= SMEM_LIMIT, "pair512 kernel shared memory");
@@ -2257,7 +2110,7 @@ const char* launch_pair512(const CUtensorMap& ma, const CUtensorMap& mb, const C
       return "cudaFuncSetAttribute(max dynamic shared memory) failed";
     attr_done_dev[dev & 63] = true;
   }
-  if (launch_kernel(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ma, mb, mc, kp) != cudaSuccess) {
+  if (launch_kernel(kern, dim3(2 * pairs), dim3(NUM_THREADS), smem, stream, ma, mb, kp) != cudaSuccess) {
     cudaGetLastError();
     return "GEMM pair512 kernel launch failed";
   }
@@ -2290,28 +2143,7 @@ const char* launch_gemm_pair(uint32_t M, uint32_t N, uint32_t K, int bn, bool ta
     return "cuTensorMapEncodeTiled failed";
   const uint32_t limit = uint32_t(max_ctas > 0 ? max_ctas : sm_count) / 2;
   const uint32_t pairs = std::max<uint32_t>(1u, std::min<uint32_t>(kp.num_tiles, limit));
-  if (tall) {
-    // C as a TMA store target: boxes of 32 columns x 32 rows, 128-byte swizzle.
-    CUtensorMap mc;
-    std::memset(&mc, 0, sizeof(mc));
-    kp.tma_store = 0;
-    static const bool want_tma_store = [] {
-      const char* e = std::getenv("GONNGPU_TMA_STORE");  // experiment switch, off by default
-      return e && std::atoi(e) != 0;
-    }();
-    if (want_tma_store && kp.vec_store && !kp.c_in) {
-      EncodeTiledFn fn = encode_tiled();
-      cuuint64_t dims[2] = {N, M};
-      cuuint64_t strides[1] = {kp.ldc * 4};
-      cuuint32_t box[2] = {32, 32};
-      cuuint32_t estr[2] = {1, 1};
-      if (fn && fn(&mc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, kp.C, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
-        kp.tma_store = 1;
-    }
-    return launch_pair512(ma, mb, mc, kp, pairs, stream);
-  }
+  if (tall) return launch_pair512(ma, mb, kp, pairs, stream);
   if (gated) return launch_pair_variant<256, 2, true>(ma, mb, kp, pairs, stream);
   if (bn == 256) return launch_pair_variant<256, 2>(ma, mb, kp, pairs, stream);
   return launch_pair_variant<128, 2>(ma, mb, kp, pairs, stream);

@@ -131,10 +131,19 @@ class Tensor {
     getGlobalMemoryPool().trackAllocation(p, int64_t(Data.size() * sizeof(float)));
   }
 
-  // tensor.go:154-184
+  // Number of elements the shape describes.
+  size_t Size() const {
+    size_t n = 1;
+    for (int d : Shape) n *= size_t(d);
+    return n;
+  }
+
+  // tensor.go:154-184.  A result tensor made on the device (NewDeviceTensor) gets its host
+  // slice here, the first time someone asks for the values.
   void RetrieveCPU() {
     if (!isOnGPU_) return;
     if (!gpuPtr_) throw gonngpu::Error("tensor is marked as on GPU but has no GPU pointer");
+    if (Data.size() != Size()) Data.resize(Size());
     CError err{nullptr};
     const int rc =
         retrieve_gpu_buffer_data(gpuPtr_, Data.data(), long(Data.size() * sizeof(float)), &err);
@@ -158,7 +167,7 @@ class Tensor {
     gpuPtr_ = p;
     devicePtr_ = d;
     isOnGPU_ = true;
-    getGlobalMemoryPool().trackAllocation(p, int64_t(Data.size() * sizeof(float)));
+    getGlobalMemoryPool().trackAllocation(p, int64_t(Size() * sizeof(float)));
   }
 
   GPUPtr GPUPointer() const { return gpuPtr_; }        // tensor.go:206 (GPUPtr)
@@ -187,6 +196,24 @@ inline TensorPtr NewTensor(std::vector<int> shape, std::vector<float> data) {
     throw gonngpu::Error("data length (" + std::to_string(data.size()) +
                          ") does not match shape dimensions (" + std::to_string(size) + ")");
   return std::make_shared<Tensor>(std::move(shape), std::move(data));
+}
+
+// A result tensor that starts its life on the device: the buffer is allocated there and no
+// host slice is made (or zero-filled) until RetrieveCPU.  The reference's operations build
+// their results with make([]float32, n) + NewTensor + EnsureGPU (gpu/matrix/matrix.go:61-79);
+// by its own protocol Data of such a tensor is not to be read before RetrieveCPU, so the
+// zero-filled slice is only a cost: 17 MB per training step of the small MLP.
+inline TensorPtr NewDeviceTensor(std::vector<int> shape) {
+  auto t = std::make_shared<Tensor>(std::move(shape), std::vector<float>());
+  CError err{nullptr};
+  GPUPtr p = nullptr;
+  const size_t bytes = t->Size() * sizeof(float);
+  const int rc = gonngpu_alloc_device_buffer(long(bytes ? bytes : 4), &p, &err);
+  if (rc != 0)
+    throw gonngpu::Error("failed to create GPU buffer (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  t->AdoptGPU(p, nullptr);
+  return t;
 }
 
 }  // namespace tensor
@@ -361,7 +388,10 @@ inline TensorPtr MatMul(const TensorPtr& A, const TensorPtr& B) {
                          std::to_string(A->Shape[1]) + ") != B rows (" +
                          std::to_string(B->Shape[0]) + ")");
   const int rows = A->Shape[0], cols = B->Shape[1];
-  TensorPtr result = tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols));
+  // (unified mode copies the host slice into the shared buffer, so it must exist there)
+  TensorPtr result = detail::global_matrix_device()
+                         ? tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols))
+                         : tensor::NewDeviceTensor({rows, cols});
   ensureUnifiedGPU(A);
   ensureUnifiedGPU(B);
   ensureUnifiedGPU(result);
@@ -379,7 +409,7 @@ inline TensorPtr MatMul(const TensorPtr& A, const TensorPtr& B) {
 inline TensorPtr Transpose(const TensorPtr& A) {
   if (A->Shape.size() != 2) throw gonngpu::Error("Transpose requires 2D tensor (matrix)");
   const int orows = A->Shape[1], ocols = A->Shape[0];
-  TensorPtr result = tensor::NewTensor({orows, ocols}, std::vector<float>(size_t(orows) * ocols));
+  TensorPtr result = tensor::NewDeviceTensor({orows, ocols});
   A->EnsureGPU();
   result->EnsureGPU();
   CError err{nullptr};
@@ -398,7 +428,7 @@ inline TensorPtr AddBroadcast(const TensorPtr& A, const TensorPtr& B) {
   if (A->Shape.size() != 2 || B->Shape.size() != 2)
     throw gonngpu::Error("Add requires 2D tensors (matrices)");
   const int rows = std::max(A->Shape[0], B->Shape[0]), cols = std::max(A->Shape[1], B->Shape[1]);
-  TensorPtr result = tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols));
+  TensorPtr result = tensor::NewDeviceTensor({rows, cols});
   A->EnsureGPU();
   B->EnsureGPU();
   result->EnsureGPU();
@@ -421,7 +451,10 @@ using ScalarEntry = int (*)(GPUPtr, long, long, float, GPUPtr, DevicePtr, CError
 inline TensorPtr same_shape_op(const TensorPtr& A, const TensorPtr& B, BinaryEntry entry,
                                const char* failed) {
   const int rows = A->Shape[0], cols = A->Shape[1];
-  TensorPtr result = tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols));
+  // the divide stops at the first zero divisor and leaves the rest of the (zeroed) result as it is
+  TensorPtr result = entry == perform_mps_matrix_element_divide
+                         ? tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols))
+                         : tensor::NewDeviceTensor({rows, cols});
   A->EnsureGPU();
   B->EnsureGPU();
   result->EnsureGPU();
@@ -447,7 +480,7 @@ inline TensorPtr scalar_op(const TensorPtr& A, float scalar, ScalarEntry entry, 
                            const char* failed) {
   if (A->Shape.size() != 2) throw gonngpu::Error(std::string(op) + " requires 2D tensor (matrix)");
   const int rows = A->Shape[0], cols = A->Shape[1];
-  TensorPtr result = tensor::NewTensor({rows, cols}, std::vector<float>(size_t(rows) * cols));
+  TensorPtr result = tensor::NewDeviceTensor({rows, cols});
   A->EnsureGPU();
   result->EnsureGPU();
   CError err{nullptr};
@@ -508,7 +541,7 @@ inline TensorPtr ActivationForward(const TensorPtr& input, ActivationType type, 
     throw gonngpu::Error("softmax currently supports only 1D and 2D tensors");
   long n = 1;
   for (int d : input->Shape) n *= d;
-  TensorPtr result = tensor::NewTensor(input->Shape, std::vector<float>(size_t(n)));
+  TensorPtr result = tensor::NewDeviceTensor(input->Shape);
   input->EnsureGPU();
   result->EnsureGPU();
   GPUPtr in = input->GPUPointer(), out = result->GPUPointer();
@@ -550,7 +583,7 @@ inline TensorPtr ActivationBackward(const TensorPtr& gradOutput, const TensorPtr
       throw gonngpu::Error("gradient and activation output shape mismatch at dimension " + std::to_string(i));
   long n = 1;
   for (int d : gradOutput->Shape) n *= d;
-  TensorPtr result = tensor::NewTensor(gradOutput->Shape, std::vector<float>(size_t(n)));
+  TensorPtr result = tensor::NewDeviceTensor(gradOutput->Shape);
   gradOutput->EnsureGPU();
   activationOutput->EnsureGPU();
   result->EnsureGPU();
@@ -648,7 +681,7 @@ inline TensorPtr FusedLinearActivationForward(const std::vector<TensorPtr>& inpu
   X->EnsureGPU();
   W->EnsureGPU();
   if (bias) bias->EnsureGPU();
-  TensorPtr Y = tensor::NewTensor({batch, out}, std::vector<float>(size_t(batch) * out));
+  TensorPtr Y = tensor::NewDeviceTensor({batch, out});
   Y->EnsureGPU();
   int code = 0;
   float alpha = 0.f;
@@ -677,7 +710,7 @@ inline TensorPtr MatMulTransposed(const TensorPtr& A, bool transA, const TensorP
   if (K != Kb)
     throw gonngpu::Error("incompatible matrix dimensions for multiplication: A columns (" +
                          std::to_string(K) + ") != B rows (" + std::to_string(Kb) + ")");
-  TensorPtr result = tensor::NewTensor({M, N}, std::vector<float>(size_t(M) * N));
+  TensorPtr result = tensor::NewDeviceTensor({M, N});
   A->EnsureGPU();
   B->EnsureGPU();
   result->EnsureGPU();
@@ -703,7 +736,7 @@ inline TensorPtr OptimizedBatchMatMul(const TensorPtr& A, const TensorPtr& B) {
   if (K != K2)
     throw gonngpu::Error("matrix dimensions don't match: K=" + std::to_string(K) +
                          " vs K2=" + std::to_string(K2));
-  TensorPtr out = tensor::NewTensor({batch, M, N}, std::vector<float>(size_t(batch) * M * N));
+  TensorPtr out = tensor::NewDeviceTensor({batch, M, N});
   A->EnsureGPU();
   B->EnsureGPU();
   out->EnsureGPU();
@@ -732,9 +765,9 @@ inline LinearGradients LinearBackward(const TensorPtr& input, const TensorPtr& w
     throw gonngpu::Error("LinearBackward: shapes of input, weight and gradOutput do not match");
   const int batch = input->Shape[0], in = input->Shape[1], out = weight->Shape[1];
   LinearGradients g;
-  g.Input = tensor::NewTensor({batch, in}, std::vector<float>(size_t(batch) * in));
-  g.Weight = tensor::NewTensor({in, out}, std::vector<float>(size_t(in) * out));
-  g.Bias = tensor::NewTensor({out}, std::vector<float>(size_t(out)));
+  g.Input = tensor::NewDeviceTensor({batch, in});
+  g.Weight = tensor::NewDeviceTensor({in, out});
+  g.Bias = tensor::NewDeviceTensor({out});
   input->EnsureGPU();
   weight->EnsureGPU();
   gradOutput->EnsureGPU();
@@ -770,7 +803,7 @@ inline TensorPtr ForwardFloat16(const TensorPtr& input, const TensorPtr& weights
                          std::to_string(input->Shape[1]) + ") != B rows (" +
                          std::to_string(weights->Shape[0]) + ")");
   const int M = input->Shape[0], N = weights->Shape[1];
-  TensorPtr result = tensor::NewTensor({M, N}, std::vector<float>(size_t(M) * N));
+  TensorPtr result = tensor::NewDeviceTensor({M, N});
   input->EnsureGPU();
   weights->EnsureGPU();
   if (bias) bias->EnsureGPU();

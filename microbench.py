@@ -1,13 +1,16 @@
 """Per-configuration timings of the dense path on one GPU (device-resident inputs).
 
-    python go-nngpu_b200/microbench.py [--config c1|c2|c2nn|transpose|c3|c4|gonum|elementwise|all] [--iters N] [--cpu]
+    python microbench.py [--config c1|c2|c2nn|transpose|c3|c4|gonum|elementwise|all] [--iters N] [--cpu] [--fresh]
 
 Prints one JSON line per measured operation: time, TFLOP/s or GB/s, and the
 fraction of the measured peaks when MEASURED_PEAKS.json lies beside the
 repository root.  Inputs are the seeded synthetic matrices of the benchmark
 configurations (numpy PCG64).  Timing: `iters` asynchronous calls on the
 library's stream between two synchronisations; operands rotate over several
-buffer sets where one set would fit in the 126 MB L2.
+buffer sets where one set would fit in the 126 MB L2.  By default the converted
+operand planes of a GEMM are cached between calls (weights of a layer); with
+--fresh both operands are marked modified before every call, so every call pays
+its fp32 -> fp16 / tf32 pre-pass as a product of new activations does.
 """
 import argparse
 import json
@@ -18,15 +21,16 @@ import time
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.join(HERE, "go-nngpu_b200"))
 import gonngpu as g  # noqa: E402
 
 
 CPU_LEG = False
+FRESH = False
 
 
 def peaks():
-    path = os.path.join(os.path.dirname(HERE), "MEASURED_PEAKS.json")
+    path = os.path.join(HERE, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
@@ -71,8 +75,14 @@ def gemm_case(name, A, B, ta, tb, precision, iters):
     N = B.shape[0] if tb else B.shape[1]
     a, b = g.Buffer.from_host(A), g.Buffer.from_host(B)
     c = g.Buffer.empty(M * N * 4)
-    dt = timed(lambda s: g.matmul_ex(a, A.shape, ta, b, B.shape, tb, c, (M, N), precision=precision), iters)
-    extra = {}
+    def call(_):
+        if FRESH:
+            g.lib().gonngpu_mark_modified(a.handle)
+            g.lib().gonngpu_mark_modified(b.handle)
+        g.matmul_ex(a, A.shape, ta, b, B.shape, tb, c, (M, N), precision=precision)
+
+    dt = timed(call, iters)
+    extra = {"operands": "fresh (pre-pass inside every call)" if FRESH else "converted planes cached"}
     if precision == g.FP32_3XTF32:
         # three tf32 MMAs are issued per useful product; 1100 TFLOP/s is the nominal dense tf32 rate
         issued = 3 * 2.0 * M * N * K / dt / 1e12
@@ -152,6 +162,15 @@ def config3(iters):
     emit("c3 MLP step 512x(784-1024-1024-10) fwd+bwd, 6 fused calls", dt, flops=flops)
     for x in w + b + h + dh + dw + db:
         x.release()
+    # the same step as a caller of the layer stack drives it (C++ mirror of Sequential)
+    import subprocess
+    import tempfile
+    pkg = os.path.join(HERE, "go-nngpu_b200")
+    exe = os.path.join(tempfile.mkdtemp(), "mlp_step")
+    subprocess.run(["g++", "-std=c++17", "-O2", "-o", exe, os.path.join(pkg, "host", "mlp_step.cpp"),
+                    "-L" + pkg, "-lgonngpu_cuda", "-Wl,-rpath," + pkg], check=True)
+    for fuse in ("1", "0"):
+        print(subprocess.run([exe, str(iters), fuse], capture_output=True, text=True).stdout.strip(), flush=True)
 
 
 def config4(iters):
@@ -229,9 +248,12 @@ def main():
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--cpu", action="store_true",
                     help="also time the float64 product on the host cores and report the error against it")
+    ap.add_argument("--fresh", action="store_true",
+                    help="mark both GEMM operands modified before every call (pre-pass inside the timing)")
     args = ap.parse_args()
-    global CPU_LEG
+    global CPU_LEG, FRESH
     CPU_LEG = args.cpu
+    FRESH = args.fresh
     assert g.lib().gonngpu_set_device(0) == 0, "no usable B200"
     run = {"c1": lambda: config1(args.iters), "c2": lambda: config2(args.iters),
            "c2nn": lambda: config2(args.iters, transposes=False),

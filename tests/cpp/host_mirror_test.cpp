@@ -405,8 +405,9 @@ static void mlp_step_through_layers(bool fuse) {
   for (size_t i = 0; i < h1.size(); ++i) flips += (h1dev->Data[i] > 0) != (h1[i] > 0);
   for (size_t i = 0; i < h2.size(); ++i) flips += (h2dev->Data[i] > 0) != (h2[i] > 0);
   CHECK(flips <= 8);  // only elements at rounding distance from zero may differ
-  for (size_t i = 0; i < h1.size(); ++i) h1[i] = h1dev->Data[i] > 0 ? h1[i] : 0.0;
-  for (size_t i = 0; i < h2.size(); ++i) h2[i] = h2dev->Data[i] > 0 ? h2[i] : 0.0;
+  std::vector<char> on1(h1.size()), on2(h2.size());  // the derivative the device applies
+  for (size_t i = 0; i < h1.size(); ++i) on1[i] = h1dev->Data[i] > 0;
+  for (size_t i = 0; i < h2.size(); ++i) on2[i] = h2dev->Data[i] > 0;
   (void)net.Forward(tX);  // the layers' caches belong to the net's own forward pass again
   gin = net.Backward(tensor::NewTensor({batch, d3}, dY));
   gin->RetrieveCPU();
@@ -433,10 +434,10 @@ static void mlp_step_through_layers(bool fuse) {
   std::vector<double> Xd(X.begin(), X.end());
   backward(g3, h2, l3->Weight->Data, batch, d2, d3, dW3, db3, dX3);
   for (size_t i = 0; i < dX3.size(); ++i)
-    if (!(h2[i] > 0)) dX3[i] = 0.0;
+    if (!on2[i]) dX3[i] = 0.0;
   backward(dX3, h1, l2->Weight->Data, batch, d1, d2, dW2, db2, dX2);
   for (size_t i = 0; i < dX2.size(); ++i)
-    if (!(h1[i] > 0)) dX2[i] = 0.0;
+    if (!on1[i]) dX2[i] = 0.0;
   backward(dX2, Xd, l1->Weight->Data, batch, d0, d1, dW1, db1, dX1);
   auto grads = net.GetGradients();
   CHECK(grads.size() == 6);

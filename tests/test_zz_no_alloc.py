@@ -54,6 +54,8 @@ def test_static_scratch_matmul_matches_allocating_entry_twice(gpu):
     for (A, B, a, b, c, pa, pb, pc) in bufs:
         gpu.matmul_f16_static_scratch(pa, A.shape, pb, B.shape, pc)
         c.upload(np.zeros((A.shape[0], B.shape[1]), np.float32))   # the checked results come from the calls below
+    import gc
+    gc.collect()                                       # buffers of earlier tests are released now, not mid-measurement
     hbm_before = gpu.stats()["hbm_bytes"]
     free_before = _free_bytes()
     for (A, B, a, b, c, pa, pb, pc) in bufs:           # two calls in a row
