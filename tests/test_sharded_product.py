@@ -165,7 +165,7 @@ def test_rank_whose_b_never_arrives_gives_up_and_reports(gpu):
     assert ei.value.code == -6 and "role 6" in ei.value.message
     assert 1.0 < dt < 20.0
     st = g.last_kernel_status()
-    assert st[0] == 6 and st[1] == 0 and st[3] == 3                 # slab 0, epoch 3
+    assert st[0] == 6 and st[1] in (0, 1) and st[3] == 3            # one of the two slabs, epoch 3
     w = grp.words()
     assert not w.any()                                              # no flag, no acknowledgement, scratch zero
     # now the data "arrives": B into slot 1 (epoch 3), both slabs flagged
