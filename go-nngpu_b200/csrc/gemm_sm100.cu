@@ -37,9 +37,10 @@ constexpr uint32_t SLAB_ROW_BYTES = 128;             // one swizzle row
 constexpr uint32_t A_TILE_BYTES = BLOCK_M * SLAB_ROW_BYTES;  // 16 KiB per plane per k block
 constexpr uint32_t KSTEPS = 4;                       // MMAs (per product) per k block
 constexpr uint32_t NUM_THREADS = 192;
-constexpr uint32_t SENDER_WARPS = 4;     // extra warps of the row-sharded product that move B
+constexpr uint32_t SENDER_WARPS = 8;     // extra warps of the row-sharded product that move B
+constexpr uint32_t SENDER_GROUPS = 4;    // the slabs are dealt out to this many groups of sender warps
 constexpr uint32_t GATED_THREADS = NUM_THREADS + 32 * SENDER_WARPS;
-constexpr uint32_t SENDER_DEPTH = 8;     // 16-byte loads a sender lane keeps in flight
+constexpr uint32_t SENDER_DEPTH = 16;    // 16-byte loads a sender lane keeps in flight
 constexpr uint32_t SMEM_LIMIT = 227 * 1024;
 
 // How one operand's k-block tile is fetched by TMA and described to the MMA.
@@ -472,9 +473,8 @@ __device__ __forceinline__ ShardControl* shard_ctrl(const ShardParams& s, uint32
   return reinterpret_cast<ShardControl*>(static_cast<char*>(s.bases[rank]) + s.ctrl_offset);
 }
 
-// Sender warps of the owner.  Warp `group` (0 .. SENDER_WARPS-1) of every CTA forms one
-// group with the same warp of all other CTAs (`nwarps` warps, this one is `wid`); group g
-// sends the slabs g, g + SENDER_WARPS, ...  Within a slab each warp takes whole rows
+// Sender warps of the owner.  The sender warps of all CTAs form SENDER_GROUPS groups (`nwarps`
+// warps each, this one is `wid` of group `group`); group g sends the slabs g, g + SENDER_GROUPS, ...  Within a slab each warp takes whole rows
 // (consecutive lanes, consecutive 16-byte chunks).  After a slab every lane fences at system
 // scope and the warp counts itself in; the warp that completes the count fences again and
 // writes the slab's arrival flag on every rank with st.release.sys.  A reader that took the
@@ -495,7 +495,7 @@ __device__ void push_b_slabs(const ShardParams& s, uint32_t group, uint32_t wid,
     if (!ok && (atomicOr(&mine->gave_up, 2u) & 2u) == 0u) report(status, 4, lane, s.epoch, s.ack_needed);
     return;
   }
-  for (uint32_t slab = group; slab < s.num_slabs; slab += SENDER_WARPS) {
+  for (uint32_t slab = group; slab < s.num_slabs; slab += SENDER_GROUPS) {
     const uint32_t c0 = slab * s.slab_chunks;
     const uint32_t width = min(s.slab_chunks, s.row_chunks - c0);
     // The link only runs at full rate with enough bytes in flight (rate x latency is about
@@ -767,7 +767,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   } else if (GATED && warp >= 6) {
     // ------------------------------------------- sender warps (owner of B only)
     if (p.sh.rank == p.sh.owner)
-      push_b_slabs(p.sh, warp - 6u, blockIdx.x, gridDim.x, lane, p.status);
+      push_b_slabs(p.sh, (warp - 6u) % SENDER_GROUPS, blockIdx.x * (SENDER_WARPS / SENDER_GROUPS) + (warp - 6u) / SENDER_GROUPS,
+                   gridDim.x * (SENDER_WARPS / SENDER_GROUPS), lane, p.status);
   } else {
     // ------------------------------------------------------------ epilogue
     const uint32_t quarter = warp & 3u;
