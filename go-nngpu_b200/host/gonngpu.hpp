@@ -820,6 +820,32 @@ inline TensorPtr ForwardFloat16(const TensorPtr& input, const TensorPtr& weights
   return result;
 }
 
+// ForwardFloat16's product (fp16-precision inputs, fp32 accumulate) for a tall A, split by rows
+// over the GPUs this process sees: the multi-GPU form of the same call, straight from and
+// into the tensors' host slices (gonngpu_matmul_sharded).  n_devices 0 = every visible GPU.
+// The reference has one device and no counterpart.
+inline TensorPtr ForwardFloat16Sharded(const TensorPtr& input, const TensorPtr& weights, int n_devices = 0,
+                                       bool round_to_nearest = false) {
+  if (input->Shape.size() != 2 || weights->Shape.size() != 2)
+    throw gonngpu::Error("MatMul requires 2D tensors (matrices)");
+  if (input->Shape[1] != weights->Shape[0])
+    throw gonngpu::Error("incompatible matrix dimensions for multiplication: A columns (" +
+                         std::to_string(input->Shape[1]) + ") != B rows (" +
+                         std::to_string(weights->Shape[0]) + ")");
+  input->RetrieveCPU();  // the call reads the host slices
+  weights->RetrieveCPU();
+  const int M = input->Shape[0], N = weights->Shape[1];
+  TensorPtr result = tensor::NewTensor({M, N}, std::vector<float>(size_t(M) * N));
+  CError err{nullptr};
+  const int rc = gonngpu_matmul_sharded(input->Data.data(), M, input->Shape[1], weights->Data.data(),
+                                        weights->Shape[0], N, result->Data.data(),
+                                        round_to_nearest ? GONNGPU_FP16_RN : GONNGPU_FP16_TRUNC, n_devices, &err);
+  if (rc != 0)
+    throw gonngpu::Error("GPU matrix multiplication failed (code " + std::to_string(rc) +
+                         "): " + gonngpu::detail::take_message(err));
+  return result;
+}
+
 // ---- gpu/matrix/mixed-precision-{efficient,fixed,optimized}.go: precision selectors ------
 // Thin decisions, by operand size, between the float32 MatMul and a reduced-precision one.
 // The thresholds and the host-side "simulated precision" scaling of the result are the

@@ -551,6 +551,22 @@ static void layers_stats_unified_selectors() {
     big->RetrieveCPU();
     CHECK(rel_frob(big->Data, ref_gemm(big_a->Data, big_b->Data, 300, 600, 300)) <= 1e-5);
   }
+  // the sharded form of ForwardFloat16 against the one-device form and the float64 loops
+  {
+    const int M = 9000, K = 96, N = 136;
+    std::vector<float> A(size_t(M) * K), B(size_t(K) * N);
+    for (auto& x : A) x = u(rng);
+    for (auto& x : B) x = u(rng);
+    auto tA = tensor::NewTensor({M, K}, A), tB = tensor::NewTensor({K, N}, B);
+    auto one = matrix::ForwardFloat16(tA, tB);
+    one->RetrieveCPU();
+    auto all = matrix::ForwardFloat16Sharded(tA, tB, 0);
+    auto first = matrix::ForwardFloat16Sharded(tA, tB, 1);
+    CHECK(!all->IsOnGPU() && all->Data.size() == one->Data.size());
+    CHECK_LE(rel_frob(all->Data, std::vector<double>(one->Data.begin(), one->Data.end())), 1e-6);
+    CHECK_LE(rel_frob(first->Data, std::vector<double>(all->Data.begin(), all->Data.end())), 1e-6);
+    CHECK_LE(rel_frob(all->Data, ref_gemm(A, B, M, K, N)), 1e-2);
+  }
   // GradFusedLinearActivation: forward through the fused kernel, backward with the right mask
   {
     const int M = 30, K = 12, N = 20;

@@ -305,6 +305,48 @@ def test_config4_fp16_8192_sampled_rows_and_checksum(gpu):
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-4
 
 
+def test_config5_full_size_from_page_locked_host_memory(gpu):
+    """The benchmarked configuration at full size (M = 131072, K = N = 4096, fp16 in / fp32
+    accumulate) through create_gpu_buffer -> gonngpu_matmul_ex -> retrieve with the matrices in
+    page-locked host memory, which is the streamed path (upload, convert, multiply and write-back
+    in row blocks): 2048-odd sampled rows, the first and last row of every eighth among them,
+    against the float64 oracle on the fp16-rounded inputs, and the checksum C.1 == A16.(B16.1)
+    over every output."""
+    g = gpu
+    m, k, n = 131072, 4096, 4096
+    hA, pA = g.pinned_array((m, k))
+    hB, pB = g.pinned_array((k, n))
+    hC, pC = g.pinned_array((m, n))
+    rng = np.random.default_rng(4)                  # the benchmark's inputs: A first, then B
+    s = 1.0 / np.sqrt(k)
+    for r in range(0, m, 8192):
+        np.multiply(rng.standard_normal((8192, k)), s, out=hA[r:r + 8192], casting="same_kind")
+    hB[...] = rng.standard_normal((k, n)) * s
+    hC[...] = -123.0
+    a, b, c = g.Buffer.from_host(hA), g.Buffer.from_host(hB), g.Buffer.from_host(hC)
+    try:
+        g.matmul_ex(a, (m, k), False, b, (k, n), False, c, (m, n), precision=g.FP16_RN)
+        c.retrieve_into(hC)
+    finally:
+        for x in (a, b, c):
+            x.release()
+    rows = _row_sample(m, shards=8, per_shard=256)
+    assert len(rows) >= 2048
+    B16 = oracle.f16_rn(hB)
+    ref = oracle.gemm_f64(oracle.f16_rn(hA[rows]), B16)
+    assert oracle.rel_frobenius(hC[rows], ref) <= FP16_TOL
+    assert oracle.rel_frobenius(hC[rows], ref) <= 5e-5        # exact fp16 products, fp32 accumulation
+    b1 = B16.astype(np.float64) @ np.ones(n)
+    worst = 0.0
+    for r in range(0, m, 8192):                     # blockwise: bounds the float64 temporaries
+        want = oracle.f16_rn(hA[r:r + 8192]).astype(np.float64) @ b1
+        got = hC[r:r + 8192].astype(np.float64) @ np.ones(n)
+        worst = max(worst, float(np.linalg.norm(got - want) / np.linalg.norm(want)))
+    assert worst <= 1e-4
+    for p in (pA, pB, pC):
+        g.lib().gonngpu_host_free(p)
+
+
 def test_buffer_protocol(gpu):
     """Lazy upload, retrieval of an untouched buffer, size checks, release."""
     x = np.arange(12, dtype=np.float32)
