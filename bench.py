@@ -616,7 +616,7 @@ def merge_e2e(per_rank, one_call):
 
 # DRAM bytes of one GEMM launch measured with ncu (dram__bytes_read.sum +
 # dram__bytes_write.sum) on the M=8192 case of this kernel: see profiles/.
-NCU_TRAFFIC_M8192 = {"read": 179.0e6, "write": 99.8e6, "rows": 8192}
+NCU_TRAFFIC_M8192 = {"read": 178.2e6, "write": 99.7e6, "rows": 8192}
 
 
 def traffic_estimate(rows):
