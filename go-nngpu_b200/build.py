@@ -29,14 +29,8 @@ def _stale():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False, out=None, extra_flags=()):
-    """Compiles every CUDA source into one shared library; returns its path.
-    `out` / `extra_flags` build a variant (timing probes) beside the product."""
-    if out is not None:
-        nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-        cmd = [nvcc] + NVCC_FLAGS + list(extra_flags) + [os.path.join(CSRC, s) for s in SOURCES] + ["-o", out]
-        subprocess.run(cmd, check=True, capture_output=not verbose)
-        return out
+def build(force=False, verbose=False):
+    """Compiles every CUDA source into one shared library; returns its path."""
     if not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
