@@ -26,6 +26,17 @@ constexpr size_t kStageBytes = 16u << 20;  // pinned staging chunk
 
 std::recursive_mutex g_mu;
 
+// Waits for a stream with the library's lock released, so that other threads of the caller
+// (the reference allows goroutine-concurrent calls) can enqueue their own uploads and kernels
+// instead of queueing behind a wait.  The calling thread holds g_mu (every entry point takes it);
+// everything the waiter touches afterwards is re-read under the lock.
+cudaError_t wait_stream(cudaStream_t s) {
+  g_mu.unlock();
+  const cudaError_t e = cudaStreamSynchronize(s);
+  g_mu.lock();
+  return e;
+}
+
 // Converted copy of a buffer for the tensor cores ("operand plane").
 struct Plane {
   void* p0 = nullptr;
@@ -256,7 +267,7 @@ bool copy_d2h(Device& d, void* dst, const void* src, size_t bytes) {
   g_stats[2] += long(bytes);
   if (host_is_pinned(dst)) {
     return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, d.stream) == cudaSuccess &&
-           cudaStreamSynchronize(d.stream) == cudaSuccess;
+           wait_stream(d.stream) == cudaSuccess;
   }
   // chunk i is copied out of staging while chunk i+1 crosses the bus
   size_t off = 0, pending_off = 0, pending_n = 0;
@@ -368,7 +379,7 @@ Plane* get_plane(Device& d, Buffer* b, uint64_t rows, uint64_t cols, int kind) {
 // entry point returns for an execution failure.
 int finish(Device& d, CError* err, int exec_code, const char* what) {
   cudaError_t e = cudaGetLastError();
-  if (e == cudaSuccess && g_blocking) e = cudaStreamSynchronize(d.stream);
+  if (e == cudaSuccess && g_blocking) e = wait_stream(d.stream);
   if (e != cudaSuccess) {
     set_error(err, "%s: CUDA error: %s", what, cudaGetErrorString(e));
     return exec_code;
@@ -483,9 +494,9 @@ bool streamed_issue(Device& d, const StreamedShard& s, const char** msg) {
 
 // Everything a streamed_issue enqueued is complete on return.
 bool streamed_wait(Device& d) {
-  const bool a = cudaStreamSynchronize(d.copy_stream) == cudaSuccess;
-  const bool b = cudaStreamSynchronize(d.stream) == cudaSuccess;
-  const bool c = cudaStreamSynchronize(d.d2h_stream) == cudaSuccess;
+  const bool a = wait_stream(d.copy_stream) == cudaSuccess;
+  const bool b = wait_stream(d.stream) == cudaSuccess;
+  const bool c = wait_stream(d.d2h_stream) == cudaSuccess;
   return a && b && c;
 }
 
