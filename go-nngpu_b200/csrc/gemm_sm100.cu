@@ -114,8 +114,11 @@ __device__ __forceinline__ void tile_coords(const KernelParams& p, uint32_t t, u
   if (p.group_m0) {
     const uint32_t first = p.group_m0 * p.tiles_n;
     if (t < first) {
-      tm = t % p.group_m0;
+      // slab by slab, down the rows for even slabs and up for odd ones: the rows of A touched
+      // last are touched first again, which is what an LRU-like L2 keeps
       tn = t / p.group_m0;
+      const uint32_t r = t - tn * p.group_m0;
+      tm = (tn & 1u) ? p.group_m0 - 1u - r : r;
       return;
     }
     t -= first;
