@@ -37,10 +37,9 @@ constexpr uint32_t SLAB_ROW_BYTES = 128;             // one swizzle row
 constexpr uint32_t A_TILE_BYTES = BLOCK_M * SLAB_ROW_BYTES;  // 16 KiB per plane per k block
 constexpr uint32_t KSTEPS = 4;                       // MMAs (per product) per k block
 constexpr uint32_t NUM_THREADS = 192;
-constexpr uint32_t SENDER_WARPS = 8;     // extra warps of the row-sharded product that move B
-constexpr uint32_t SENDER_GROUPS = 4;    // the slabs are dealt out to this many groups of sender warps
-constexpr uint32_t GATED_THREADS = NUM_THREADS + 32 * SENDER_WARPS;
-constexpr uint32_t SENDER_DEPTH = 16;    // 16-byte loads a sender lane keeps in flight
+constexpr uint32_t GATED_THREADS = 320;   // row-sharded product: 4 more warps, used by the sending CTAs
+constexpr uint32_t SENDER_GROUPS = 4;     // the slabs are dealt out to this many groups of sender warps
+constexpr uint32_t SENDER_DEPTH = 16;     // 16-byte loads a sender lane keeps in flight
 constexpr uint32_t SMEM_LIMIT = 227 * 1024;
 
 // How one operand's k-block tile is fetched by TMA and described to the MMA.
@@ -75,6 +74,10 @@ struct ShardParams {
   uint32_t rows;         // K
   uint32_t row_chunks;   // 16-byte chunks per row of B
   uint32_t slab_chunks;  // 16-byte chunks per row of one slab
+  // On the owner the last `sender_pairs` CTA pairs push B with all their warps before they
+  // multiply, and the tile order leaves them out of the first `late_rounds` rounds (both 0 on
+  // the other ranks).
+  uint32_t sender_pairs, late_rounds;
 };
 
 struct KernelParams {
@@ -557,6 +560,18 @@ __device__ __forceinline__ void shard_exit(const ShardParams& s, bool gave_up) {
   }
 }
 
+// The i-th tile of pair `pair` in the gated product.  Everywhere but on the owner that is the
+// usual pair + i * num_pairs.  On the owner the last `sender_pairs` pairs are busy sending when
+// the kernel starts: the first `late_rounds` rounds are dealt out among the other pairs only,
+// and the sending pairs join behind them, so that they end up with about as many tiles fewer
+// as the sending took.  A pair is done when the result reaches num_tiles.
+__device__ __forceinline__ uint32_t gated_tile_at(const ShardParams& s, uint32_t pair,
+                                                  uint32_t num_pairs, uint32_t i) {
+  const uint32_t early = num_pairs - s.sender_pairs;
+  if (pair >= early) return s.late_rounds * early + i * num_pairs + pair;
+  return i < s.late_rounds ? i * early + pair : s.late_rounds * early + (i - s.late_rounds) * num_pairs + pair;
+}
+
 // ---------------------------------------------------------------------------
 // fp16 kernel for large problems: CTA pairs (cta_group::2).
 //
@@ -578,9 +593,10 @@ __device__ __forceinline__ void shard_exit(const ShardParams& s, bool gave_up) {
 // A stage holds SUB k blocks (each laid out as A tile then B half tile); one
 // barrier round (full wait, commit) therefore covers 4*SUB MMAs.
 //
-// GATED: the row-sharded product that replicates B itself.  SENDER_WARPS more warps per CTA
-// (6 and up) push B on the owner; every producer waits for the arrival flag of a tile's column slab
-// before the tile's first load; the last CTA to leave acknowledges the epoch.
+// GATED: the row-sharded product that replicates B itself.  On the owner the last pairs push B
+// with all their warps (ten per CTA) before they join the product; every producer waits for
+// the arrival flag of a tile's column slab before the tile's first load; the last CTA to leave
+// acknowledges the epoch.
 template <int BLOCK_N, int STAGES, int SUB, bool GATED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATED ? GATED_THREADS : NUM_THREADS, 1)
 gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
@@ -645,12 +661,29 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   ptx::grid_dependency_release();
   ptx::grid_dependency_wait();
 
+  // i-th tile of this pair (>= num_tiles: done)
+  auto tile_at = [&](uint32_t i) -> uint32_t {
+    if constexpr (GATED) return gated_tile_at(p.sh, pair, num_pairs, i);
+    else return pair + i * num_pairs;
+  };
+  if constexpr (GATED) {
+    // ------------------------------------------- sending pairs (owner of B only)
+    const uint32_t early = num_pairs - p.sh.sender_pairs;
+    if (pair >= early) {
+      constexpr uint32_t WARPS = GATED_THREADS / 32;
+      const uint32_t w = ((pair - early) * 2u + cta_rank) * WARPS + warp;  // among all sender warps
+      push_b_slabs(p.sh, w % SENDER_GROUPS, w / SENDER_GROUPS, p.sh.sender_pairs * 2u * WARPS / SENDER_GROUPS,
+                   lane, p.status);
+      __syncthreads();
+    }
+  }
+
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     uint32_t stage = 0, phase = 0;
     bool alive = true;
     uint32_t slabs_seen = 0;  // GATED: column slabs of B known to have arrived (bit per slab)
-    for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs) {
+    for (uint32_t i = 0, t = tile_at(0); alive && t < p.num_tiles; t = tile_at(++i)) {
       uint32_t tm, tn;
       tile_coords(p, t, tm, tn);
       const int32_t a_tile = int32_t(tm * 2 + cta_rank);  // in units of 128 rows
@@ -729,7 +762,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t local = 0;
       uint32_t ready = 0;
       bool alive = true;
-      for (uint32_t t = pair; alive && t < p.num_tiles; t += num_pairs, ++local) {
+      for (uint32_t t = tile_at(0); alive && t < p.num_tiles; t = tile_at(++local)) {
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
         if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
@@ -767,16 +800,13 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
       }
     }
-  } else if (GATED && warp >= 6) {
-    // ------------------------------------------- sender warps (owner of B only)
-    if (p.sh.rank == p.sh.owner)
-      push_b_slabs(p.sh, (warp - 6u) % SENDER_GROUPS, blockIdx.x * (SENDER_WARPS / SENDER_GROUPS) + (warp - 6u) / SENDER_GROUPS,
-                   gridDim.x * (SENDER_WARPS / SENDER_GROUPS), lane, p.status);
+  } else if (warp >= 6) {
+    // (the extra warps of the gated product only take part in sending)
   } else {
     // ------------------------------------------------------------ epilogue
     const uint32_t quarter = warp & 3u;
     uint32_t local = 0;
-    for (uint32_t t = pair; t < p.num_tiles; t += num_pairs, ++local) {
+    for (uint32_t t = tile_at(0); t < p.num_tiles; t = tile_at(++local)) {
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
       uint32_t tm, tn;
@@ -2392,6 +2422,22 @@ const char* launch_gemm_sharded(uint32_t M, uint32_t N, uint32_t K, const void* 
   sh.rows = K;
   sh.row_chunks = N / 8;
   sh.slab_chunks = sh.slab_tiles * bn / 8;
+  // Sending pairs of the owner: a quarter of the pairs, 16 at most (32 SMs push at the rate of a
+  // kernel that does nothing else; measured 98 us for 32 MiB to 8 GPUs, arrival flags included),
+  // left out of as many rounds of tiles as the push is expected to take: bytes at 400 GB/s plus
+  // four fence stalls of about 14 us, against 2 * 256 * 256 * K flop per tile at the pair's share
+  // of 1.35 PFLOP/s.  A wrong guess only shifts a few tiles between pairs.
+  const uint32_t tiles_m = (M + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
+  const uint32_t pairs = std::max<uint32_t>(1u, std::min<uint32_t>(tiles_m * tiles_n, uint32_t(sm_count) / 2));
+  if (link.rank == link.owner) {
+    sh.sender_pairs = link.sender_pairs >= 0 ? uint32_t(link.sender_pairs)
+                                             : (pairs >= 8 ? std::min<uint32_t>(16u, pairs / 4) : 1u);
+    sh.sender_pairs = std::max<uint32_t>(1u, std::min<uint32_t>(sh.sender_pairs, pairs));
+    const double push_s = double(K) * N * 2.0 / 400e9 + 56e-6;
+    const double tile_s = 2.0 * 256 * 256 * K / (1.35e15 / (double(sm_count) / 2));
+    sh.late_rounds = link.late_rounds >= 0 ? uint32_t(link.late_rounds)
+                                           : uint32_t(std::min(64.0, std::floor(push_s / tile_s + 0.5)));
+  }
   // Row tiles swept slab by slab while B arrives.  A slab must be consumed no faster than the
   // next one arrives: the group's tiles of one slab have to last as long as a slab's transfer.
   // Measured on B200s: a 2 MiB slab takes about 4.5 us to reach 2 GPUs and 7 to 11 us to reach

@@ -148,10 +148,10 @@ cudaError_t launch_replicate_wait(void* const* bases, int owner, int my_rank, ui
 
 // ---- row-sharded product with the replication of B inside the kernel ---------------
 // Every rank multiplies its rows of A by the whole of B, which only the owner holds.  The
-// product kernel itself moves B: on the owner, extra warps of every CTA push B, column slab by
+// product kernel itself moves B: on the owner, a few CTA pairs first push B, column slab by
 // column slab, into the current slot of every rank's symmetric buffer (multimem.st through
 // NVSwitch, or plain peer stores when the group has no multicast address) and publish one
-// arrival flag per slab; on every rank the TMA producer of a tile waits for the flag of the
+// arrival flag per slab, then join the product with correspondingly fewer tiles; on every rank the TMA producer of a tile waits for the flag of the
 // tile's slab before its first load, and the last CTA to leave acknowledges the epoch to the
 // owner, which may then overwrite the slot two epochs later.  Tiles are visited slab by slab
 // while B is arriving, so the product runs beside the transfer instead of behind it.
@@ -180,6 +180,8 @@ struct ShardLink {
   int slot = 0;
   uint32_t epoch = 1;
   uint32_t first_group = 0;      // row tiles (256 rows) visited slab by slab; 0 = choose
+  int sender_pairs = -1;         // owner: CTA pairs that push B before they multiply; -1 = choose
+  int late_rounds = -1;          // owner: rounds of tiles those pairs are left out of; -1 = choose
 };
 
 // C[M,N] = A[M,K] . B[K,N] for this rank's rows, fp16 operands, fp32 accumulate; `b_slot` is

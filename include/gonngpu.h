@@ -323,11 +323,12 @@ GONNGPU_API int gonngpu_shard_plan(long rows, int n_devices, int device, long *f
  * peer stores instead).  At `slots_offset` it holds two slots of aCols*bCols*2
  * bytes, at `ctrl_offset` 512 bytes of control words, zero before epoch 1.
  *
- * On the owner extra warps of every CTA push B into slot epoch % 2 of every
- * rank, 256-column slab by slab, and raise one arrival flag per slab; on every
- * rank a tile's loads wait for the flag of its slab, and the first `first_group`
- * 256-row tiles (0 = chosen from the group size) are visited slab by slab, so the
- * product runs while B is still arriving.  The last CTA to leave acknowledges the
+ * On the owner a few CTA pairs (32 of the 148 SMs) first push B into slot
+ * epoch % 2 of every rank, 256-column slab by slab, raising one arrival flag per
+ * slab, and then join the product with as many tiles fewer as the push took; on
+ * every rank a tile's loads wait for the flag of its slab, and the first
+ * `first_group` 256-row tiles (0 = chosen from the group size) are visited slab by
+ * slab, so the product runs while B is still arriving.  The last CTA to leave acknowledges the
  * epoch to the owner, which overwrites a slot only when every rank has
  * acknowledged the epoch that used it before (epoch - 2).  Every rank calls this
  * once per step with the same epoch: 1, 2, 3 ...  The kernels read B from their
@@ -436,6 +437,10 @@ GONNGPU_API int gonngpu_set_gemm_tuning(int block_n, int max_ctas);
  * 0 never, 1 force 256-row tiles (block_n 0, 128 or 256), 2 force 512-row
  * tiles (block_n 0 or 256). */
 GONNGPU_API int gonngpu_set_gemm_pair_mode(int mode);
+/* gonngpu_gemm_f16_sharded on the owner of B: how many CTA pairs push B before they
+ * multiply (1..74) and how many rounds of tiles they are left out of (0..64); -1 (default)
+ * lets the library choose from the sizes.  For measurements. */
+GONNGPU_API int gonngpu_set_sharded_tuning(int sender_pairs, int late_rounds);
 /* Split-K of the fp32 GEMM (products with too few tiles to fill the GPU share a
  * tile's K range among several SMs and add the partial sums in a fixed order):
  * 0 (default) chosen by problem size, 1 never, n > 1 force n splits. */
