@@ -86,6 +86,7 @@ bool g_blocking = true;
 bool g_plane_cache = true;
 gonn::GemmTuning g_tune;
 int g_shard_sender_pairs = -1, g_shard_late_rounds = -1;  // gonngpu_set_sharded_tuning
+void* g_shard_trace = nullptr;                            // gonngpu_set_sharded_trace
 // Split-K workspace per device: room for one wave of 128 x 256 partial tiles.
 constexpr size_t kSplitKBytes = size_t(24) << 20;
 constexpr uint32_t kSplitKSlots = 4096;
@@ -1122,6 +1123,7 @@ int gonngpu_gemm_f16_sharded(const void* a, long aRows, long aCols, long aPitch,
   link.first_group = uint32_t(first_group);
   link.sender_pairs = g_shard_sender_pairs;
   link.late_rounds = g_shard_late_rounds;
+  link.trace = g_shard_trace;
   const char* msg = gonn::launch_gemm_sharded(uint32_t(aRows), uint32_t(bCols), uint32_t(aCols), a,
                                               uint64_t(aPitch), static_cast<char*>(local_base) + link.slot_offset,
                                               c, uint64_t(ldc), link, d.status_dev, d.sm_count, d.stream);
@@ -2048,6 +2050,12 @@ int gonngpu_set_sharded_tuning(int sender_pairs, int late_rounds) {
   if (sender_pairs < -1 || sender_pairs > 74 || late_rounds < -1 || late_rounds > 64) return -1;
   g_shard_sender_pairs = sender_pairs;
   g_shard_late_rounds = late_rounds;
+  return 0;
+}
+
+int gonngpu_set_sharded_trace(void* device_words) {
+  std::lock_guard<std::recursive_mutex> lk(g_mu);
+  g_shard_trace = device_words;
   return 0;
 }
 

@@ -78,6 +78,11 @@ struct ShardParams {
   // multiply, and the tile order leaves them out of the first `late_rounds` rounds (both 0 on
   // the other ranks).
   uint32_t sender_pairs, late_rounds;
+  // Optional timeline of one launch (device memory, 128 words of %globaltimer nanoseconds, or
+  // null): [0] first CTA past its set-up, [1 + s] slab s published by the owner's senders,
+  // [40 + s] slab s first seen by a producer of this rank (atomicMin: preset to ~0), [80] last
+  // CTA leaving.
+  unsigned long long* trace;
 };
 
 struct KernelParams {
@@ -479,19 +484,17 @@ __device__ __forceinline__ ShardControl* shard_ctrl(const ShardParams& s, uint32
   return reinterpret_cast<ShardControl*>(static_cast<char*>(s.bases[rank]) + s.ctrl_offset);
 }
 
-// Sender warps of the owner.  The sender warps of all CTAs form SENDER_GROUPS groups (`nwarps`
-// warps each, this one is `wid` of group `group`); group g sends the slabs g, g + SENDER_GROUPS, ...  Within a slab each warp takes whole rows
-// (consecutive lanes, consecutive 16-byte chunks).  After a slab every lane fences at system
-// scope and the warp counts itself in; the warp that completes the count fences again and
-// writes the slab's arrival flag on every rank with st.release.sys.  A reader that took the
-// flag with ld.acquire.sys therefore sees the slab.  A fence waits until the switch has
-// acknowledged the warp's stores, ten microseconds and more beside a running product, and a
-// warp that sent every slab would pay that once per slab, one after the other (measured: 32
-// MiB took 300 us that way); with the slabs dealt out to the groups, one group's fence runs
-// beside the other groups' stores.  No multicast load is issued: only stores use the
-// multicast address.
-__device__ void push_b_slabs(const ShardParams& s, uint32_t group, uint32_t wid, uint32_t nwarps,
-                             uint32_t lane, GemmStatus* status) {
+// Sending CTAs of the owner.  The sending CTAs form up to SENDER_GROUPS groups BY CTA (CTA c
+// of the senders is in group c % groups); group g sends the slabs g, g + groups, ...  Within a
+// slab each warp takes whole rows (consecutive lanes, consecutive 16-byte chunks).  After a
+// slab every lane fences at system scope and the warp counts itself in on the slab's counter.
+// A system-scope fence waits for every store the SM still has in flight, not only the warp's
+// own: with warps of one SM working on different slabs each fence waited for all of them
+// (measured: 25 to 50 us per slab), which is why a whole CTA works on one slab at a time.
+// The arrival flag itself is written by a watcher (see publish_slabs) on an SM that sends
+// nothing, or, where every pair sends, by the warp that completes the count.
+__device__ void push_b_slabs(const ShardParams& s, uint32_t group, uint32_t groups, uint32_t wid,
+                             uint32_t nwarps, uint32_t lane, bool publish, GemmStatus* status) {
   ShardControl* mine = shard_ctrl(s, s.rank);
   // the slot may be overwritten only when every rank has finished with the epoch that last used it
   bool ok = true;
@@ -501,7 +504,7 @@ __device__ void push_b_slabs(const ShardParams& s, uint32_t group, uint32_t wid,
     if (!ok && (atomicOr(&mine->gave_up, 2u) & 2u) == 0u) report(status, 4, lane, s.epoch, s.ack_needed);
     return;
   }
-  for (uint32_t slab = group; slab < s.num_slabs; slab += SENDER_GROUPS) {
+  for (uint32_t slab = group; slab < s.num_slabs; slab += groups) {
     const uint32_t c0 = slab * s.slab_chunks;
     const uint32_t width = min(s.slab_chunks, s.row_chunks - c0);
     // The link only runs at full rate with enough bytes in flight (rate x latency is about
@@ -534,13 +537,50 @@ __device__ void push_b_slabs(const ShardParams& s, uint32_t group, uint32_t wid,
     uint32_t last = 0;
     if (lane == 0) last = (atomicAdd(&mine->sent[slab], 1u) == nwarps - 1u) ? 1u : 0u;
     last = __shfl_sync(0xffffffffu, last, 0);
-    if (last) {
+    if (last && publish) {
+      if (lane == 0 && s.trace) s.trace[1 + slab] = ptx::globaltimer_ns();
       if (lane == 0) mine->sent[slab] = 0;  // zero again for the next launch
       if (lane < s.world) {
         __threadfence_system();
         ptx::st_release_sys(&shard_ctrl(s, lane)->arrived[s.slot][slab], s.epoch);
       }
     }
+  }
+}
+
+// Sender warps of group g: the sending CTAs c with c % groups == g, `warps` warps each.
+__device__ __forceinline__ uint32_t sender_group_warps(uint32_t sender_ctas, uint32_t groups, uint32_t g,
+                                                       uint32_t warps) {
+  return ((sender_ctas - g + groups - 1u) / groups) * warps;
+}
+
+// Watcher (one warp of the owner's first CTA, which sends nothing): polls the slabs' counters
+// and writes a slab's arrival flag on every rank as soon as all its sender warps have counted
+// themselves in.  The senders fenced before they counted in; the flag goes out with
+// st.release.sys from an SM that has no stores of its own in flight, so its fence is short.
+__device__ void publish_slabs(const ShardParams& s, uint32_t sender_ctas, uint32_t groups, uint32_t warps,
+                              uint32_t lane) {
+  ShardControl* mine = shard_ctrl(s, s.rank);
+  uint32_t pending = s.num_slabs >= 32u ? 0xffffffffu : ((1u << s.num_slabs) - 1u);
+  const uint64_t t0 = ptx::globaltimer_ns();
+  // (a push that gave up never completes its counts: the limit ends the watch, and the
+  // products' own waits report)
+  while (pending && ptx::globaltimer_ns() - t0 < ptx::kAckWaitLimitNs + ptx::kDataWaitLimitNs) {
+    for (uint32_t slab = 0; slab < s.num_slabs; ++slab) {
+      if (!((pending >> slab) & 1u)) continue;
+      uint32_t done = 0;
+      if (lane == 0) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(done) : "l"(&mine->sent[slab]) : "memory");
+        done = done == sender_group_warps(sender_ctas, groups, slab % groups, warps);
+      }
+      done = __shfl_sync(0xffffffffu, done, 0);
+      if (!done) continue;
+      if (lane == 0 && s.trace) s.trace[1 + slab] = ptx::globaltimer_ns();
+      if (lane == 0) mine->sent[slab] = 0;  // zero again for the next launch
+      if (lane < s.world) ptx::st_release_sys(&shard_ctrl(s, lane)->arrived[s.slot][slab], s.epoch);
+      pending &= ~(1u << slab);
+    }
+    __nanosleep(200);
   }
 }
 
@@ -551,6 +591,7 @@ __device__ __forceinline__ void shard_exit(const ShardParams& s, bool gave_up) {
   if (gave_up) atomicOr(&mine->gave_up, 1u);
   __threadfence();
   if (atomicAdd(&mine->exited, 1u) == gridDim.x - 1u) {
+    if (s.trace) s.trace[80] = ptx::globaltimer_ns();
     mine->exited = 0;
     const uint32_t gave = atomicExch(&mine->gave_up, 0u);
     if (!gave) {
@@ -661,6 +702,9 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   ptx::grid_dependency_release();
   ptx::grid_dependency_wait();
 
+  if constexpr (GATED) {
+    if (p.sh.trace && blockIdx.x == 0 && threadIdx.x == 0) p.sh.trace[0] = ptx::globaltimer_ns();
+  }
   // i-th tile of this pair (>= num_tiles: done)
   auto tile_at = [&](uint32_t i) -> uint32_t {
     if constexpr (GATED) return gated_tile_at(p.sh, pair, num_pairs, i);
@@ -668,13 +712,18 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   };
   if constexpr (GATED) {
     // ------------------------------------------- sending pairs (owner of B only)
+    constexpr uint32_t WARPS = GATED_THREADS / 32;
     const uint32_t early = num_pairs - p.sh.sender_pairs;
+    const uint32_t sender_ctas = 2u * p.sh.sender_pairs;
+    const uint32_t groups = min(SENDER_GROUPS, sender_ctas);
+    const bool watched = early > 0;  // a CTA that sends nothing exists and watches the counters
     if (pair >= early) {
-      constexpr uint32_t WARPS = GATED_THREADS / 32;
-      const uint32_t w = ((pair - early) * 2u + cta_rank) * WARPS + warp;  // among all sender warps
-      push_b_slabs(p.sh, w % SENDER_GROUPS, w / SENDER_GROUPS, p.sh.sender_pairs * 2u * WARPS / SENDER_GROUPS,
-                   lane, p.status);
+      const uint32_t c = (pair - early) * 2u + cta_rank;  // among the sending CTAs
+      push_b_slabs(p.sh, c % groups, groups, (c / groups) * WARPS + warp,
+                   sender_group_warps(sender_ctas, groups, c % groups, WARPS), lane, !watched, p.status);
       __syncthreads();
+    } else if (p.sh.sender_pairs && blockIdx.x == 0 && warp == 6) {
+      publish_slabs(p.sh, sender_ctas, groups, WARPS, lane);
     }
   }
 
@@ -698,6 +747,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
             // the slab was written by another GPU's stores: order the flag's acquire before
             // this thread's TMA loads of the slab
             ptx::fence_proxy_async_global();
+            if (p.sh.trace) atomicMin(&p.sh.trace[40 + slab], ptx::globaltimer_ns());
           }
           if (!__all_sync(0xffffffffu, here)) {
             if (lane == 0) {
@@ -2422,18 +2472,21 @@ const char* launch_gemm_sharded(uint32_t M, uint32_t N, uint32_t K, const void* 
   sh.rows = K;
   sh.row_chunks = N / 8;
   sh.slab_chunks = sh.slab_tiles * bn / 8;
+  sh.trace = static_cast<unsigned long long*>(link.trace);
   // Sending pairs of the owner: a quarter of the pairs, 16 at most (32 SMs push at the rate of a
   // kernel that does nothing else; measured 98 us for 32 MiB to 8 GPUs, arrival flags included),
-  // left out of as many rounds of tiles as the push is expected to take: bytes at 400 GB/s plus
-  // four fence stalls of about 14 us, against 2 * 256 * 256 * K flop per tile at the pair's share
-  // of 1.35 PFLOP/s.  A wrong guess only shifts a few tiles between pairs.
+  // left out of as many rounds of tiles as the push is expected to take beyond the wait of the
+  // other pairs for the first slabs: bytes at 400 GB/s plus 10 us (measured: 112 us for 32 MiB
+  // to 2 GPUs beside the running product, first slab after 26 us), against 2 * 256 * 256 * K flop
+  // per tile at the pair's share of 1.35 PFLOP/s.  A wrong guess only shifts a few tiles between
+  // pairs.
   const uint32_t tiles_m = (M + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
   const uint32_t pairs = std::max<uint32_t>(1u, std::min<uint32_t>(tiles_m * tiles_n, uint32_t(sm_count) / 2));
   if (link.rank == link.owner) {
     sh.sender_pairs = link.sender_pairs >= 0 ? uint32_t(link.sender_pairs)
                                              : (pairs >= 8 ? std::min<uint32_t>(16u, pairs / 4) : 1u);
     sh.sender_pairs = std::max<uint32_t>(1u, std::min<uint32_t>(sh.sender_pairs, pairs));
-    const double push_s = double(K) * N * 2.0 / 400e9 + 56e-6;
+    const double push_s = double(K) * N * 2.0 / 400e9 + 10e-6;
     const double tile_s = 2.0 * 256 * 256 * K / (1.35e15 / (double(sm_count) / 2));
     sh.late_rounds = link.late_rounds >= 0 ? uint32_t(link.late_rounds)
                                            : uint32_t(std::min(64.0, std::floor(push_s / tile_s + 0.5)));

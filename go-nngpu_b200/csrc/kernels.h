@@ -182,6 +182,7 @@ struct ShardLink {
   uint32_t first_group = 0;      // row tiles (256 rows) visited slab by slab; 0 = choose
   int sender_pairs = -1;         // owner: CTA pairs that push B before they multiply; -1 = choose
   int late_rounds = -1;          // owner: rounds of tiles those pairs are left out of; -1 = choose
+  void* trace = nullptr;         // optional timeline of the launch: 128 x uint64 of device memory
 };
 
 // C[M,N] = A[M,K] . B[K,N] for this rank's rows, fp16 operands, fp32 accumulate; `b_slot` is

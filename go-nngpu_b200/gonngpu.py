@@ -123,6 +123,7 @@ SIGNATURES = {
     "gonngpu_set_gemm_pair_mode": (_c_int, [_c_int]),
     "gonngpu_set_gemm_split_k": (_c_int, [_c_int]),
     "gonngpu_set_sharded_tuning": (_c_int, [_c_int, _c_int]),
+    "gonngpu_set_sharded_trace": (_c_int, [_vp]),
     "gonngpu_trim_cache": (_c_long, []),
     "gonngpu_get_stats": (None, [ctypes.POINTER(_c_long)]),
     "gonngpu_last_kernel_status": (None, [ctypes.POINTER(ctypes.c_uint)]),

@@ -441,6 +441,12 @@ GONNGPU_API int gonngpu_set_gemm_pair_mode(int mode);
  * multiply (1..74) and how many rounds of tiles they are left out of (0..64); -1 (default)
  * lets the library choose from the sizes.  For measurements. */
 GONNGPU_API int gonngpu_set_sharded_tuning(int sender_pairs, int late_rounds);
+/* Timeline of the next gonngpu_gemm_f16_sharded launches, for measurements: `device_words`
+ * is device memory of the current GPU holding 128 64-bit words (NULL switches it off), which
+ * every launch fills with %globaltimer nanoseconds: [0] start, [1 + s] slab s published by
+ * the owner, [40 + s] slab s first seen by this rank (a minimum: preset the words to ~0),
+ * [80] last CTA leaving. */
+GONNGPU_API int gonngpu_set_sharded_trace(void *device_words);
 /* Split-K of the fp32 GEMM (products with too few tiles to fill the GPU share a
  * tile's K range among several SMs and add the partial sums in a fixed order):
  * 0 (default) chosen by problem size, 1 never, n > 1 force n splits. */
