@@ -485,7 +485,8 @@ __device__ __forceinline__ ShardControl* shard_ctrl(const ShardParams& s, uint32
 }
 
 // Sending CTAs of the owner.  The sending CTAs form up to SENDER_GROUPS groups BY CTA (CTA c
-// of the senders is in group c % groups); group g sends the slabs g, g + groups, ...  Within a
+// of the senders is in group c % groups); after slab 0, which all of them send together, group g
+// sends the slabs 1 + g, 1 + g + groups, ...  Within a
 // slab each warp takes whole rows (consecutive lanes, consecutive 16-byte chunks).  After a
 // slab every lane fences at system scope and the warp counts itself in on the slab's counter.
 // A system-scope fence waits for every store the SM still has in flight, not only the warp's
@@ -493,8 +494,9 @@ __device__ __forceinline__ ShardControl* shard_ctrl(const ShardParams& s, uint32
 // (measured: 25 to 50 us per slab), which is why a whole CTA works on one slab at a time.
 // The arrival flag itself is written by a watcher (see publish_slabs) on an SM that sends
 // nothing, or, where every pair sends, by the warp that completes the count.
-__device__ void push_b_slabs(const ShardParams& s, uint32_t group, uint32_t groups, uint32_t wid,
-                             uint32_t nwarps, uint32_t lane, bool publish, GemmStatus* status) {
+__device__ void push_b_slabs(const ShardParams& s, uint32_t group, uint32_t groups, uint32_t group_wid,
+                             uint32_t group_nwarps, uint32_t all_wid, uint32_t all_nwarps, uint32_t lane,
+                             bool publish, GemmStatus* status) {
   ShardControl* mine = shard_ctrl(s, s.rank);
   // the slot may be overwritten only when every rank has finished with the epoch that last used it
   bool ok = true;
@@ -504,7 +506,12 @@ __device__ void push_b_slabs(const ShardParams& s, uint32_t group, uint32_t grou
     if (!ok && (atomicOr(&mine->gave_up, 2u) & 2u) == 0u) report(status, 4, lane, s.epoch, s.ack_needed);
     return;
   }
-  for (uint32_t slab = group; slab < s.num_slabs; slab += groups) {
+  // Slab 0 is what every pair of every rank waits for when the kernel starts: all sending warps
+  // push it together (`all_wid` of `all_nwarps`), then the groups take the slabs 1, 2, ... in turn.
+  for (uint32_t k = 0; k == 0 || group + (k - 1u) * groups + 1u < s.num_slabs; ++k) {
+    const uint32_t slab = k == 0 ? 0u : group + (k - 1u) * groups + 1u;
+    const uint32_t wid = k == 0 ? all_wid : group_wid;
+    const uint32_t nwarps = k == 0 ? all_nwarps : group_nwarps;
     const uint32_t c0 = slab * s.slab_chunks;
     const uint32_t width = min(s.slab_chunks, s.row_chunks - c0);
     // The link only runs at full rate with enough bytes in flight (rate x latency is about
@@ -571,7 +578,8 @@ __device__ void publish_slabs(const ShardParams& s, uint32_t sender_ctas, uint32
       uint32_t done = 0;
       if (lane == 0) {
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(done) : "l"(&mine->sent[slab]) : "memory");
-        done = done == sender_group_warps(sender_ctas, groups, slab % groups, warps);
+        done = done == (slab == 0 ? sender_ctas * warps
+                                  : sender_group_warps(sender_ctas, groups, (slab - 1u) % groups, warps));
       }
       done = __shfl_sync(0xffffffffu, done, 0);
       if (!done) continue;
@@ -720,7 +728,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (pair >= early) {
       const uint32_t c = (pair - early) * 2u + cta_rank;  // among the sending CTAs
       push_b_slabs(p.sh, c % groups, groups, (c / groups) * WARPS + warp,
-                   sender_group_warps(sender_ctas, groups, c % groups, WARPS), lane, !watched, p.status);
+                   sender_group_warps(sender_ctas, groups, c % groups, WARPS), c * WARPS + warp,
+                   sender_ctas * WARPS, lane, !watched, p.status);
       __syncthreads();
     } else if (p.sh.sender_pairs && blockIdx.x == 0 && warp == 6) {
       publish_slabs(p.sh, sender_ctas, groups, WARPS, lane);
@@ -2473,8 +2482,8 @@ const char* launch_gemm_sharded(uint32_t M, uint32_t N, uint32_t K, const void* 
   sh.row_chunks = N / 8;
   sh.slab_chunks = sh.slab_tiles * bn / 8;
   sh.trace = static_cast<unsigned long long*>(link.trace);
-  // Sending pairs of the owner: a quarter of the pairs, 16 at most (32 SMs push at the rate of a
-  // kernel that does nothing else; measured 98 us for 32 MiB to 8 GPUs, arrival flags included),
+  // Sending pairs of the owner: a quarter of the pairs, 8 at most (measured on 8 GPUs: 0.517 ms per
+  // step with 8 sending pairs, 0.534 with 16, 0.546 with 24),
   // left out of as many rounds of tiles as the push is expected to take beyond the wait of the
   // other pairs for the first slabs: bytes at 400 GB/s plus 10 us (measured: 112 us for 32 MiB
   // to 2 GPUs beside the running product, first slab after 26 us), against 2 * 256 * 256 * K flop
@@ -2484,7 +2493,7 @@ const char* launch_gemm_sharded(uint32_t M, uint32_t N, uint32_t K, const void* 
   const uint32_t pairs = std::max<uint32_t>(1u, std::min<uint32_t>(tiles_m * tiles_n, uint32_t(sm_count) / 2));
   if (link.rank == link.owner) {
     sh.sender_pairs = link.sender_pairs >= 0 ? uint32_t(link.sender_pairs)
-                                             : (pairs >= 8 ? std::min<uint32_t>(16u, pairs / 4) : 1u);
+                                             : (pairs >= 8 ? std::min<uint32_t>(8u, pairs / 4) : 1u);
     sh.sender_pairs = std::max<uint32_t>(1u, std::min<uint32_t>(sh.sender_pairs, pairs));
     const double push_s = double(K) * N * 2.0 / 400e9 + 10e-6;
     const double tile_s = 2.0 * 256 * 256 * K / (1.35e15 / (double(sm_count) / 2));
@@ -2493,9 +2502,11 @@ const char* launch_gemm_sharded(uint32_t M, uint32_t N, uint32_t K, const void* 
   }
   // Row tiles swept slab by slab while B arrives.  A slab must be consumed no faster than the
   // next one arrives: the group's tiles of one slab have to last as long as a slab's transfer.
-  // Measured on B200s: a 2 MiB slab takes about 4.5 us to reach 2 GPUs and 7 to 11 us to reach
-  // 8, a wave of 74 tiles with K = 4096 about 28 us; larger groups only cost L2 reuse of A.
-  kp.group_m0 = link.first_group ? link.first_group : (link.world <= 2 ? 16u : link.world <= 4 ? 24u : 32u);
+  // Measured on B200s: the owner publishes a 2 MiB slab every 6 to 8 us (32 MiB in 110 us to 2
+  // GPUs, 134 us to 8), a wave of 74 tiles with K = 4096 takes about 28 us, so 16 row tiles last
+  // 6 us per slab; larger groups cost L2 reuse of A (8 GPUs: 0.517 ms per step with 16, 0.528
+  // with 24, 0.536 with 32).
+  kp.group_m0 = link.first_group ? link.first_group : 16u;
   return launch_gemm_pair(M, N, K, int(bn), false, A, B, kp, sm_count, 0, stream, true);
 }
 
