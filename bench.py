@@ -337,13 +337,17 @@ def run_ours(args, rank, world, local_rank):
             okt = torch.tensor([1 if torch.equal(current_b(), B16) else 0], device=dev)
             dist.all_reduce(okt, op=dist.ReduceOp.MIN)
             replica_ok = bool(int(okt[0]))
-            dist.barrier()
-        torch.cuda.synchronize()
-
+        # everything that takes a different time on every rank (NVML start-up, event creation)
+        # comes before the barrier: a rank that starts late makes the others wait inside their
+        # first step, and that wait would be counted as step time
         sampler = ClockSampler(local_rank)
         sampler.start()
         launches0 = g.stats()["kernel_launches"]
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
         ev[0].record(stream)
         for i in range(args.steps):
             step()
