@@ -954,34 +954,14 @@ __device__ __forceinline__ void epilogue_store32_coalesced(const KernelParams& p
       if (row_base + rl >= p.M || col >= p.N) continue;
       float* c = p.C + (grow_base + rl) * p.ldc + col;
       const float* cin = p.c_in ? p.c_in + (grow_base + rl) * p.ldc + col : nullptr;
-      v.x *= p.alpha; v.y *= p.alpha; v.z *= p.alpha; v.w *= p.alpha;
       if (col + 4u <= p.N) {
-        if (cin) {
-          const float4 o = *reinterpret_cast<const float4*>(cin);
-          v.x += p.beta * o.x; v.y += p.beta * o.y; v.z += p.beta * o.z; v.w += p.beta * o.w;
-        }
-        if (p.bias) {
-          const float4 b = *reinterpret_cast<const float4*>(p.bias + col);
-          v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-        }
-        if (p.act >= 0) {
-          v.x = apply_act(v.x, p.act, p.act_param);
-          v.y = apply_act(v.y, p.act, p.act_param);
-          v.z = apply_act(v.z, p.act, p.act_param);
-          v.w = apply_act(v.w, p.act, p.act_param);
-        }
-        *reinterpret_cast<float4*>(c) = v;
+        *reinterpret_cast<float4*>(c) = epilogue_value4(p, v, cin, p.bias ? p.bias + col : nullptr);
       } else {
         const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (uint32_t k = 0; k < 4; ++k) {
-          if (col + k < p.N) {
-            float x = e[k];
-            if (cin) x += p.beta * cin[k];
-            if (p.bias) x += p.bias[col + k];
-            if (p.act >= 0) x = apply_act(x, p.act, p.act_param);
-            c[k] = x;
-          }
+          if (col + k < p.N)
+            c[k] = epilogue_value(p, e[k], cin ? cin + k : nullptr, p.bias ? p.bias + col + k : nullptr);
         }
       }
     }
@@ -994,11 +974,9 @@ __device__ __forceinline__ void epilogue_store32_coalesced(const KernelParams& p
                    : "=f"(x)
                    : "r"(staging + rl * 128u + (((lane >> 2) ^ (rl & 7u)) << 4) + (lane & 3u) * 4u));
       if (row_base + rl >= p.M || col >= p.N) continue;
-      x *= p.alpha;
-      if (p.c_in) x += p.beta * p.c_in[(grow_base + rl) * p.ldc + col];
-      if (p.bias) x += p.bias[col];
-      if (p.act >= 0) x = apply_act(x, p.act, p.act_param);
-      p.C[(grow_base + rl) * p.ldc + col] = x;
+      p.C[(grow_base + rl) * p.ldc + col] =
+          epilogue_value(p, x, p.c_in ? p.c_in + (grow_base + rl) * p.ldc + col : nullptr,
+                         p.bias ? p.bias + col : nullptr);
     }
   }
   __syncwarp();  // the staging tile may be overwritten by the next block
@@ -1554,32 +1532,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
           const float* cin_row = p.c_in ? p.c_in + (grow_base + lane) * p.ldc : nullptr;
 #pragma unroll
           for (int j = 0; j < NC; j += 4) {
-            float4 v;
-            v.x = sums[j + 0] * p.alpha;
-            v.y = sums[j + 1] * p.alpha;
-            v.z = sums[j + 2] * p.alpha;
-            v.w = sums[j + 3] * p.alpha;
-            if (cin_row) {
-              const float4 o = *reinterpret_cast<const float4*>(cin_row + col0 + j);
-              v.x += p.beta * o.x;
-              v.y += p.beta * o.y;
-              v.z += p.beta * o.z;
-              v.w += p.beta * o.w;
-            }
-            if (p.bias) {
-              const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-              v.x += b.x;
-              v.y += b.y;
-              v.z += b.z;
-              v.w += b.w;
-            }
-            if (p.act >= 0) {
-              v.x = apply_act(v.x, p.act, p.act_param);
-              v.y = apply_act(v.y, p.act, p.act_param);
-              v.z = apply_act(v.z, p.act, p.act_param);
-              v.w = apply_act(v.w, p.act, p.act_param);
-            }
-            *reinterpret_cast<float4*>(c_row + col0 + j) = v;
+            const float4 v = make_float4(sums[j + 0], sums[j + 1], sums[j + 2], sums[j + 3]);
+            *reinterpret_cast<float4*>(c_row + col0 + j) =
+                epilogue_value4(p, v, cin_row ? cin_row + col0 + j : nullptr,
+                                p.bias ? p.bias + col0 + j : nullptr);
           }
         }
       } else if (NC >= 32 && u + gridDim.x >= num_units) {
@@ -1601,13 +1557,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
 #pragma unroll
         for (int j = 0; j < NC; ++j) {
           const uint32_t col = col0 + j;
-          if (col < p.N) {
-            float v = sums[j] * p.alpha;
-            if (cin_row) v += p.beta * cin_row[col];
-            if (p.bias) v += p.bias[col];
-            if (p.act >= 0) v = apply_act(v, p.act, p.act_param);
-            c_row[col] = v;
-          }
+          if (col < p.N)
+            c_row[col] = epilogue_value(p, sums[j], cin_row ? cin_row + col : nullptr,
+                                        p.bias ? p.bias + col : nullptr);
         }
       }
     }
