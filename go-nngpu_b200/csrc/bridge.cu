@@ -58,6 +58,7 @@ struct Buffer {
   bool host_current = false;  // the registered host memory already holds the device contents
   Plane f16[2];               // [F16_RN], [F16_TRUNC]
   Plane tf32;
+  Plane tf32x;                // hi as fp32 + bf16(hi), bf16(lo): operands of the fp32 CTA-pair kernel
 };
 
 struct Device {
@@ -332,12 +333,13 @@ void free_plane(Plane& p) {
 inline uint64_t round_up(uint64_t v, uint64_t m) { return (v + m - 1) / m * m; }
 
 // Returns the operand plane(s) of `b` viewed as [rows, cols], converting when
-// the cached copy is stale.  kind: 0 fp16 RN, 1 fp16 trunc, 2 tf32 hi/lo.
+// the cached copy is stale.  kind: 0 fp16 RN, 1 fp16 trunc, 2 tf32 hi/lo, 3 tf32 hi + the
+// two bf16 planes of the CTA-pair kernel (same bytes as kind 2).
 Plane* get_plane(Device& d, Buffer* b, uint64_t rows, uint64_t cols, int kind) {
-  Plane& p = (kind == 2) ? b->tf32 : b->f16[kind];
+  Plane& p = (kind == 3) ? b->tf32x : (kind == 2) ? b->tf32 : b->f16[kind];
   if (p.p0 && p.version == b->version && p.rows == rows && p.cols == cols) return &p;
   const uint64_t pitch = round_up(cols, 64);
-  const size_t esz = (kind == 2) ? 4 : 2;
+  const size_t esz = (kind >= 2) ? 4 : 2;
   const size_t bytes = size_t(rows) * pitch * esz;
   if (!p.p0 || p.bytes < bytes) {
     free_plane(p);
@@ -348,7 +350,7 @@ Plane* get_plane(Device& d, Buffer* b, uint64_t rows, uint64_t cols, int kind) {
     }
     g_stats[0] += long(bytes);
     g_stats[6] += long(bytes);
-    if (kind == 2) {
+    if (kind >= 2) {
       if (pool_alloc(d.ordinal, &p.p1, bytes) != cudaSuccess) {
         cudaGetLastError();
         pool_free(d.ordinal, p.p0, bytes);
@@ -365,7 +367,9 @@ Plane* get_plane(Device& d, Buffer* b, uint64_t rows, uint64_t cols, int kind) {
   p.rows = rows;
   p.cols = cols;
   p.pitch = pitch;
-  if (kind == 2) {
+  if (kind == 3) {
+    gonn::launch_split_tf32_bf16(b->dptr, rows, cols, static_cast<float*>(p.p0), p.p1, pitch, d.stream);
+  } else if (kind == 2) {
     gonn::launch_split_tf32(b->dptr, rows, cols, static_cast<float*>(p.p0),
                             static_cast<float*>(p.p1), pitch, d.stream);
   } else {
@@ -624,8 +628,11 @@ int matmul_core(const MatmulArgs& m, const int codes[6], const char* what, CErro
     return codes[5];
   }
   const int pkind = (m.precision == GONNGPU_FP32_3XTF32) ? 2 : (m.precision == GONNGPU_FP16_RN ? 0 : 1);
-  Plane* pa = get_plane(d, A, uint64_t(m.aRows), uint64_t(m.aCols), pkind);
-  Plane* pb = get_plane(d, B, uint64_t(m.bRows), uint64_t(m.bCols), pkind);
+  // large fp32 products run on the CTA-pair kernel, which takes its correction terms from bf16 planes
+  const bool bf16x = pkind == 2 && gonn::tf32_takes_pair_kernel(uint32_t(M), uint32_t(N), uint32_t(K),
+                                                                d.sm_count, tune_for(d));
+  Plane* pa = get_plane(d, A, uint64_t(m.aRows), uint64_t(m.aCols), bf16x ? 3 : pkind);
+  Plane* pb = get_plane(d, B, uint64_t(m.bRows), uint64_t(m.bCols), bf16x ? 3 : pkind);
   if (!pa || !pb) {
     set_error(err, "%s: could not allocate operand planes.", what);
     return codes[4];
@@ -635,10 +642,12 @@ int matmul_core(const MatmulArgs& m, const int codes[6], const char* what, CErro
   oa.plane1 = pa->p1;
   oa.pitch = pa->pitch;
   oa.mn_major = m.transA;  // stored [K, M]: M contiguous
+  oa.plane1_bf16 = bf16x;
   ob.plane0 = pb->p0;
   ob.plane1 = pb->p1;
   ob.pitch = pb->pitch;
   ob.mn_major = !m.transB;  // stored [K, N]: N contiguous
+  ob.plane1_bf16 = bf16x;
   gonn::GemmEpilogue epi;
   epi.alpha = m.alpha;
   epi.beta = m.beta;
@@ -660,8 +669,8 @@ int matmul_core(const MatmulArgs& m, const int codes[6], const char* what, CErro
   const int rc = finish(d, err, codes[5], what);
   if (!g_plane_cache) {
     if (g_blocking || cudaStreamSynchronize(d.stream) == cudaSuccess) {
-      free_plane(A->f16[0]); free_plane(A->f16[1]); free_plane(A->tf32);
-      free_plane(B->f16[0]); free_plane(B->f16[1]); free_plane(B->tf32);
+      free_plane(A->f16[0]); free_plane(A->f16[1]); free_plane(A->tf32); free_plane(A->tf32x);
+      free_plane(B->f16[0]); free_plane(B->f16[1]); free_plane(B->tf32); free_plane(B->tf32x);
     }
   }
   return rc;
@@ -761,6 +770,7 @@ int release_gpu_buffer(GPUPtr gpuPtr) {
   free_plane(b->f16[0]);
   free_plane(b->f16[1]);
   free_plane(b->tf32);
+  free_plane(b->tf32x);
   if (b->owns && b->dptr) {
     pool_free(b->device, b->dptr, b->bytes ? b->bytes : 4);
     g_stats[0] -= long(b->bytes);
@@ -1674,25 +1684,48 @@ int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOu
     // planes are written, the masked gradient itself is never stored
     const uint64_t pitch = round_up(uint64_t(out_size), 64);
     const size_t pbytes = size_t(batch) * pitch * 4;
-    void *hi = nullptr, *lo = nullptr;
-    if (pool_alloc(dev, &hi, pbytes) != cudaSuccess || pool_alloc(dev, &lo, pbytes) != cudaSuccess) {
+    // each product takes the low planes of the kernel it will run on: bf16 planes on the
+    // CTA-pair kernel, tf32 planes otherwise (a layer can need both: a small batch makes dX
+    // a small product and dW a large one)
+    const gonn::GemmTuning tune = tune_for(d);
+    const bool dw_x = dW && gonn::tf32_takes_pair_kernel(uint32_t(in_size), uint32_t(out_size),
+                                                         uint32_t(batch), d.sm_count, tune);
+    const bool dx_x = dX && gonn::tf32_takes_pair_kernel(uint32_t(batch), uint32_t(in_size),
+                                                         uint32_t(out_size), d.sm_count, tune);
+    const bool need_lo = (dW && !dw_x) || (dX && !dx_x), need_x2 = dw_x || dx_x;
+    void *hi = nullptr, *lo = nullptr, *x2 = nullptr;
+    if (pool_alloc(dev, &hi, pbytes) != cudaSuccess ||
+        (need_lo && pool_alloc(dev, &lo, pbytes) != cudaSuccess) ||
+        (need_x2 && pool_alloc(dev, &x2, pbytes) != cudaSuccess)) {
       cudaGetLastError();
       if (hi) pool_free(dev, hi, pbytes);
+      if (lo) pool_free(dev, lo, pbytes);
       set_error(err, "linear backward: could not allocate operand planes.");
       return -5;
     }
-    gonn::launch_split_tf32(dY->dptr, uint64_t(batch), uint64_t(out_size), static_cast<float*>(hi),
-                            static_cast<float*>(lo), pitch, d.stream, act ? act->dptr : nullptr);
-    ++g_stats[3];
-    gonn::GemmOperand g;  // dAct stored [batch, out]
-    g.plane0 = hi;
-    g.plane1 = lo;
-    g.pitch = pitch;
+    if (need_lo) {
+      gonn::launch_split_tf32(dY->dptr, uint64_t(batch), uint64_t(out_size), static_cast<float*>(hi),
+                              static_cast<float*>(lo), pitch, d.stream, act ? act->dptr : nullptr);
+      ++g_stats[3];
+    }
+    if (need_x2) {  // writes the same hi
+      gonn::launch_split_tf32_bf16(dY->dptr, uint64_t(batch), uint64_t(out_size), static_cast<float*>(hi),
+                                   x2, pitch, d.stream, act ? act->dptr : nullptr);
+      ++g_stats[3];
+    }
+    auto dact = [&](bool bf16x) {  // dAct stored [batch, out]
+      gonn::GemmOperand g;
+      g.plane0 = hi;
+      g.plane1 = bf16x ? x2 : lo;
+      g.pitch = pitch;
+      g.plane1_bf16 = bf16x;
+      return g;
+    };
     gonn::GemmEpilogue epi;
     const char* msg = nullptr;
     if (dW) {
       // dW[in, out] = X^T . dAct : A = X stored [batch(K), in(M)], B = dAct stored [batch(K), out(N)]
-      Plane* px = get_plane(d, X, uint64_t(batch), uint64_t(in_size), 2);
+      Plane* px = get_plane(d, X, uint64_t(batch), uint64_t(in_size), dw_x ? 3 : 2);
       if (!px) {
         msg = "could not allocate operand planes";
       } else {
@@ -1701,11 +1734,12 @@ int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOu
         a.plane1 = px->p1;
         a.pitch = px->pitch;
         a.mn_major = true;
-        gonn::GemmOperand b = g;
+        a.plane1_bf16 = dw_x;
+        gonn::GemmOperand b = dact(dw_x);
         b.mn_major = true;
         msg = gonn::launch_gemm(gonn::Kind::TF32x3, uint32_t(in_size), uint32_t(out_size),
                                 uint32_t(batch), a, b, dW->dptr, uint64_t(out_size), epi, d.status_dev,
-                                d.sm_count, tune_for(d), d.stream);
+                                d.sm_count, tune, d.stream);
         if (!msg) {
           ++g_stats[3];
           ++g_stats[4];
@@ -1715,20 +1749,21 @@ int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOu
     }
     if (!msg && dX) {
       // dX[batch, in] = dAct . W^T : A = dAct stored [batch(M), out(K)], B = W stored [in(N), out(K)]
-      Plane* pw = get_plane(d, W, uint64_t(in_size), uint64_t(out_size), 2);
+      Plane* pw = get_plane(d, W, uint64_t(in_size), uint64_t(out_size), dx_x ? 3 : 2);
       if (!pw) {
         msg = "could not allocate operand planes";
       } else {
-        gonn::GemmOperand a = g;
+        gonn::GemmOperand a = dact(dx_x);
         a.mn_major = false;
         gonn::GemmOperand b;
         b.plane0 = pw->p0;
         b.plane1 = pw->p1;
         b.pitch = pw->pitch;
         b.mn_major = false;
+        b.plane1_bf16 = dx_x;
         msg = gonn::launch_gemm(gonn::Kind::TF32x3, uint32_t(batch), uint32_t(in_size),
                                 uint32_t(out_size), a, b, dX->dptr, uint64_t(in_size), epi,
-                                d.status_dev, d.sm_count, tune_for(d), d.stream);
+                                d.status_dev, d.sm_count, tune, d.stream);
         if (!msg) {
           ++g_stats[3];
           ++g_stats[4];
@@ -1739,7 +1774,8 @@ int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOu
     // The planes go back to the cache; later work on the same stream may reuse them
     // only after the GEMMs above (stream order).
     pool_free(dev, hi, pbytes);
-    pool_free(dev, lo, pbytes);
+    if (lo) pool_free(dev, lo, pbytes);
+    if (x2) pool_free(dev, x2, pbytes);
     if (msg) {
       cudaGetLastError();
       set_error(err, "linear backward: %s", msg);

@@ -111,6 +111,11 @@ struct KernelParams {
   float* sk_ws;
   uint32_t* sk_count;
   GemmStatus* status;
+  // fp32 pair kernel with bf16 correction planes: the bf16 tiles' descriptors (without the
+  // start address), their advance per K = 16 step, whether the operand is MN-major, and the
+  // instruction descriptor of the bf16 MMAs
+  uint64_t ax_desc, bx_desc;
+  uint32_t ax_kstep, bx_kstep, ax_mn, bx_mn, idesc_x;
   ShardParams sh;
 };
 
@@ -163,6 +168,14 @@ __device__ __forceinline__ void load_operand(const OperandPlan& o, const CUtenso
     if (PAIR) ptx::tma_load_2d_pair(dst + s * o.slab_bytes, m, c0, c1, bar);
     else ptx::tma_load_2d(dst + s * o.slab_bytes, m, c0, c1, bar);
   }
+}
+
+// Both bf16 planes of one operand tile's k block (32 of K) in one box; `tile` counts 128 rows
+// or columns.  See gemm_tf32x3_pair_kernel.
+__device__ __forceinline__ void load_bf16_planes(uint32_t mn_major, const CUtensorMap* m, uint32_t dst,
+                                                 int32_t tile, int32_t kb, uint32_t bar) {
+  if (mn_major) ptx::tma_load_4d_pair(dst, m, 0, kb * 32, tile * 2, 0, bar);
+  else ptx::tma_load_3d_pair(dst, m, kb * 32, tile * 128, 0, bar);
 }
 
 __device__ __forceinline__ float apply_act(float v, int act, float param) {
@@ -1583,10 +1596,18 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
 }
 
 // ---------------------------------------------------------------------------
-// fp32-accurate variant on CTA pairs: the same three-MMA tf32 scheme and chunked
-// promotion as gemm_tf32x3_kernel, with the 2-SM MMA (M=256) of the fp16 pair
-// kernel: each CTA stages its 128 rows of A (hi, lo) and its half of the B tile
-// (hi, lo), 64 KB per k block of 32 for 12 MMAs.  8 drain warps per CTA.
+// fp32-accurate variant on CTA pairs: chunked promotion as in gemm_tf32x3_kernel, the 2-SM MMA
+// (M=256) of the fp16 pair kernel, and the two correction products (hi.lo + lo.hi) taken from
+// bf16 planes instead of tf32 ones.  They are 2^-11 of the product, so 8 bits of them are
+// enough for fp32-grade results (measured 8.8e-7 relative Frobenius error against float64 at
+// K = 4096, the same as with tf32 corrections: the accumulation dominates), and the bf16 MMA
+// runs at twice the tf32 rate: 4 tf32 + 4 bf16 MMAs per k block of 32 - the tensor-pipe time
+// of 8 tf32 MMAs - instead of 12.  Each CTA stages its 128 rows of A and its half of the B
+// tile: hi as fp32 (16 KB each) and, through one map per operand that covers both bf16 planes
+// (last dimension = plane), bf16(hi) and bf16(lo) (8 KB each), one box per k block:
+//   K-major operand: box (32 of K = 64 bytes, 128 rows, 2 planes), 64-byte swizzle;
+//   MN-major:        box (64 of MN = 128 bytes, 32 rows of K, 2 slabs, 2 planes).
+// 64 KB per k block and CTA.  8 drain warps per CTA.
 //   full[s] leader; empty[s] both; tfull[a] both; tempty[a] leader, 16 arrivals.
 template <int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TF32_THREADS, 1)
@@ -1598,6 +1619,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
   constexpr uint32_t BN = 256;
   constexpr uint32_t B_TILE_BYTES = (BN / 2) * SLAB_ROW_BYTES;  // this CTA's half, one plane
   constexpr uint32_t STAGE_BYTES = 2 * (A_TILE_BYTES + B_TILE_BYTES);
+  constexpr uint32_t X_PLANE_BYTES = A_TILE_BYTES / 2;  // one bf16 tile: 128 rows/columns x 32 of K
+  static_assert(A_TILE_BYTES == B_TILE_BYTES, "the bf16 planes of A and B tiles are the same size");
   constexpr uint32_t TMEM_COLS = 512;
   constexpr int NC = BN / 2;  // columns per drain thread
 
@@ -1680,16 +1703,11 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
           if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
           const uint32_t fb = ptx::mapa_shared(full_bar(stage), 0);
           uint32_t dst = smem_base + stage * STAGE_BYTES;
-#pragma unroll
-          for (uint32_t pl = 0; pl < 2; ++pl) {
-            load_operand<true>(p.a, pl ? &tm_a1 : &tm_a0, dst, a_tile, int32_t(kb), 0, fb);
-            dst += A_TILE_BYTES;
-          }
-#pragma unroll
-          for (uint32_t pl = 0; pl < 2; ++pl) {
-            load_operand<true>(p.b, pl ? &tm_b1 : &tm_b0, dst, b_tile, int32_t(kb), 0, fb);
-            dst += B_TILE_BYTES;
-          }
+          load_operand<true>(p.a, &tm_a0, dst, a_tile, int32_t(kb), 0, fb);
+          load_bf16_planes(p.ax_mn, &tm_a1, dst + A_TILE_BYTES, a_tile, int32_t(kb), fb);
+          dst += 2 * A_TILE_BYTES;
+          load_operand<true>(p.b, &tm_b0, dst, b_tile, int32_t(kb), 0, fb);
+          load_bf16_planes(p.bx_mn, &tm_b1, dst + B_TILE_BYTES, b_tile, int32_t(kb), fb);
         }
         __syncwarp();
         if (++stage == STAGES) {
@@ -1704,6 +1722,9 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
       const uint32_t a_hi32 = uint32_t(p.a.desc >> 32), b_hi32 = uint32_t(p.b.desc >> 32);
       const uint32_t a_lo0 = uint32_t(p.a.desc), b_lo0 = uint32_t(p.b.desc);
       const uint32_t a_step = p.a.kstep_bytes >> 4, b_step = p.b.kstep_bytes >> 4;
+      const uint32_t ax_hi32 = uint32_t(p.ax_desc >> 32), bx_hi32 = uint32_t(p.bx_desc >> 32);
+      const uint32_t ax_lo0 = uint32_t(p.ax_desc), bx_lo0 = uint32_t(p.bx_desc);
+      const uint32_t ax_step = p.ax_kstep >> 4, bx_step = p.bx_kstep >> 4;
       uint32_t stage = 0, phase = 0;
       uint32_t chunk = 0;
       uint32_t ready = 0;
@@ -1731,19 +1752,25 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a0,
             const uint32_t next_phase = (stage + 1 == STAGES) ? phase ^ 1u : phase;
             const uint32_t ready_next = ptx::mbar_test_wait(full_bar(next_stage), next_phase);
             const uint32_t st = smem_base + stage * STAGE_BYTES;
-            const uint32_t ah = a_lo0 + (st >> 4), al = a_lo0 + ((st + A_TILE_BYTES) >> 4);
+            const uint32_t ah = a_lo0 + (st >> 4);
             const uint32_t bh = b_lo0 + ((st + 2 * A_TILE_BYTES) >> 4);
-            const uint32_t bl = b_lo0 + ((st + 2 * A_TILE_BYTES + B_TILE_BYTES) >> 4);
+            // the small terms first: bf16(lo_a).bf16(hi_b) + bf16(hi_a).bf16(lo_b), K = 16 each
+            const uint32_t axh = ax_lo0 + ((st + A_TILE_BYTES) >> 4);
+            const uint32_t axl = axh + (X_PLANE_BYTES >> 4);
+            const uint32_t bxh = bx_lo0 + ((st + 2 * A_TILE_BYTES + B_TILE_BYTES) >> 4);
+            const uint32_t bxl = bxh + (X_PLANE_BYTES >> 4);
 #pragma unroll
-            for (uint32_t ks = 0; ks < KSTEPS; ++ks) {
+            for (uint32_t ks = 0; ks < KSTEPS / 2; ++ks) {
               const uint32_t accum = ((kb - kb0) | ks) ? 1u : 0u;
-              ptx::mma_tf32_pair_lohi(d_tmem, al + ks * a_step, a_hi32, bh + ks * b_step, b_hi32,
-                                      p.idesc, accum);
-              ptx::mma_tf32_pair_lohi(d_tmem, ah + ks * a_step, a_hi32, bl + ks * b_step, b_hi32,
-                                      p.idesc, 1u);
+              ptx::mma_f16_pair_lohi(d_tmem, axl + ks * ax_step, ax_hi32, bxh + ks * bx_step, bx_hi32,
+                                     p.idesc_x, accum);
+              ptx::mma_f16_pair_lohi(d_tmem, axh + ks * ax_step, ax_hi32, bxl + ks * bx_step, bx_hi32,
+                                     p.idesc_x, 1u);
+            }
+#pragma unroll
+            for (uint32_t ks = 0; ks < KSTEPS; ++ks)
               ptx::mma_tf32_pair_lohi(d_tmem, ah + ks * a_step, a_hi32, bh + ks * b_step, b_hi32,
                                       p.idesc, 1u);
-            }
             ptx::mma_commit_pair(empty_bar(stage), 3);
             if (kb + 1 == kb_end) ptx::mma_commit_pair(tfull_bar(acc), 3);
             stage = next_stage;
@@ -1841,7 +1868,7 @@ EncodeTiledFn encode_tiled_driver() {
 // encoded maps are kept: a GEMM call then costs a table look-up per operand instead of a
 // driver call.  Bounded: the table is emptied when it reaches kMapCacheMax entries.
 struct MapKey {
-  uint64_t w[12];
+  uint64_t w[16];
   bool operator==(const MapKey& o) const { return std::memcmp(w, o.w, sizeof(w)) == 0; }
 };
 struct MapKeyHash {
@@ -1861,16 +1888,16 @@ CUresult encode_cached(CUtensorMap* map, CUtensorMapDataType dtype, cuuint32_t r
                        CUtensorMapL2promotion promo, CUtensorMapFloatOOBfill oob) {
   EncodeTiledFn fn = encode_tiled_driver();
   if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
-  if (rank > 3) return fn(map, dtype, rank, base, dims, strides, box, estr, il, sw, promo, oob);
+  if (rank > 4) return fn(map, dtype, rank, base, dims, strides, box, estr, il, sw, promo, oob);
   MapKey k{};
   k.w[0] = uint64_t(dtype) | (uint64_t(rank) << 8) | (uint64_t(il) << 16) | (uint64_t(sw) << 24) |
            (uint64_t(promo) << 32) | (uint64_t(oob) << 40);
   k.w[1] = reinterpret_cast<uint64_t>(base);
   for (cuuint32_t i = 0; i < rank; ++i) {
     k.w[2 + i] = dims[i];
-    k.w[8 + i] = uint64_t(box[i]) | (uint64_t(estr[i]) << 32);
+    k.w[9 + i] = uint64_t(box[i]) | (uint64_t(estr[i]) << 32);
   }
-  for (cuuint32_t i = 0; i + 1 < rank; ++i) k.w[5 + i] = strides[i];
+  for (cuuint32_t i = 0; i + 1 < rank; ++i) k.w[6 + i] = strides[i];
   {
     std::lock_guard<std::mutex> lk(g_map_mu);
     auto it = g_map_cache.find(k);
@@ -1985,6 +2012,32 @@ bool make_map_kgroup(CUtensorMap* map, const void* base, uint64_t inner, uint64_
                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+// Map over the two bf16 planes behind GemmOperand::plane1 (plane1_bf16), the plane index as the
+// last dimension: K-major operands (rows = MN, `inner` = K) as boxes of (32 of K, tile rows,
+// 2 planes) with the 64-byte swizzle; MN-major operands (rows = K, `inner` = MN) as boxes of
+// (64 of MN, 32 rows of K, the tile's slabs, 2 planes) with the 128-byte swizzle.
+bool make_map_bf16_planes(CUtensorMap* map, const GemmOperand& op, uint64_t inner, uint64_t outer,
+                          uint32_t tile_mn) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return false;
+  const uint64_t plane_bytes = outer * op.pitch * 2;
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (!op.mn_major) {
+    cuuint64_t dims[3] = {inner, outer, 2};
+    cuuint64_t strides[2] = {op.pitch * 2, plane_bytes};
+    cuuint32_t box[3] = {32, tile_mn, 2};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(op.plane1), dims, strides, box,
+              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  cuuint64_t dims[4] = {64, outer, (inner + 63) / 64, 2};
+  cuuint64_t strides[3] = {op.pitch * 2, SLAB_ROW_BYTES, plane_bytes};
+  cuuint32_t box[4] = {64, 32, tile_mn / 64, 2};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(op.plane1), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // The tensor map(s) of one operand (plane1 only for the fp32 path) and, where the operand is
@@ -2203,6 +2256,8 @@ const char* launch_tf32_pair(uint32_t M, uint32_t N, uint32_t K, const GemmOpera
   constexpr int STAGES = int((SMEM_LIMIT - 1024 - 256) / stage);
   constexpr uint32_t smem = STAGES * stage + 1024 + 256;
   static_assert(STAGES >= 3 && smem <= SMEM_LIMIT, "tf32 pair kernel shared memory");
+  if (!A.plane1_bf16 || !B.plane1_bf16) return "the fp32 CTA-pair kernel takes bf16 low planes";
+  if (A.pitch % 64 || B.pitch % 64) return "bf16 low planes need a pitch of whole 64-element slabs";
   kp.a = plan_operand(true, A.mn_major, BLOCK_M, block_k);
   kp.b = plan_operand(true, B.mn_major, 128, block_k);
   kp.tiles_m = (M + 255) / 256;
@@ -2216,9 +2271,21 @@ const char* launch_tf32_pair(uint32_t M, uint32_t N, uint32_t K, const GemmOpera
   const uint32_t a_box = A.mn_major ? block_k : BLOCK_M, b_box = B.mn_major ? block_k : 128;
   const uint64_t a_in = A.mn_major ? M : K, a_out = A.mn_major ? K : M;
   const uint64_t b_in = B.mn_major ? N : K, b_out = B.mn_major ? K : N;
-  if (!make_operand_maps(true, A, a_in, a_out, a_box, kp.a, &maps[0], &maps[1]) ||
-      !make_operand_maps(true, B, b_in, b_out, b_box, kp.b, &maps[2], &maps[3]))
+  if (!make_operand_maps(true, A, a_in, a_out, a_box, kp.a, &maps[0], nullptr) ||
+      !make_operand_maps(true, B, b_in, b_out, b_box, kp.b, &maps[2], nullptr) ||
+      !make_map_bf16_planes(&maps[1], A, a_in, a_out, 128) ||
+      !make_map_bf16_planes(&maps[3], B, b_in, b_out, 128))
     return "cuTensorMapEncodeTiled failed";
+  // K-major bf16 tile: rows of 64 bytes, groups of 8 rows 512 bytes apart, 32 bytes per K = 16.
+  // MN-major: as the fp16 kernels' (slabs of 64 columns, here 32 rows of K = 4 KB each).
+  const OperandPlan xmn = plan_operand(false, true, 128, block_k);
+  kp.ax_mn = A.mn_major;
+  kp.bx_mn = B.mn_major;
+  kp.ax_desc = A.mn_major ? xmn.desc : ptx::smem_desc(4, 16, 512);
+  kp.bx_desc = B.mn_major ? xmn.desc : ptx::smem_desc(4, 16, 512);
+  kp.ax_kstep = A.mn_major ? xmn.kstep_bytes : 32u;
+  kp.bx_kstep = B.mn_major ? xmn.kstep_bytes : 32u;
+  kp.idesc_x = ptx::make_idesc(1u, A.mn_major, B.mn_major, 2 * BLOCK_M, 256);
   auto kern = gemm_tf32x3_pair_kernel<STAGES>;
   static bool attr_done_dev[64] = {};
   int dev = 0;
@@ -2240,6 +2307,13 @@ const char* launch_tf32_pair(uint32_t M, uint32_t N, uint32_t K, const GemmOpera
 }
 
 }  // namespace
+
+bool tf32_takes_pair_kernel(uint32_t M, uint32_t N, uint32_t K, int sm_count, const GemmTuning& tune) {
+  (void)K;
+  if (tune.pair == 0 || !(tune.block_n == 0 || tune.block_n == 256)) return false;
+  const uint64_t pair_tiles = uint64_t((M + 255) / 256) * ((N + 255) / 256);
+  return tune.pair >= 1 || (M >= 256 && N >= 128 && pair_tiles >= uint64_t(sm_count) / 2);
+}
 
 const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const GemmOperand& A,
                         const GemmOperand& B, float* C, uint64_t ldc, const GemmEpilogue& epi,
@@ -2324,11 +2398,9 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
     }
   }
 
-  if (kind == Kind::TF32x3 && !batch && tune.pair != 0 && (tune.block_n == 0 || tune.block_n == 256)) {
-    const uint64_t pair_tiles = uint64_t((M + 255) / 256) * ((N + 255) / 256);
-    if (tune.pair >= 1 || (M >= 256 && N >= 128 && pair_tiles >= uint64_t(sm_count) / 2))
-      return launch_tf32_pair(M, N, K, A, B, kp, sm_count, tune.max_ctas, stream);
-  }
+  if (kind == Kind::TF32x3 && !batch && tf32_takes_pair_kernel(M, N, K, sm_count, tune))
+    return launch_tf32_pair(M, N, K, A, B, kp, sm_count, tune.max_ctas, stream);
+  if (A.plane1_bf16 || B.plane1_bf16) return "bf16 low planes are for the CTA-pair kernel only";
 
   // Tensor maps: inner extent is the contiguous index, outer the row index.
   CUtensorMap maps[4];

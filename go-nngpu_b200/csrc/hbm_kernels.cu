@@ -221,6 +221,65 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
   }
 }
 
+// The same split for the kernel that takes its correction terms from bf16 planes: hi as
+// above, then bf16(hi) and bf16(x - hi) in two planes of `plane` elements behind `x2`.
+// The two cross products hi.lo + lo.hi only have to be good to 2^-8 of themselves (they are
+// 2^-11 of the product), which is what bf16 keeps; it also keeps fp32's exponent range.
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));  // a in the low half
+  return r;
+}
+__global__ void __launch_bounds__(256) split_tf32_bf16_kernel(const float* __restrict__ src,
+                                                              const float* __restrict__ mask,
+                                                              uint64_t rows, uint64_t cols,
+                                                              float* __restrict__ hi,
+                                                              uint16_t* __restrict__ x2,
+                                                              uint64_t pitch, uint64_t plane,
+                                                              int vec) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
+  const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+  const uint64_t start = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  if (vec) {
+    const uint64_t q = cols >> 2;
+    for (RowWalk w(start, stride, q); w.r < rows; w.next(q)) {
+      const uint64_t r = w.r, c = w.g << 2;
+      float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * cols + c));
+      if (mask) {
+        const float4 m = __ldcs(reinterpret_cast<const float4*>(mask + r * cols + c));
+        v.x = m.x > 0.0f ? v.x : 0.0f;
+        v.y = m.y > 0.0f ? v.y : 0.0f;
+        v.z = m.z > 0.0f ? v.z : 0.0f;
+        v.w = m.w > 0.0f ? v.w : 0.0f;
+      }
+      float4 h;
+      h.x = rna_tf32(v.x);
+      h.y = rna_tf32(v.y);
+      h.z = rna_tf32(v.z);
+      h.w = rna_tf32(v.w);
+      *reinterpret_cast<float4*>(hi + r * pitch + c) = h;
+      uint2 hb, lb;
+      hb.x = pack_bf16(h.x, h.y);
+      hb.y = pack_bf16(h.z, h.w);
+      lb.x = pack_bf16(v.x - h.x, v.y - h.y);
+      lb.y = pack_bf16(v.z - h.z, v.w - h.w);
+      *reinterpret_cast<uint2*>(x2 + r * pitch + c) = hb;
+      *reinterpret_cast<uint2*>(x2 + plane + r * pitch + c) = lb;
+    }
+  } else {
+    for (RowWalk w(start, stride, cols); w.r < rows; w.next(cols)) {
+      const uint64_t i = w.r * cols + w.g;
+      float x = src[i];
+      if (mask && !(mask[i] > 0.0f)) x = 0.0f;
+      const float h = rna_tf32(x);
+      hi[w.r * pitch + w.g] = h;
+      x2[w.r * pitch + w.g] = uint16_t(pack_bf16(h, 0.0f) & 0xFFFFu);
+      x2[plane + w.r * pitch + w.g] = uint16_t(pack_bf16(x - h, 0.0f) & 0xFFFFu);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ elementwise
 // Bias broadcast add, the four patterns of
 // internal/cgo/metal_bridge_matrix.m:273-312.
@@ -409,6 +468,16 @@ void launch_split_tf32(const float* src, uint64_t rows, uint64_t cols, float* hi
   const uint64_t items = vec ? rows * (cols / 4) : rows * cols;
   launch_kernel(split_tf32_kernel, dim3(stream_grid(items, 256, 148 * 16)), dim3(256), 0, stream, src, mask, rows, cols, hi,
                                                                            lo, pitch, vec);
+}
+
+void launch_split_tf32_bf16(const float* src, uint64_t rows, uint64_t cols, float* hi, void* x2,
+                            uint64_t pitch, cudaStream_t stream, const float* mask) {
+  if (rows == 0 || cols == 0) return;
+  const int vec = (cols % 4 == 0) && aligned16(src) && aligned16(hi) && aligned16(x2) &&
+                  (pitch % 8 == 0) && (!mask || aligned16(mask));
+  const uint64_t items = vec ? rows * (cols / 4) : rows * cols;
+  launch_kernel(split_tf32_bf16_kernel, dim3(stream_grid(items, 256, 148 * 16)), dim3(256), 0, stream,
+                src, mask, rows, cols, hi, static_cast<uint16_t*>(x2), pitch, rows * pitch, vec);
 }
 
 void launch_add_broadcast(const float* a, const float* b, float* c, uint64_t rows, uint64_t cols,

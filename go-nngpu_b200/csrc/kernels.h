@@ -23,11 +23,15 @@ enum Act : int { ACT_RELU = 0, ACT_LEAKY = 1, ACT_SIGMOID = 2, ACT_TANH = 3, ACT
 // N) index and K is contiguous ("K-major").  `mn_major == true`: rows are the K
 // index and M (or N) is contiguous.  `pitch` is in elements and must make the
 // row pitch a multiple of 16 bytes; `plane1` is the low tf32 plane (TF32x3 only).
+// `plane1_bf16`: plane1 holds instead two bf16 planes of the same shape and pitch, one
+// behind the other: bf16(hi), then bf16(x - hi) (launch_split_tf32_bf16); both operands of
+// a product must agree, and only products that tf32_takes_pair_kernel() accepts may use it.
 struct GemmOperand {
   const void* plane0 = nullptr;
   const void* plane1 = nullptr;
   uint64_t pitch = 0;
   bool mn_major = false;
+  bool plane1_bf16 = false;
 };
 
 // C = act(alpha * A.B + beta * C_in + bias[n])
@@ -79,6 +83,10 @@ const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const Gem
                         GemmStatus* status, int sm_count, const GemmTuning& tune,
                         cudaStream_t stream, const GemmBatch* batch = nullptr);
 
+// True when launch_gemm(Kind::TF32x3, ...) with these sizes runs on the CTA-pair kernel, the
+// one that also takes the correction terms from bf16 planes (GemmOperand::plane1_bf16).
+bool tf32_takes_pair_kernel(uint32_t M, uint32_t N, uint32_t K, int sm_count, const GemmTuning& tune);
+
 // ---- pre-pass: operand planes ---------------------------------------------
 enum F16Mode : int { F16_RN = 0, F16_TRUNC = 1 };
 // fp32 [rows, cols] (pitch cols) -> fp16 plane with `pitch` elements per row.
@@ -88,6 +96,11 @@ void launch_cvt_f16(const float* src, uint64_t rows, uint64_t cols, void* dst, u
 // With `mask` (same shape as src): x is taken as 0 where mask <= 0 (ReLU derivative).
 void launch_split_tf32(const float* src, uint64_t rows, uint64_t cols, float* hi, float* lo,
                        uint64_t pitch, cudaStream_t stream, const float* mask = nullptr);
+
+// fp32 -> hi = rna_tf32(x) as fp32, and behind `x2` two bf16 planes [rows, pitch] one after the
+// other: bf16(hi), then bf16(x - hi).  Same bytes as launch_split_tf32 writes.
+void launch_split_tf32_bf16(const float* src, uint64_t rows, uint64_t cols, float* hi, void* x2,
+                            uint64_t pitch, cudaStream_t stream, const float* mask = nullptr);
 
 // ---- HBM-bound kernels -----------------------------------------------------
 void launch_transpose(const float* in, uint64_t rows, uint64_t cols, float* out, int sm_count,

@@ -297,6 +297,16 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtens
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2), "r"(bar_cluster)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const CUtensorMap* m,
+                                                 int32_t c0, int32_t c1, int32_t c2, int32_t c3,
+                                                 uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+        "r"(bar_cluster)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
                ::"r"(smem_result), "r"(ncols) : "memory");
@@ -419,7 +429,8 @@ __device__ __forceinline__ bool flag_wait(const uint32_t* word, uint32_t wanted,
 //   [0,14) start address >> 4, [16,30) leading byte offset >> 4,
 //   [32,46) stride byte offset >> 4, [46,48) version = 1, [61,64) layout.
 // `layout`: 2 = 128-byte swizzle of 16-byte chunks; 1 = 128-byte swizzle of
-// 32-byte chunks, the only layout tf32 operands may use when MN-major.
+// 32-byte chunks, the only layout tf32 operands may use when MN-major; 4 = 64-byte
+// swizzle (K-major tiles whose rows hold 64 bytes of K: groups of 8 rows, 512 bytes).
 __host__ __device__ constexpr uint64_t smem_desc(uint32_t layout, uint32_t lbo_bytes,
                                                  uint32_t sbo_bytes) {
   return (uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16) | (uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32) |

@@ -487,6 +487,22 @@ def test_fp32_cta_pair_kernel(gpu, shape, layout):
     assert oracle.rel_frobenius(C, oracle.gemm_f64(As, Bs, ta, tb)) <= 2e-6
 
 
+@pytest.mark.parametrize("layout", ["nn", "tn", "nt", "tt"])
+def test_fp32_cta_pair_kernel_wide_dynamic_range_and_chosen_by_size(gpu, layout):
+    """The CTA-pair kernel takes its correction terms from bf16 planes: elements spread over
+    twelve decades (bf16 keeps fp32's exponent range), ragged sizes, and a shape large enough
+    that the library picks the kernel itself."""
+    m, n, k = 2311, 2377, 805
+    rng = np.random.default_rng(77 + len(layout) + ord(layout[0]) * 3 + ord(layout[1]))
+    A = (rng.standard_normal((m, k)) * 10.0 ** rng.integers(-6, 7, (m, k))).astype(np.float32)
+    B = (rng.standard_normal((k, n)) * 10.0 ** rng.integers(-6, 7, (k, n))).astype(np.float32)
+    ta, tb = layout[0] == "t", layout[1] == "t"
+    As = np.ascontiguousarray(A.T) if ta else A
+    Bs = np.ascontiguousarray(B.T) if tb else B
+    C = run_matmul(gpu, As, Bs, ta, tb, precision=gpu.FP32_3XTF32)   # 100 pair tiles: chosen by size
+    assert oracle.rel_frobenius(C, oracle.gemm_f64(As, Bs, ta, tb)) <= 2e-6
+
+
 def test_fp32_cta_pair_kernel_persistent_loop_and_epilogue(gpu):
     rng = np.random.default_rng(91)
     A = rng.integers(-3, 4, (2048, 160)).astype(np.float32)
@@ -505,7 +521,9 @@ def test_fp32_cta_pair_kernel_persistent_loop_and_epilogue(gpu):
 
 
 # ------------------------------------------------------------------ fused linear backward
-@pytest.mark.parametrize("shape", [(1, 1, 1), (33, 70, 10), (130, 257, 99), (512, 784, 1024)])
+# the last two: both products on the CTA-pair kernel; dW on it and dX (small batch) not
+@pytest.mark.parametrize("shape", [(1, 1, 1), (33, 70, 10), (130, 257, 99), (512, 784, 1024),
+                                   (2560, 2304, 2400), (200, 2304, 2400)])
 @pytest.mark.parametrize("masked", [False, True])
 def test_linear_backward_matches_unfused_oracle(gpu, shape, masked):
     """dW, dX, db of a linear layer in one call against the reference's unfused
