@@ -84,10 +84,14 @@ def gemm_case(name, A, B, ta, tb, precision, iters):
     dt = timed(call, iters)
     extra = {"operands": "fresh (pre-pass inside every call)" if FRESH else "converted planes cached"}
     if precision == g.FP32_3XTF32:
-        # three tf32 MMAs are issued per useful product; 1100 TFLOP/s is the nominal dense tf32 rate
-        issued = 3 * 2.0 * M * N * K / dt / 1e12
-        extra.update({"tf32_issued_tflops": round(issued, 1), "frac_of_nominal_tf32_issued": round(issued / 1100.0, 3),
-                      "frac_of_nominal_tf32_useful": round(issued / 3 / 1100.0, 3)})
+        # tensor-pipe work per useful product, in tf32 MMAs: the single-CTA kernel issues three;
+        # the CTA-pair kernel (products of 74 or more 256 x 256 tiles) one tf32 and two bf16 MMAs,
+        # which take the time of two.  1100 TFLOP/s is the nominal dense tf32 rate.
+        pair = M >= 256 and N >= 128 and -(-M // 256) * -(-N // 256) >= 74
+        per = 2 if pair else 3
+        issued = per * 2.0 * M * N * K / dt / 1e12
+        extra.update({"tf32_equivalents_per_product": per, "tf32_equivalent_tflops": round(issued, 1),
+                      "frac_of_nominal_tf32": round(issued / 1100.0, 3)})
     if CPU_LEG:
         # float64 product on the host cores: the comparator the benchmark names is gonum's
         # mat.Dense.Mul, which is not installed here; numpy/OpenBLAS float64 stands in for it
