@@ -649,6 +649,9 @@ def report(args, g, world, rows, total_ms, kernel_ms, resident_ms, ms_per_step, 
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_kind], "unit": "TFLOP/s",
                      "frac": achieved / peaks[peak_kind], "traffic": traffic_estimate(rows),
                      "peak_source": f"{peaks['source']} cuBLAS bf16 ({peak_kind})",
+                     # the same against the other figure of the pair (a 3.4 ms launch repeated for
+                     # 0.2 s runs into the power cap like the sustained loop, not like a burst)
+                     "frac_of_sustained_peak": achieved / peaks["sustained"],
                      "kernel_ms": kernel_ms,
                      "kernel": "gemm_f16_pair_kernel, one launch = one rank's shard"
                                + ("" if world == 1 else " (timed with B resident)")},
