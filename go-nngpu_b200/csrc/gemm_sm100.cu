@@ -2311,8 +2311,11 @@ const char* launch_tf32_pair(uint32_t M, uint32_t N, uint32_t K, const GemmOpera
 bool tf32_takes_pair_kernel(uint32_t M, uint32_t N, uint32_t K, int sm_count, const GemmTuning& tune) {
   (void)K;
   if (tune.pair == 0 || !(tune.block_n == 0 || tune.block_n == 256)) return false;
+  // Measured cross-over against the single-CTA kernel with split-K: level at 32 pair tiles
+  // (2048 x 1024 x 1024: 34 against 37 us), 64 against 91 us at 2048^3 (64 tiles); below it
+  // the pairs have too few tiles to fill the machine (1024^3, 16 tiles: 33 against 21 us).
   const uint64_t pair_tiles = uint64_t((M + 255) / 256) * ((N + 255) / 256);
-  return tune.pair >= 1 || (M >= 256 && N >= 128 && pair_tiles >= uint64_t(sm_count) / 2);
+  return tune.pair >= 1 || (M >= 256 && N >= 128 && pair_tiles >= uint64_t(sm_count) * 2 / 9);
 }
 
 const char* launch_gemm(Kind kind, uint32_t M, uint32_t N, uint32_t K, const GemmOperand& A,

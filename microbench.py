@@ -85,9 +85,9 @@ def gemm_case(name, A, B, ta, tb, precision, iters):
     extra = {"operands": "fresh (pre-pass inside every call)" if FRESH else "converted planes cached"}
     if precision == g.FP32_3XTF32:
         # tensor-pipe work per useful product, in tf32 MMAs: the single-CTA kernel issues three;
-        # the CTA-pair kernel (products of 74 or more 256 x 256 tiles) one tf32 and two bf16 MMAs,
+        # the CTA-pair kernel (products of 32 or more 256 x 256 tiles) one tf32 and two bf16 MMAs,
         # which take the time of two.  1100 TFLOP/s is the nominal dense tf32 rate.
-        pair = M >= 256 and N >= 128 and -(-M // 256) * -(-N // 256) >= 74
+        pair = M >= 256 and N >= 128 and -(-M // 256) * -(-N // 256) >= 32
         per = 2 if pair else 3
         issued = per * 2.0 * M * N * K / dt / 1e12
         extra.update({"tf32_equivalents_per_product": per, "tf32_equivalent_tflops": round(issued, 1),
