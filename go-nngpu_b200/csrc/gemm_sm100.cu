@@ -178,15 +178,23 @@ __device__ __forceinline__ void load_bf16_planes(uint32_t mn_major, const CUtens
   else ptx::tma_load_3d_pair(dst, m, kb * 32, tile * 128, 0, bar);
 }
 
-__device__ __forceinline__ float apply_act(float v, int act, float param) {
+// The epilogues keep their accumulators in registers, so their loops are fully unrolled:
+// 32 to 128 copies of whatever the activation inlines.  With expf / tanhf inlined in every
+// copy the epilogue's code no longer fits the instruction cache, and even a ReLU, which
+// only branches past them, took 11 us longer per launch (512 x 1024 x 1024: 27 against
+// 16 us).  The transcendental activations are therefore one out-of-line function.
+__device__ __noinline__ float apply_act_transcendental(float v, int act) {
   switch (act) {
-    case ACT_RELU: return fmaxf(v, 0.0f);
-    case ACT_LEAKY: return v > 0.0f ? v : v * param;
     case ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
     case ACT_TANH: return tanhf(v);
-    case ACT_GELU: return 0.5f * v * (1.0f + tanhf(0.7978845608f * (v + 0.044715f * v * v * v)));
-    default: return v;
+    default: return 0.5f * v * (1.0f + tanhf(0.7978845608f * (v + 0.044715f * v * v * v)));  // ACT_GELU
   }
+}
+__device__ __forceinline__ float apply_act(float v, int act, float param) {
+  if (act == ACT_RELU) return fmaxf(v, 0.0f);
+  if (act == ACT_LEAKY) return v > 0.0f ? v : v * param;
+  if (act == ACT_SIGMOID || act == ACT_TANH || act == ACT_GELU) return apply_act_transcendental(v, act);
+  return v;
 }
 
 // Raises the CTA's abort flag; true for the one role that raised it.  Only that role reports:
