@@ -1337,10 +1337,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // everything above touched no global memory: from here on the previous kernel's results
-  // are needed (and its reads of our output buffers must be over)
+  // Nothing above touched global memory.  The previous kernel's results are needed (and its
+  // reads of our output buffers and of the split-K workspace must be over) only where a role
+  // first touches global memory: the producer's first load, the drain warps' first store.
+  // Each waits there, so that fetching the kernel parameters and the first tile's index
+  // arithmetic (about 1.3 us between the end of the wait and the first load, measured with
+  // %globaltimer) overlap the previous kernel's tail.
   ptx::grid_dependency_release();
-  ptx::grid_dependency_wait();
   // work units: unit u is split (u % splits) of tile (u / splits); splits == 1 is one unit per tile
   const uint32_t num_units = p.num_tiles * p.splits;
   auto unit_range = [&](uint32_t u, uint32_t& t, uint32_t& kb_lo, uint32_t& kb_hi) {
@@ -1353,6 +1356,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
     // ------------------------------------------------------------ producer
     uint32_t stage = 0, phase = 0;
     bool alive = true;
+    bool waited = false;
     for (uint32_t u = blockIdx.x; alive && u < num_units; u += gridDim.x) {
       uint32_t t, kb_lo, kb_hi;
       unit_range(u, t, kb_lo, kb_hi);
@@ -1371,6 +1375,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
         }
         if (lane == 0) {
           const uint32_t fb = full_bar(stage);
+          if (!waited) {
+            ptx::grid_dependency_wait();
+            waited = true;
+          }
           ptx::mbar_arrive_expect_tx(fb, STAGE_BYTES);
           uint32_t dst = smem_base + stage * STAGE_BYTES;
 #pragma unroll
@@ -1458,6 +1466,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
     uint32_t sk_parity = 0;
     const uint32_t tid_d = threadIdx.x - 64u;  // 0..255 among the drain threads
     bool alive = true;
+    bool waited = false;
     for (uint32_t u = blockIdx.x; alive && u < num_units; u += gridDim.x) {
       uint32_t t, kb_lo, kb_hi;
       unit_range(u, t, kb_lo, kb_hi);
@@ -1487,6 +1496,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a0,
         if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
       }
       if (!alive) break;
+      if (!waited) {
+        ptx::grid_dependency_wait();
+        waited = true;
+      }
       if (p.splits > 1) {
         // Partial sums to the workspace, [unit][4 columns][thread] so that a warp's
         // 16-byte stores are contiguous; then the tile's counter says who came last.
