@@ -1688,14 +1688,16 @@ int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOu
     set_error(err, "linear backward: host to device copy failed.");
     return -6;
   }
-  // bias gradient: column sums of the masked gradient
-  if (db) {
+  // bias gradient: column sums of the masked gradient (in the same pass as the operand planes
+  // of that gradient when the products are asked for too, see below)
+  auto bias_gradient = [&] {
     gonn::launch_colsum(dY->dptr, uint64_t(batch), uint64_t(out_size), db->dptr, d.stream,
                         act ? act->dptr : nullptr, d.splitk_ws, kSplitKBytes / 4, d.splitk_counters,
                         kSplitKSlots);
     ++g_stats[3];
     wrote(db);
-  }
+  };
+  if (db && !dX && !dW) bias_gradient();
   int rc = 0;
   if (dX || dW) {
     // operand planes of dAct = dY (.) [actOut > 0]: the mask is applied while the
@@ -1721,12 +1723,26 @@ int gonngpu_linear_backward(GPUPtr xPtr, GPUPtr wPtr, GPUPtr dyPtr, GPUPtr actOu
       set_error(err, "linear backward: could not allocate operand planes.");
       return -5;
     }
-    if (need_lo) {
+    // one kind of low planes and the bias gradient wanted: one kernel writes the planes and
+    // the column sums
+    bool summed = false;
+    if (db && need_lo != need_x2) {
+      summed = gonn::launch_split_colsum(dY->dptr, uint64_t(batch), uint64_t(out_size), static_cast<float*>(hi),
+                                         need_x2 ? x2 : lo, need_x2, pitch, db->dptr, d.stream,
+                                         act ? act->dptr : nullptr, d.splitk_ws, kSplitKBytes / 4,
+                                         d.splitk_counters, kSplitKSlots);
+      if (summed) {
+        ++g_stats[3];
+        wrote(db);
+      }
+    }
+    if (db && !summed) bias_gradient();
+    if (need_lo && !summed) {
       gonn::launch_split_tf32(dY->dptr, uint64_t(batch), uint64_t(out_size), static_cast<float*>(hi),
                               static_cast<float*>(lo), pitch, d.stream, act ? act->dptr : nullptr);
       ++g_stats[3];
     }
-    if (need_x2) {  // writes the same hi
+    if (need_x2 && !summed) {  // writes the same hi
       gonn::launch_split_tf32_bf16(dY->dptr, uint64_t(batch), uint64_t(out_size), static_cast<float*>(hi),
                                    x2, pitch, d.stream, act ? act->dptr : nullptr);
       ++g_stats[3];

@@ -420,6 +420,108 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ i
   }
 }
 
+// The split of a layer's output gradient and its column sums (the bias gradient) in one pass:
+// the linear backward needs both of the same masked values.  Blocks as in colsum_kernel, each
+// thread four neighbouring columns: block (x, y) walks rows [y * chunk_rows, (y + 1) * chunk_rows)
+// of 128 columns, writes their operand planes (tf32 hi/lo, or hi and the two bf16 planes) and
+// adds them up; partial sums and the block that arrives last as in colsum_kernel.
+// cols % 4 == 0 and 16-byte aligned bases (the launcher checks).
+template <bool BF16X>
+__global__ void __launch_bounds__(256) split_colsum_kernel(const float* __restrict__ src,
+                                                           const float* __restrict__ mask,
+                                                           uint64_t rows, uint64_t cols,
+                                                           float* __restrict__ hi, void* low,
+                                                           uint64_t pitch, uint64_t plane,
+                                                           float* __restrict__ out,
+                                                           uint64_t chunk_rows, float* partial,
+                                                           uint32_t* counters) {
+  ptx::grid_dependency_release();  // programmatic dependent launch: see launch.cuh
+  ptx::grid_dependency_wait();
+  __shared__ float4 part[8][33];
+  __shared__ uint32_t last;
+  const uint32_t cx = threadIdx.x & 31u, ry = threadIdx.x >> 5;
+  const uint64_t c = (blockIdx.x * 32ull + cx) << 2;
+  const uint64_t r0 = blockIdx.y * chunk_rows;
+  const uint64_t r1 = (r0 + chunk_rows < rows) ? r0 + chunk_rows : rows;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c < cols)
+    for (uint64_t r = r0 + ry; r < r1; r += 8) {
+      float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * cols + c));
+      if (mask) {
+        const float4 m = __ldcs(reinterpret_cast<const float4*>(mask + r * cols + c));
+        v.x = m.x > 0.0f ? v.x : 0.0f;
+        v.y = m.y > 0.0f ? v.y : 0.0f;
+        v.z = m.z > 0.0f ? v.z : 0.0f;
+        v.w = m.w > 0.0f ? v.w : 0.0f;
+      }
+      s.x += v.x;
+      s.y += v.y;
+      s.z += v.z;
+      s.w += v.w;
+      float4 h;
+      h.x = rna_tf32(v.x);
+      h.y = rna_tf32(v.y);
+      h.z = rna_tf32(v.z);
+      h.w = rna_tf32(v.w);
+      *reinterpret_cast<float4*>(hi + r * pitch + c) = h;
+      if (BF16X) {
+        uint16_t* x2 = static_cast<uint16_t*>(low);
+        uint2 hb, lb;
+        hb.x = pack_bf16(h.x, h.y);
+        hb.y = pack_bf16(h.z, h.w);
+        lb.x = pack_bf16(v.x - h.x, v.y - h.y);
+        lb.y = pack_bf16(v.z - h.z, v.w - h.w);
+        *reinterpret_cast<uint2*>(x2 + r * pitch + c) = hb;
+        *reinterpret_cast<uint2*>(x2 + plane + r * pitch + c) = lb;
+      } else {
+        float4 l;
+        l.x = rna_tf32(v.x - h.x);
+        l.y = rna_tf32(v.y - h.y);
+        l.z = rna_tf32(v.z - h.z);
+        l.w = rna_tf32(v.w - h.w);
+        *reinterpret_cast<float4*>(static_cast<float*>(low) + r * pitch + c) = l;
+      }
+    }
+  part[ry][cx] = s;
+  __syncthreads();
+  float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (ry == 0) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      t.x += part[k][cx].x;
+      t.y += part[k][cx].y;
+      t.z += part[k][cx].z;
+      t.w += part[k][cx].w;
+    }
+  }
+  if (gridDim.y == 1) {
+    if (ry == 0 && c < cols) *reinterpret_cast<float4*>(out + c) = t;
+    return;
+  }
+  if (ry == 0 && c < cols) __stcg(reinterpret_cast<float4*>(partial + uint64_t(blockIdx.y) * cols + c), t);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t before = atomicAdd(counters + blockIdx.x, 1u);
+    last = (before + 1u == gridDim.y) ? 1u : 0u;
+    if (last) counters[blockIdx.x] = 0u;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  if (ry == 0 && c < cols) {
+    float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t k = 0; k < gridDim.y; ++k) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + uint64_t(k) * cols + c));
+      total.x += v.x;
+      total.y += v.y;
+      total.z += v.z;
+      total.w += v.w;
+    }
+    *reinterpret_cast<float4*>(out + c) = total;
+  }
+}
+
 inline uint32_t stream_grid(uint64_t work_items, uint32_t threads, uint32_t cap) {
   uint64_t g = (work_items + threads - 1) / threads;
   if (g < 1) g = 1;
@@ -478,6 +580,35 @@ void launch_split_tf32_bf16(const float* src, uint64_t rows, uint64_t cols, floa
   const uint64_t items = vec ? rows * (cols / 4) : rows * cols;
   launch_kernel(split_tf32_bf16_kernel, dim3(stream_grid(items, 256, 148 * 16)), dim3(256), 0, stream,
                 src, mask, rows, cols, hi, static_cast<uint16_t*>(x2), pitch, rows * pitch, vec);
+}
+
+bool launch_split_colsum(const float* src, uint64_t rows, uint64_t cols, float* hi, void* low, bool bf16x,
+                         uint64_t pitch, float* colsum, cudaStream_t stream, const float* mask, float* ws,
+                         size_t ws_floats, uint32_t* counters, uint32_t counter_slots) {
+  if (rows == 0 || cols == 0) return false;
+  if (cols % 4 || pitch % 8 || !aligned16(src) || !aligned16(hi) || !aligned16(low) || !aligned16(colsum) ||
+      (mask && !aligned16(mask)))
+    return false;
+  const uint32_t col_blocks = uint32_t((cols + 127) / 128);
+  // row chunks of at least 32 rows, enough of them to put about four blocks on every SM
+  uint64_t chunks = 1;
+  if (ws && counters && aligned16(ws) && col_blocks <= counter_slots && rows >= 64) {
+    chunks = std::min<uint64_t>(rows / 32, std::max<uint64_t>(1, 592 / col_blocks));
+    while (chunks > 1 && chunks * cols > ws_floats) --chunks;
+  }
+  uint64_t chunk_rows = (rows + chunks - 1) / chunks;
+  chunk_rows = (chunk_rows + 7) / 8 * 8;
+  chunks = (rows + chunk_rows - 1) / chunk_rows;
+  if (chunks < 1) chunks = 1;
+  if (chunks > 65535) return false;
+  const dim3 grid(col_blocks, uint32_t(chunks));
+  if (bf16x)
+    launch_kernel(split_colsum_kernel<true>, grid, dim3(256), 0, stream, src, mask, rows, cols, hi, low, pitch,
+                  rows * pitch, colsum, chunk_rows, ws, counters);
+  else
+    launch_kernel(split_colsum_kernel<false>, grid, dim3(256), 0, stream, src, mask, rows, cols, hi, low, pitch,
+                  rows * pitch, colsum, chunk_rows, ws, counters);
+  return true;
 }
 
 void launch_add_broadcast(const float* a, const float* b, float* c, uint64_t rows, uint64_t cols,

@@ -102,6 +102,15 @@ void launch_split_tf32(const float* src, uint64_t rows, uint64_t cols, float* hi
 void launch_split_tf32_bf16(const float* src, uint64_t rows, uint64_t cols, float* hi, void* x2,
                             uint64_t pitch, cudaStream_t stream, const float* mask = nullptr);
 
+// Both of the above and the column sums of the same (masked) values in one pass, for the linear
+// backward: `low` is the lo plane or, with `bf16x`, the two bf16 planes; `colsum` gets `cols`
+// sums.  `ws` / `counters` as for launch_colsum.  Returns false without launching when the
+// shape or an address does not allow 16-byte accesses (the caller then launches the two
+// kernels separately).
+bool launch_split_colsum(const float* src, uint64_t rows, uint64_t cols, float* hi, void* low, bool bf16x,
+                         uint64_t pitch, float* colsum, cudaStream_t stream, const float* mask, float* ws,
+                         size_t ws_floats, uint32_t* counters, uint32_t counter_slots);
+
 // ---- HBM-bound kernels -----------------------------------------------------
 void launch_transpose(const float* in, uint64_t rows, uint64_t cols, float* out, int sm_count,
                       cudaStream_t stream);

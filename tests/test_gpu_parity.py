@@ -385,6 +385,25 @@ def test_buffer_protocol(gpu):
 
 
 # ------------------------------------------------------------------ CTA-pair (2-SM MMA) fp16 kernels
+def test_released_buffers_small_and_large_come_back_from_the_cache(gpu):
+    """A released block goes to the per-device cache (small ones in 512-byte classes) and the
+    next buffer of that class takes it from there; gonngpu_trim_cache empties the cache."""
+    import gc
+    g = gpu
+    gc.collect()
+    g.lib().gonngpu_trim_cache()
+    assert g.stats()["cached_bytes"] == 0
+    for nbytes, cls in ((40, 512), (4000, 4096), (4096, 4096), (3 << 20, 3 << 20)):
+        a = g.Buffer.empty(nbytes)
+        held = g.stats()["hbm_bytes"]
+        a.release()
+        assert g.stats()["cached_bytes"] == cls and g.stats()["hbm_bytes"] == held - nbytes
+        b = g.Buffer.empty(cls - 1 if cls <= 4096 else cls)      # same class: served from the cache
+        assert g.stats()["cached_bytes"] == 0
+        b.release()
+        assert g.lib().gonngpu_trim_cache() == cls and g.stats()["cached_bytes"] == 0
+
+
 @pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("shape", [(256, 256, 64), (512, 256, 256), (1024, 512, 512), (600, 400, 136),
                                    (130, 300, 200), (257, 129, 65), (2048, 2048, 1024)])
