@@ -213,6 +213,49 @@ def apply_act_f64(z, act, alpha=0.0):
     return z
 
 
+# ---------------------------------------------------------------- model of the fp32-accuracy splits
+# The CUDA fp32 path multiplies splits of its operands on the tensor cores.  These functions
+# restate the splits (not the tensor cores: products and sums are exact here), so that a test
+# can bound what the splits alone cost and show that small integers pass through unchanged.
+def _round_mantissa(x, keep, ties_away):
+    """float32 -> float32 with `keep` explicit mantissa bits (exponent range unchanged):
+    ties away from zero (cvt.rna.tf32) or to even (cvt.rn.bf16)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    drop = np.uint64(23 - keep)
+    half = np.uint64(1) << (drop - np.uint64(1))
+    if ties_away:
+        u = u + half
+    else:
+        u = u + (half - np.uint64(1)) + ((u >> drop) & np.uint64(1))
+    u = (u >> drop) << drop
+    return u.astype(np.uint32).view(np.float32)
+
+
+def split_tf32(x):
+    """(hi, lo): hi = rna_tf32(x), lo = rna_tf32(x - hi), as the pre-pass of the single-CTA kernel."""
+    hi = _round_mantissa(x, 10, True)
+    return hi, _round_mantissa((np.asarray(x, np.float32) - hi).astype(np.float32), 10, True)
+
+
+def split_tf32_bf16(x):
+    """(hi, bf16(hi), bf16(x - hi)) as the pre-pass of the CTA-pair kernel."""
+    hi = _round_mantissa(x, 10, True)
+    return hi, _round_mantissa(hi, 7, False), _round_mantissa((np.asarray(x, np.float32) - hi).astype(np.float32), 7, False)
+
+
+def gemm_split_model(A, B, bf16_corrections):
+    """A.B from the splits with exact arithmetic: hi.hi + hi.lo + lo.hi (lo.lo is dropped), the
+    two correction products from tf32 or from bf16 planes."""
+    f = lambda X, Y: X.astype(np.float64) @ Y.astype(np.float64)  # noqa: E731
+    if bf16_corrections:
+        ah, ahb, alb = split_tf32_bf16(A)
+        bh, bhb, blb = split_tf32_bf16(B)
+        return f(ah, bh) + f(ahb, blb) + f(alb, bhb)
+    ah, al = split_tf32(A)
+    bh, bl = split_tf32(B)
+    return f(ah, bh) + f(ah, bl) + f(al, bh)
+
+
 # Seeded inputs of the benchmark configurations: numpy PCG64, drawn in float64
 # in the order listed, cast to float32, row-major.
 def config1(n=1024):

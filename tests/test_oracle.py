@@ -2,6 +2,7 @@
 vectors, against the committed golden file, and against independent numpy
 restatements."""
 import numpy as np
+import pytest
 
 from oracle import oracle
 
@@ -159,3 +160,43 @@ def test_softmax_elu_swish_gelu_against_reference_properties(golden):
     G = rng.standard_normal((7, 33)).astype(np.float32)
     assert np.allclose(oracle.softmax_backward(G, sm.astype(np.float32)),
                        sm * (G - (G * sm).sum(axis=1, keepdims=True)), atol=1e-6)
+
+
+# ---------------------------------------------------------------- the fp32-accuracy splits
+@pytest.mark.parametrize("bf16", [False, True])
+def test_split_model_stays_far_below_the_fp32_tolerance(bf16):
+    """What the operand splits of the CUDA fp32 path cost by themselves (exact products and
+    sums): below 1e-6 relative Frobenius error for both kinds of correction planes, on
+    benchmark-like data, on all-positive data and on elements spread over twelve decades; the
+    stated tolerance of the path is 1e-5."""
+    rng = np.random.default_rng(11)
+    k = 1024
+    cases = {
+        "normal": ((rng.standard_normal((96, k)) / np.sqrt(k)), (rng.standard_normal((k, 80)) / np.sqrt(k))),
+        "uniform": (rng.random((96, k)), rng.random((k, 80))),
+        "decades": (rng.standard_normal((96, k)) * 10.0 ** rng.integers(-6, 7, (96, k)),
+                    rng.standard_normal((k, 80)) * 10.0 ** rng.integers(-6, 7, (k, 80))),
+    }
+    for name, (A, B) in cases.items():
+        A, B = A.astype(np.float32), B.astype(np.float32)
+        err = oracle.rel_frobenius(oracle.gemm_split_model(A, B, bf16), oracle.gemm_f64(A, B))
+        assert err <= (1e-6 if bf16 else 2e-7), (name, err)
+
+
+def test_split_model_is_exact_on_small_integers_and_splits_add_up():
+    rng = np.random.default_rng(12)
+    A = rng.integers(-8, 9, (40, 300)).astype(np.float32)
+    B = rng.integers(-8, 9, (300, 24)).astype(np.float32)
+    for bf16 in (False, True):
+        assert np.array_equal(oracle.gemm_split_model(A, B, bf16), oracle.gemm_f64(A, B))
+    x = (rng.standard_normal(4096) * 10.0 ** rng.integers(-20, 20, 4096)).astype(np.float32)
+    hi, lo = oracle.split_tf32(x)
+    assert np.all(np.abs(x.astype(np.float64) - hi.astype(np.float64) - lo.astype(np.float64))
+                  <= np.abs(x.astype(np.float64)) * 2.0 ** -21)
+    assert np.all((hi.view(np.uint32) & 0x1FFF) == 0) and np.all((lo.view(np.uint32) & 0x1FFF) == 0)
+    hi2, hb, lb = oracle.split_tf32_bf16(x)
+    assert np.array_equal(hi, hi2)
+    assert np.all((hb.view(np.uint32) & 0xFFFF) == 0) and np.all((lb.view(np.uint32) & 0xFFFF) == 0)
+    # bf16(hi) is hi to 2^-9, bf16(lo) is x - hi to 2^-9 of itself
+    assert np.all(np.abs(hb.astype(np.float64) - hi) <= np.abs(hi.astype(np.float64)) * 2.0 ** -8)
+    assert np.all(np.abs(lb.astype(np.float64) - (x.astype(np.float64) - hi)) <= np.abs(x.astype(np.float64) - hi) * 2.0 ** -8 + 1e-45)
